@@ -1,0 +1,146 @@
+/*
+ * sla_b200 -- C ABI of the B200 (sm_100a) implementation of the SLA attention hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle. The caller owns
+ * all memory (inputs, outputs and workspaces); except where an entry point says otherwise the
+ * library allocates nothing, keeps no pointer after returning, enqueues all work on the given
+ * stream and never synchronises. Return value: SLA_OK (0) or a negative sla_status.
+ *
+ * Tensor layouts (all contiguous, row-major):
+ *   q, k, v, o, o_s, do, dq, dk, dv : (B, H, L, D)     16-bit float given by sla_shape.dtype
+ *   lse, delta                      : (B, H, L)        fp32, log2 units of the scaled score
+ *   lut                             : (B, H, M_BLOCKS, topk) int32, ascending inside a row
+ *   sparse_map                      : (B, H, M_BLOCKS, N_BLOCKS) int8 0/1
+ *   col_offsets                     : (B, H, N_BLOCKS + 1) int32   } per-KV-block list of the
+ *   col_index                       : (B, H, M_BLOCKS * topk) int32 } query blocks that selected it
+ *   lin_state                       : (B, H, D*D + D)  16-bit: H = phi(k)^T v then z = sum phi(k)
+ *   w, bias                         : (D, D), (D)      fp32 (nn.Linear parameters of proj_l)
+ * with M_BLOCKS = ceil(L / BLKQ), N_BLOCKS = ceil(L / BLKK).
+ *
+ * "Replaces" comments name the reference (thu-ml/SLA) interface each entry point stands in for,
+ * by path inside that project.
+ */
+#ifndef SLA_B200_H_
+#define SLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* sla_stream_t; /* a cudaStream_t / CUstream */
+
+#if defined(__GNUC__)
+#define SLA_API __attribute__((visibility("default")))
+#else
+#define SLA_API
+#endif
+
+enum sla_status {
+  SLA_OK = 0,
+  SLA_ERR_BAD_SHAPE = -1,   /* unsupported D / BLKQ / BLKK / empty tensor */
+  SLA_ERR_BAD_DTYPE = -2,
+  SLA_ERR_BAD_ALIGN = -3,   /* a tensor pointer is not 16-byte aligned */
+  SLA_ERR_BAD_TOPK = -4,    /* topk < 1 or topk > N_BLOCKS (the reference divides 0/0 there) */
+  SLA_ERR_WS_TOO_SMALL = -5,
+  SLA_ERR_WRONG_ARCH = -6,  /* the current device is not compute capability 10.x */
+  SLA_ERR_CUDA = -7,        /* a CUDA runtime call failed; see sla_last_cuda_error() */
+  SLA_ERR_TIMEOUT = -8,     /* a bounded device-side wait ran out */
+  SLA_ERR_NULL = -9,        /* a required pointer is NULL */
+  SLA_ERR_UNSUPPORTED = -10
+};
+
+enum sla_dtype { SLA_BF16 = 0, SLA_FP16 = 1, SLA_FP32 = 2 };
+enum sla_feature { SLA_PHI_SOFTMAX = 0, SLA_PHI_RELU = 1, SLA_PHI_ELU = 2 };
+enum sla_op { SLA_OP_BLOCK_MAP = 0, SLA_OP_FWD = 1, SLA_OP_BWD = 2, SLA_OP_LINEAR_STATE = 3,
+              SLA_OP_SAGE_FWD = 4 };
+enum sla_flags {
+  SLA_FLAG_SPARSE_ONLY = 1, /* skip the linear branch and proj_l (the `_attention` operator) */
+  SLA_FLAG_LEGACY_MMA = 2   /* use the mma.sync kernels instead of the tcgen05 ones */
+};
+
+typedef struct sla_shape {
+  int32_t B, H, L, D;     /* D in {64, 128} */
+  int32_t BLKQ, BLKK;     /* BLKQ in {64, 128}, BLKK == 64 (kernel.py:247-248) */
+  int32_t topk;           /* selected KV blocks per query block, see sla_topk_count */
+  int32_t dtype;          /* SLA_BF16 or SLA_FP16: element type of q,k,v,o and of the MMAs */
+  int32_t feature_map;    /* sla_feature */
+  int32_t flags;          /* sla_flags */
+  float qk_scale;         /* softmax scale; 0 selects D^-0.5 (kernel.py:251-252) */
+} sla_shape;
+
+SLA_API int sla_version(void);
+SLA_API const char* sla_status_string(int status);
+/* Text of the last CUDA runtime error seen by the calling thread inside this library. */
+SLA_API const char* sla_last_cuda_error(void);
+/* Diagnostic: number of kernels this library has launched in the process so far. */
+SLA_API long long sla_launch_count(void);
+
+/* Replaces sparse_linear_attention/utils.py:61-62: min(n_blocks, int(topk_ratio * n_blocks)). */
+SLA_API int sla_topk_count(int n_blocks, double topk_ratio);
+
+/* Bytes of caller-provided workspace `op` needs for `shape` (a multiple of 256). */
+SLA_API size_t sla_workspace_bytes(const sla_shape* shape, int op);
+
+/*
+ * Replaces sparse_linear_attention/utils.py:55-67 get_block_map (with mean_pool / compress_kernel,
+ * utils.py:21-52). q and k are in `in_dtype` (any sla_dtype: the reference predicts the mask on the
+ * tensors as given, core.py:83). Writes lut (required); sparse_map, col_offsets + col_index are
+ * optional (NULL to skip; the column lists need sparse_map or workspace room for it).
+ * Ties at the k-th score go to the lower block index.
+ */
+SLA_API int sla_block_map(const sla_shape* shape, int in_dtype, const void* q, const void* k,
+                  int32_t* lut, int8_t* sparse_map, int32_t* col_offsets, int32_t* col_index,
+                  void* ws, size_t ws_bytes, sla_stream_t stream);
+
+/* Builds the per-KV-block query-block lists from a 0/1 block map. Stands in for the way
+ * sparse_linear_attention/kernel.py:208-210 consults k_block_id inside the dK/dV kernel: callers
+ * that bring their own sparse_map (the `_attention.apply` signature, kernel.py:242) convert it once. */
+SLA_API int sla_column_lists(const sla_shape* shape, const int8_t* sparse_map, int32_t* col_offsets,
+                             int32_t* col_index, sla_stream_t stream);
+
+/* Replaces sparse_linear_attention/kernel.py:242-274 _attention.forward (+ _attn_fwd :21-82). */
+SLA_API int sla_sparse_fwd(const sla_shape* shape, const void* q, const void* k, const void* v,
+                   const int32_t* lut, void* o_s, float* lse, sla_stream_t stream);
+
+/* Replaces sparse_linear_attention/kernel.py:277-320 _attention.backward (+ kernels :85-237).
+ * delta (B,H,L) fp32 is written by the call. If `accumulate` is non-zero dq/dk/dv already hold
+ * a contribution (the linear branch's) that is added to the sparse one. */
+SLA_API int sla_sparse_bwd(const sla_shape* shape, const void* q, const void* k, const void* v,
+                   const void* o_s, const float* lse, const void* do_s, const int32_t* lut,
+                   const int32_t* col_offsets, const int32_t* col_index, void* dq, void* dk,
+                   void* dv, float* delta, int accumulate, sla_stream_t stream);
+
+/* Replaces the feature map on k and the two state reductions of
+ * sparse_linear_attention/core.py:91,93-94 (kvsum, ksum). Writes lin_state. */
+SLA_API int sla_linear_state(const sla_shape* shape, const void* k, const void* v, void* lin_state,
+                     void* ws, size_t ws_bytes, sla_stream_t stream);
+
+/* Replaces sparse_linear_attention/core.py:88-100 (everything in SparseLinearAttention.forward
+ * after get_block_map and the dtype casts): sparse branch, feature maps, linear branch, proj_l and
+ * the final sum. o_s may be NULL when no backward will follow. lin_state and lse are outputs. */
+SLA_API int sla_fwd(const sla_shape* shape, const void* q, const void* k, const void* v,
+            const int32_t* lut, const float* w, const float* bias, void* o, void* o_s, float* lse,
+            void* lin_state, void* ws, size_t ws_bytes, sla_stream_t stream);
+
+/* Replaces the autograd backward of sparse_linear_attention/core.py:88-100 (kernel.py:277-320 for
+ * the sparse branch; PyTorch autograd of core.py:90-100 for the rest). dw (D,D) and dbias (D) are
+ * fp32 and are OVERWRITTEN with this call's gradient. */
+SLA_API int sla_bwd(const sla_shape* shape, const void* q, const void* k, const void* v, const void* o_s,
+            const float* lse, const void* d_o, const int32_t* lut, const int32_t* col_offsets,
+            const int32_t* col_index, const float* w, const void* lin_state, void* dq, void* dk,
+            void* dv, float* dw, float* dbias, void* ws, size_t ws_bytes, sla_stream_t stream);
+
+/* Replaces SageSLA/core.py:100-158 (SageSparseLinearAttention.forward after get_block_map and the
+ * casts): INT8 Q.K^T with per-block scales and K-mean smoothing, FP8 e4m3 P.V, then the same
+ * linear branch and proj_l. BLKQ must be 128 and BLKK 64 (SageSLA/README.md:16-17). */
+SLA_API int sage_sla_fwd(const sla_shape* shape, const void* q, const void* k, const void* v,
+                 const int32_t* lut, const float* w, const float* bias, void* o, void* lin_state,
+                 void* ws, size_t ws_bytes, sla_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLA_B200_H_ */

@@ -1,0 +1,93 @@
+"""ctypes binding of libsla_b200.so, the C-ABI library declared in include/sla_b200.h.
+
+The library is the product: there is no Python or CPU fallback. Importing this module without the
+built shared object raises, and every call converts a negative status into an exception.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsla_b200.so")
+
+SLA_BF16, SLA_FP16, SLA_FP32 = 0, 1, 2
+PHI = {"softmax": 0, "relu": 1, "elu": 2}
+OP_BLOCK_MAP, OP_FWD, OP_BWD, OP_LINEAR_STATE, OP_SAGE_FWD = 0, 1, 2, 3, 4
+FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA = 1, 2
+
+# every symbol include/sla_b200.h declares
+EXPORTS = (
+    "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_topk_count", "sla_workspace_bytes",
+    "sla_block_map", "sla_column_lists", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_fwd", "sla_bwd",
+    "sage_sla_fwd",
+)
+
+
+class SlaShape(C.Structure):
+    _fields_ = [
+        ("B", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("D", C.c_int32),
+        ("BLKQ", C.c_int32), ("BLKK", C.c_int32), ("topk", C.c_int32), ("dtype", C.c_int32),
+        ("feature_map", C.c_int32), ("flags", C.c_int32), ("qk_scale", C.c_float),
+    ]
+
+
+class SlaError(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"sla_b200 status {status}: {text}")
+        self.status = status
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python sla_b200/build.py` (needs nvcc). "
+            "sla_b200 has no fallback path.")
+    lib = C.CDLL(LIB_PATH)
+    vp, i32p, f32p, i8p = C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p
+    sp = C.POINTER(SlaShape)
+    lib.sla_version.restype = C.c_int
+    lib.sla_status_string.restype = C.c_char_p
+    lib.sla_status_string.argtypes = [C.c_int]
+    lib.sla_last_cuda_error.restype = C.c_char_p
+    lib.sla_launch_count.restype = C.c_longlong
+    lib.sla_topk_count.restype = C.c_int
+    lib.sla_topk_count.argtypes = [C.c_int, C.c_double]
+    lib.sla_workspace_bytes.restype = C.c_size_t
+    lib.sla_workspace_bytes.argtypes = [sp, C.c_int]
+    lib.sla_block_map.restype = C.c_int
+    lib.sla_block_map.argtypes = [sp, C.c_int, vp, vp, i32p, i8p, i32p, i32p, vp, C.c_size_t, vp]
+    lib.sla_column_lists.restype = C.c_int
+    lib.sla_column_lists.argtypes = [sp, i8p, i32p, i32p, vp]
+    lib.sla_sparse_fwd.restype = C.c_int
+    lib.sla_sparse_fwd.argtypes = [sp, vp, vp, vp, i32p, vp, f32p, vp]
+    lib.sla_sparse_bwd.restype = C.c_int
+    lib.sla_sparse_bwd.argtypes = [sp, vp, vp, vp, vp, f32p, vp, i32p, i32p, i32p, vp, vp, vp, f32p, C.c_int, vp]
+    lib.sla_linear_state.restype = C.c_int
+    lib.sla_linear_state.argtypes = [sp, vp, vp, vp, vp, C.c_size_t, vp]
+    lib.sla_fwd.restype = C.c_int
+    lib.sla_fwd.argtypes = [sp, vp, vp, vp, i32p, f32p, f32p, vp, vp, f32p, vp, vp, C.c_size_t, vp]
+    lib.sla_bwd.restype = C.c_int
+    lib.sla_bwd.argtypes = [sp, vp, vp, vp, vp, f32p, vp, i32p, i32p, i32p, f32p, vp, vp, vp, vp, f32p, f32p,
+                            vp, C.c_size_t, vp]
+    lib.sage_sla_fwd.restype = C.c_int
+    lib.sage_sla_fwd.argtypes = [sp, vp, vp, vp, i32p, f32p, f32p, vp, vp, vp, C.c_size_t, vp]
+    return lib
+
+
+lib = _load()
+
+
+def check(status: int) -> None:
+    if status == 0:
+        return
+    text = lib.sla_status_string(status).decode()
+    if status == -7:
+        text += " -- " + lib.sla_last_cuda_error().decode()
+    if status == -10:
+        raise NotImplementedError(f"sla_b200 status {status}: {text}")
+    raise SlaError(status, text)
+
+
+def topk_count(n_blocks: int, ratio: float) -> int:
+    return int(lib.sla_topk_count(int(n_blocks), float(ratio)))

@@ -1,0 +1,103 @@
+"""Module level: the reference's two nn.Modules with unchanged constructor / forward signatures.
+
+SparseLinearAttention      <- sparse_linear_attention/core.py:24-105
+SageSparseLinearAttention  <- SageSLA/core.py:33-163
+
+Parameters keep the reference's names, shapes and dtype (``proj_l.weight`` (D,D) fp32,
+``proj_l.bias`` (D) fp32, zero-initialised), so reference checkpoints load unchanged.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import ops
+
+_FEATURES = ("elu", "relu", "softmax")
+
+
+class SparseLinearAttention(nn.Module):
+    def __init__(self, head_dim, topk, feature_map="softmax", BLKQ=64, BLKK=64, use_bf16=True,
+                 tie_feature_map_qk=True):
+        R"""
+        Args:
+            head_dim: dimension of each head (64 or 128).
+            topk: ratio of keys selected for sparse attention, shared across all queries.
+            feature_map: feature map for linear attention, one of ['elu', 'relu', 'softmax'].
+            BLKQ: block size for query (64 or 128).
+            BLKK: block size for key (64).
+            use_bf16: bfloat16 (default) or float16 computation; the cast is done inside the module.
+            tie_feature_map_qk: kept for signature compatibility; q and k always share the map type
+                (in the reference both choices select the same function, core.py:43-60).
+        """
+        super().__init__()
+        self.dtype = torch.bfloat16 if use_bf16 else torch.float16
+        self.topk = topk
+        self.BLKQ = BLKQ
+        self.BLKK = BLKK
+        self.proj_l = nn.Linear(head_dim, head_dim, dtype=torch.float32)
+        if feature_map not in _FEATURES:
+            raise NotImplementedError(f"Not supported feature map {feature_map}.")
+        self.feature_map = feature_map
+        self.tie_feature_map_qk = tie_feature_map_qk
+        self.impl_flags = 0
+        self.init_weights_()
+
+    def init_weights_(self):
+        with torch.no_grad():
+            nn.init.zeros_(self.proj_l.weight)
+            nn.init.zeros_(self.proj_l.bias)
+
+    def forward(self, q, k, v, return_sparsity=False):
+        R"""
+        Args:
+            q, k, v: (B, H, L, D) CUDA tensors (any float dtype; output has q's dtype).
+            return_sparsity: also return topk / N_BLOCKS, the kept fraction of KV blocks.
+        """
+        dtype = q.dtype
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        need_grad = torch.is_grad_enabled() and (
+            q.requires_grad or k.requires_grad or v.requires_grad or self.proj_l.weight.requires_grad)
+        bm = ops.block_map(q, k, self.topk, self.BLKQ, self.BLKK, want_cols=need_grad)  # on the given dtype
+        q, k, v = q.to(self.dtype), k.to(self.dtype), v.to(self.dtype)
+        o = ops.sla_attention(q, k, v, self.proj_l.weight, self.proj_l.bias, bm, self.BLKQ, self.BLKK,
+                              self.feature_map, self.impl_flags)
+        o = o.to(dtype)
+        if return_sparsity:
+            return o, bm.topk / bm.n_blocks
+        return o
+
+
+class SageSparseLinearAttention(nn.Module):
+    def __init__(self, head_dim, topk, feature_map="softmax", use_bf16=True, tie_feature_map_qk=True,
+                 BLKQ=128, BLKK=64):
+        R"""Quantized forward (INT8 QK^T, FP8 PV). Same arguments as the reference; BLKQ/BLKK are
+        accepted because the reference's README passes them, and must be 128/64."""
+        super().__init__()
+        if BLKQ != 128 or BLKK != 64:
+            raise ValueError("SageSLA only supports BLKQ=128 and BLKK=64")
+        self.dtype = torch.bfloat16 if use_bf16 else torch.float16
+        self.topk = topk
+        self.proj_l = nn.Linear(head_dim, head_dim, dtype=torch.float32)
+        if feature_map not in _FEATURES:
+            raise NotImplementedError(f"Not supported feature map {feature_map}.")
+        self.feature_map = feature_map
+        self.init_weights_()
+
+    def init_weights_(self):
+        with torch.no_grad():
+            nn.init.zeros_(self.proj_l.weight)
+            nn.init.zeros_(self.proj_l.bias)
+
+    def forward(self, q, k, v, return_sparsity=False):
+        dtype = q.dtype
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        assert q.size(-1) in [64, 128], "headdim should be in [64, 128]."
+        bm = ops.block_map(q, k, self.topk, 128, 64)
+        q, k, v = q.to(self.dtype), k.to(self.dtype), v.to(self.dtype)
+        with torch.no_grad():
+            o = ops.sage_sla_attention(q, k, v, self.proj_l.weight, self.proj_l.bias, bm, self.feature_map)
+        o = o.to(dtype)
+        if return_sparsity:
+            return o, bm.topk / bm.n_blocks
+        return o

@@ -1,0 +1,398 @@
+// Block-mask prediction: K column mean -> pooled Q / pooled (K - mean) -> pooled scores -> per-row
+// top-k -> block LUT (+ optional 0/1 map and per-KV-block column lists).
+// Follows sparse_linear_attention/utils.py:21-67 including its rounding points: the column mean, the
+// smoothed K, the pooled means and the pooled scores are each rounded to the input dtype.
+// All kernels here are HBM/L2-bound integer/compare work; none uses tensor cores.
+#include "common.cuh"
+#include "workspace.h"
+
+namespace sla {
+
+template <typename TIn>
+struct VecLoad {
+  static constexpr int N = 16 / sizeof(TIn);
+  __device__ static inline void load(float (&out)[N], const TIn* p) {
+    uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const TIn* e = reinterpret_cast<const TIn*>(&raw);
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = Elem<TIn>::to_f(e[i]);
+  }
+};
+
+// ---- 1. column sums of K over chunks of rows: partial[bh][chunk][D] (fp32) ----
+template <typename TIn, int D>
+__global__ void __launch_bounds__(256) colsum_kernel(const TIn* __restrict__ k, float* __restrict__ partial,
+                                                     int L, int nch) {
+  constexpr int N = VecLoad<TIn>::N;
+  constexpr int TPR = D / N;       // threads per row
+  constexpr int RP = 256 / TPR;    // rows per pass
+  __shared__ float red[RP][D];
+  int bh = blockIdx.y, ch = blockIdx.x;
+  int tid = threadIdx.x, rg = tid / TPR, c = (tid % TPR) * N;
+  int row0 = ch * kColsumRows, row1 = min(L, row0 + kColsumRows);
+  const TIn* base = k + static_cast<size_t>(bh) * L * D;
+  float acc[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) acc[i] = 0.f;
+  for (int r = row0 + rg; r < row1; r += RP) {
+    float v[N];
+    VecLoad<TIn>::load(v, base + static_cast<size_t>(r) * D + c);
+#pragma unroll
+    for (int i = 0; i < N; ++i) acc[i] += v[i];
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) red[rg][c + i] = acc[i];
+  __syncthreads();
+  if (tid < D) {
+    float s = 0.f;
+#pragma unroll 4
+    for (int g = 0; g < RP; ++g) s += red[g][tid];
+    partial[(static_cast<size_t>(bh) * nch + ch) * D + tid] = s;
+  }
+}
+
+// ---- 2. mean[bh][d] = round_T(sum / L) (torch.mean keeps the input dtype, utils.py:56) ----
+template <typename TIn>
+__global__ void kmean_finalize_kernel(const float* __restrict__ partial, float* __restrict__ kmean, int L,
+                                      int nch, int D) {
+  int bh = blockIdx.x, d = threadIdx.x;
+  if (d >= D) return;
+  float s = 0.f;
+  for (int c = 0; c < nch; ++c) s += partial[(static_cast<size_t>(bh) * nch + c) * D + d];
+  kmean[static_cast<size_t>(bh) * D + d] = round_to<TIn>(s / static_cast<float>(L));
+}
+
+// ---- 3. mean pooling of Q (z = 0) and of K - mean (z = 1), utils.py:21-40 ----
+template <typename TIn, int D>
+__global__ void __launch_bounds__(256) pool_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k,
+                                                   const float* __restrict__ kmean, TIn* __restrict__ pooled_q,
+                                                   TIn* __restrict__ pooled_k, int L, int blkq, int blkk) {
+  constexpr int N = VecLoad<TIn>::N;
+  constexpr int TPR = D / N;
+  constexpr int RP = 256 / TPR;
+  __shared__ float red[RP][D];
+  const bool is_k = blockIdx.z == 1;
+  const int blk = is_k ? blkk : blkq;
+  const int nblk = (L + blk - 1) / blk;
+  if (static_cast<int>(blockIdx.x) >= nblk) return;
+  int bh = blockIdx.y, ib = blockIdx.x;
+  int tid = threadIdx.x, rg = tid / TPR, c = (tid % TPR) * N;
+  int row0 = ib * blk, row1 = min(L, row0 + blk);
+  const TIn* base = (is_k ? k : q) + static_cast<size_t>(bh) * L * D;
+  float mean[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) mean[i] = is_k ? kmean[static_cast<size_t>(bh) * D + c + i] : 0.f;
+  float acc[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) acc[i] = 0.f;
+  for (int r = row0 + rg; r < row1; r += RP) {
+    float v[N];
+    VecLoad<TIn>::load(v, base + static_cast<size_t>(r) * D + c);
+#pragma unroll
+    for (int i = 0; i < N; ++i) acc[i] += is_k ? round_to<TIn>(v[i] - mean[i]) : v[i];
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) red[rg][c + i] = acc[i];
+  __syncthreads();
+  if (tid < D) {
+    float s = 0.f;
+#pragma unroll 4
+    for (int g = 0; g < RP; ++g) s += red[g][tid];
+    float nx = static_cast<float>(row1 - row0);
+    TIn* out = (is_k ? pooled_k : pooled_q) + (static_cast<size_t>(bh) * nblk + ib) * D;
+    out[tid] = Elem<TIn>::from_f(s / nx);
+  }
+}
+
+// ---- 4. pooled scores + per-row top-k ----
+__device__ inline uint32_t order_key(float x) {
+  uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+constexpr int kTopkRows = 8;  // query-block rows per CTA == warps per CTA
+
+// One CTA scores kTopkRows query-block rows against every KV block of the head, then each warp
+// selects the top-k of one row by a 4-pass radix select on order-preserving keys and writes the
+// selected indices in ascending order; ties at the k-th score go to the lower index.
+template <typename TIn, int D>
+__global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
+    const TIn* __restrict__ pooled_q, const TIn* __restrict__ pooled_k, int32_t* __restrict__ lut,
+    int8_t* __restrict__ sparse_map, int32_t* __restrict__ col_offsets, int mb, int nb, int topk) {
+  constexpr int N = VecLoad<TIn>::N;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* spq = reinterpret_cast<float*>(smem_raw);                        // [R][D]
+  uint32_t* hist = reinterpret_cast<uint32_t*>(spq + kTopkRows * D);       // [R][256]
+  uint32_t* keys = hist + kTopkRows * 256;                                 // [R][nb]
+  const int bh = blockIdx.y, row_base = blockIdx.x * kTopkRows;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  for (int i = tid; i < kTopkRows * D; i += blockDim.x) {
+    int r = i / D, d = i % D;
+    int row = row_base + r;
+    spq[i] = row < mb ? Elem<TIn>::to_f(pooled_q[(static_cast<size_t>(bh) * mb + row) * D + d]) : 0.f;
+  }
+  __syncthreads();
+
+  const TIn* pk = pooled_k + static_cast<size_t>(bh) * nb * D;
+  for (int j = tid; j < nb; j += blockDim.x) {
+    float acc[kTopkRows];
+#pragma unroll
+    for (int r = 0; r < kTopkRows; ++r) acc[r] = 0.f;
+#pragma unroll 2
+    for (int c = 0; c < D; c += N) {
+      float kv[N];
+      VecLoad<TIn>::load(kv, pk + static_cast<size_t>(j) * D + c);
+#pragma unroll
+      for (int r = 0; r < kTopkRows; ++r) {
+#pragma unroll
+        for (int e = 0; e < N; e += 4) {
+          float4 qv = *reinterpret_cast<const float4*>(spq + r * D + c + e);
+          acc[r] = fmaf(qv.x, kv[e], acc[r]);
+          acc[r] = fmaf(qv.y, kv[e + 1], acc[r]);
+          acc[r] = fmaf(qv.z, kv[e + 2], acc[r]);
+          acc[r] = fmaf(qv.w, kv[e + 3], acc[r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kTopkRows; ++r) keys[r * nb + j] = order_key(round_to<TIn>(acc[r]));  // utils.py:59
+  }
+  __syncthreads();
+
+  const int row = row_base + warp;
+  if (row >= mb) return;
+  const uint32_t* kr = keys + warp * nb;
+  uint32_t* h = hist + warp * 256;
+  // radix select: find the key of the topk-th largest element
+  uint32_t prefix = 0, prefix_mask = 0;
+  int need = topk;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int b = lane; b < 256; b += 32) h[b] = 0;
+    __syncwarp();
+    for (int j = lane; j < nb; j += 32) {
+      uint32_t key = kr[j];
+      if ((key & prefix_mask) == prefix) atomicAdd(&h[(key >> shift) & 255u], 1u);
+    }
+    __syncwarp();
+    // lane owns bins [255 - 8*lane - 7, 255 - 8*lane], scanned from the top
+    uint32_t cnt[8];
+    uint32_t lane_sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      cnt[i] = h[255 - 8 * lane - i];
+      lane_sum += cnt[i];
+    }
+    uint32_t incl = lane_sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    uint32_t excl = incl - lane_sum;
+    bool owner = excl < static_cast<uint32_t>(need) && incl >= static_cast<uint32_t>(need);
+    uint32_t sel_bin = 0, above = 0;
+    if (owner) {
+      uint32_t run = excl;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (run < static_cast<uint32_t>(need) && run + cnt[i] >= static_cast<uint32_t>(need)) {
+          sel_bin = 255 - 8 * lane - i;
+          above = run;
+        }
+        run += cnt[i];
+      }
+    }
+    uint32_t ob = __ballot_sync(0xffffffffu, owner);
+    int src = __ffs(ob) - 1;
+    sel_bin = __shfl_sync(0xffffffffu, sel_bin, src);
+    above = __shfl_sync(0xffffffffu, above, src);
+    need -= static_cast<int>(above);
+    prefix |= sel_bin << shift;
+    prefix_mask |= 255u << shift;
+    __syncwarp();
+  }
+  const uint32_t thr = prefix;  // key of the k-th largest; `need` of the elements equal to it are taken
+  int32_t* out = lut + (static_cast<size_t>(bh) * mb + row) * topk;
+  int8_t* map_row = sparse_map ? sparse_map + (static_cast<size_t>(bh) * mb + row) * nb : nullptr;
+  int32_t* cols = col_offsets ? col_offsets + static_cast<size_t>(bh) * (nb + 1) : nullptr;
+  int n_out = 0, eq_seen = 0;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  for (int base = 0; base < nb; base += 32) {
+    int j = base + lane;
+    uint32_t key = j < nb ? kr[j] : 0u;
+    bool gt = j < nb && key > thr;
+    bool eq = j < nb && key == thr;
+    uint32_t be = __ballot_sync(0xffffffffu, eq);
+    int eq_rank = eq_seen + __popc(be & lt_mask);
+    bool sel = gt || (eq && eq_rank < need);
+    uint32_t bs = __ballot_sync(0xffffffffu, sel);
+    if (sel) {
+      out[n_out + __popc(bs & lt_mask)] = j;
+      if (cols) atomicAdd(&cols[j + 1], 1);
+    }
+    if (map_row && j < nb) map_row[j] = sel ? 1 : 0;
+    n_out += __popc(bs);
+    eq_seen += __popc(be);
+  }
+}
+
+// ---- 5. column lists: in-place inclusive scan of the per-column counts ----
+__global__ void __launch_bounds__(1024) col_scan_kernel(int32_t* __restrict__ col_offsets, int nb) {
+  __shared__ int32_t warp_tot[32];
+  int32_t* c = col_offsets + static_cast<size_t>(blockIdx.x) * (nb + 1);
+  int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int per = (nb + 1 + 1023) / 1024;
+  int lo = tid * per, hi = min(nb + 1, lo + per);
+  int32_t s = 0;
+  for (int i = lo; i < hi; ++i) s += c[i];
+  int32_t incl = s;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int32_t w = warp_tot[lane], wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int32_t t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += t;
+    }
+    warp_tot[lane] = wi - w;
+  }
+  __syncthreads();
+  int32_t run = warp_tot[warp] + incl - s;
+  for (int i = lo; i < hi; ++i) {
+    run += c[i];
+    c[i] = run;
+  }
+}
+
+// ---- 6. column lists: for KV block j the ascending list of query blocks whose row selects j ----
+__global__ void __launch_bounds__(1024) col_fill_kernel(const int8_t* __restrict__ sparse_map,
+                                                        const int32_t* __restrict__ col_offsets,
+                                                        int32_t* __restrict__ col_index, int mb, int nb,
+                                                        int topk) {
+  int bh = blockIdx.y;
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int j = blockIdx.x * 32 + warp;
+  if (j >= nb) return;
+  const int8_t* m = sparse_map + static_cast<size_t>(bh) * mb * nb;
+  int32_t* out = col_index + static_cast<size_t>(bh) * mb * topk;
+  int pos = col_offsets[static_cast<size_t>(bh) * (nb + 1) + j];
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  for (int i0 = 0; i0 < mb; i0 += 32) {
+    int i = i0 + lane;
+    bool f = i < mb && m[static_cast<size_t>(i) * nb + j] != 0;
+    uint32_t b = __ballot_sync(0xffffffffu, f);
+    if (f) out[pos + __popc(b & lt_mask)] = i;
+    pos += __popc(b);
+  }
+}
+
+// ---- 6b. per-column counts straight from a 0/1 map (for maps not produced by sla_block_map) ----
+__global__ void __launch_bounds__(1024) col_count_kernel(const int8_t* __restrict__ sparse_map,
+                                                         int32_t* __restrict__ col_offsets, int mb, int nb) {
+  int bh = blockIdx.y;
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int j = blockIdx.x * 32 + warp;
+  if (j >= nb) return;
+  const int8_t* m = sparse_map + static_cast<size_t>(bh) * mb * nb;
+  int cnt = 0;
+  for (int i0 = 0; i0 < mb; i0 += 32) {
+    int i = i0 + lane;
+    bool f = i < mb && m[static_cast<size_t>(i) * nb + j] != 0;
+    cnt += __popc(__ballot_sync(0xffffffffu, f));
+  }
+  if (lane == 0) col_offsets[static_cast<size_t>(bh) * (nb + 1) + j + 1] = cnt;
+}
+
+template <typename TIn, int D>
+static int launch_block_map(const sla_shape* s, const TIn* q, const TIn* k, int32_t* lut, int8_t* sparse_map,
+                            int32_t* col_offsets, int32_t* col_index, unsigned char* ws, cudaStream_t st) {
+  const int bh = s->B * s->H, L = s->L;
+  const int mb = ceil_div(L, s->BLKQ), nb = ceil_div(L, s->BLKK);
+  WsBlockMap w = ws_block_map(s);
+  float* partial = reinterpret_cast<float*>(ws + w.colsum_partial);
+  float* kmean = reinterpret_cast<float*>(ws + w.kmean);
+  TIn* pq = reinterpret_cast<TIn*>(ws + w.pooled_q);
+  TIn* pk = reinterpret_cast<TIn*>(ws + w.pooled_k);
+  const bool want_cols = col_offsets != nullptr && col_index != nullptr;
+  if (want_cols && sparse_map == nullptr) sparse_map = reinterpret_cast<int8_t*>(ws + w.map);
+
+  colsum_kernel<TIn, D><<<dim3(w.nch, bh), 256, 0, st>>>(k, partial, L, w.nch);
+  SLA_LAUNCH_OK();
+  kmean_finalize_kernel<TIn><<<bh, D, 0, st>>>(partial, kmean, L, w.nch, D);
+  SLA_LAUNCH_OK();
+  pool_kernel<TIn, D><<<dim3(max(mb, nb), bh, 2), 256, 0, st>>>(q, k, kmean, pq, pk, L, s->BLKQ, s->BLKK);
+  SLA_LAUNCH_OK();
+  if (want_cols) SLA_CUDA_OK(cudaMemsetAsync(col_offsets, 0, sizeof(int32_t) * size_t(bh) * (nb + 1), st));
+  size_t smem = size_t(kTopkRows) * (D + 256 + nb) * 4;
+  if (smem > 200 * 1024) return SLA_ERR_BAD_SHAPE;
+  auto kern = score_topk_kernel<TIn, D>;
+  SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  kern<<<dim3(ceil_div(mb, kTopkRows), bh), kTopkRows * 32, smem, st>>>(
+      pq, pk, lut, sparse_map, want_cols ? col_offsets : nullptr, mb, nb, s->topk);
+  SLA_LAUNCH_OK();
+  if (want_cols) {
+    col_scan_kernel<<<bh, 1024, 0, st>>>(col_offsets, nb);
+    SLA_LAUNCH_OK();
+    col_fill_kernel<<<dim3(ceil_div(nb, 32), bh), 1024, 0, st>>>(sparse_map, col_offsets, col_index, mb, nb,
+                                                                s->topk);
+    SLA_LAUNCH_OK();
+  }
+  return SLA_OK;
+}
+
+}  // namespace sla
+
+extern "C" int sla_column_lists(const sla_shape* s, const int8_t* sparse_map, int32_t* col_offsets,
+                                int32_t* col_index, sla_stream_t stream) {
+  using namespace sla;
+  if (!s || !sparse_map || !col_offsets || !col_index) return SLA_ERR_NULL;
+  if (s->B < 1 || s->H < 1 || s->L < 1 || s->BLKQ < 1 || s->BLKK < 1) return SLA_ERR_BAD_SHAPE;
+  int rc = check_device_arch();
+  if (rc != SLA_OK) return rc;
+  const int bh = s->B * s->H, mb = ceil_div(s->L, s->BLKQ), nb = ceil_div(s->L, s->BLKK);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  SLA_CUDA_OK(cudaMemsetAsync(col_offsets, 0, sizeof(int32_t) * size_t(bh) * (nb + 1), st));
+  col_count_kernel<<<dim3(ceil_div(nb, 32), bh), 1024, 0, st>>>(sparse_map, col_offsets, mb, nb);
+  SLA_LAUNCH_OK();
+  col_scan_kernel<<<bh, 1024, 0, st>>>(col_offsets, nb);
+  SLA_LAUNCH_OK();
+  col_fill_kernel<<<dim3(ceil_div(nb, 32), bh), 1024, 0, st>>>(sparse_map, col_offsets, col_index, mb, nb, s->topk);
+  SLA_LAUNCH_OK();
+  return SLA_OK;
+}
+
+extern "C" int sla_block_map(const sla_shape* s, int in_dtype, const void* q, const void* k, int32_t* lut,
+                             int8_t* sparse_map, int32_t* col_offsets, int32_t* col_index, void* ws,
+                             size_t ws_bytes, sla_stream_t stream) {
+  using namespace sla;
+  if (s == nullptr || q == nullptr || k == nullptr || lut == nullptr || ws == nullptr) return SLA_ERR_NULL;
+  if (s->B < 1 || s->H < 1 || s->L < 1 || (s->D != 64 && s->D != 128)) return SLA_ERR_BAD_SHAPE;
+  if (s->BLKQ < 16 || s->BLKK < 16 || s->BLKQ > 1024 || s->BLKK > 1024) return SLA_ERR_BAD_SHAPE;
+  if (static_cast<long long>(s->B) * s->H > 65535) return SLA_ERR_BAD_SHAPE;
+  int nb = ceil_div(s->L, s->BLKK);
+  if (s->topk < 1 || s->topk > nb) return SLA_ERR_BAD_TOPK;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(ws)) return SLA_ERR_BAD_ALIGN;
+  if ((col_offsets == nullptr) != (col_index == nullptr)) return SLA_ERR_NULL;
+  if (ws_bytes < ws_block_map(s).total) return SLA_ERR_WS_TOO_SMALL;
+  int rc = check_device_arch();
+  if (rc != SLA_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned char* w = static_cast<unsigned char*>(ws);
+#define SLA_BM(TIn, DD) \
+  return launch_block_map<TIn, DD>(s, static_cast<const TIn*>(q), static_cast<const TIn*>(k), lut, sparse_map, \
+                                   col_offsets, col_index, w, st)
+  switch (in_dtype) {
+    case SLA_BF16: if (s->D == 64) SLA_BM(__nv_bfloat16, 64); else SLA_BM(__nv_bfloat16, 128);
+    case SLA_FP16: if (s->D == 64) SLA_BM(__half, 64); else SLA_BM(__half, 128);
+    case SLA_FP32: if (s->D == 64) SLA_BM(float, 64); else SLA_BM(float, 128);
+    default: return SLA_ERR_BAD_DTYPE;
+  }
+#undef SLA_BM
+}

@@ -1,0 +1,140 @@
+// extern "C" entry points of the attention operators: argument checks, workspace carving, launches.
+#include <initializer_list>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "workspace.h"
+
+using namespace sla;
+
+namespace {
+
+int check_common(const sla_shape* s) {
+  int rc = validate_shape(s);
+  if (rc != SLA_OK) return rc;
+  return check_device_arch();
+}
+
+bool all_aligned(std::initializer_list<const void*> ps) {
+  for (const void* p : ps)
+    if (p != nullptr && !aligned16(p)) return false;
+  return true;
+}
+
+FwdParams make_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+                   void* o, void* o_s, float* lse, const void* lin_state, const void* wbits) {
+  FwdParams p;
+  p.q = q; p.k = k; p.v = v; p.lut = lut; p.o = o; p.o_s = o_s; p.lse = lse;
+  p.lin_state = lin_state; p.wbits = wbits;
+  p.L = s->L; p.mb = ceil_div(s->L, s->BLKQ); p.topk = s->topk;
+  p.scale_log2 = softmax_scale(s) * kLog2e;
+  return p;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sla_sparse_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+                   void* o_s, float* lse, sla_stream_t stream) {
+  if (!q || !k || !v || !lut || !o_s || !lse) return SLA_ERR_NULL;
+  int rc = check_common(s);
+  if (rc != SLA_OK) return rc;
+  if (!all_aligned({q, k, v, o_s})) return SLA_ERR_BAD_ALIGN;
+  FwdParams p = make_fwd(s, q, k, v, lut, o_s, nullptr, lse, nullptr, nullptr);
+  return run_sparse_fwd_mma(s, p, false, static_cast<cudaStream_t>(stream));
+}
+
+int sla_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, void* ws,
+                     size_t ws_bytes, sla_stream_t stream) {
+  if (!k || !v || !lin_state || !ws) return SLA_ERR_NULL;
+  int rc = check_common(s);
+  if (rc != SLA_OK) return rc;
+  if (!all_aligned({k, v, lin_state, ws})) return SLA_ERR_BAD_ALIGN;
+  WsLinearState w = ws_linear_state(s);
+  if (ws_bytes < w.total) return SLA_ERR_WS_TOO_SMALL;
+  return run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + w.partial),
+                          w.nch, w.rows, static_cast<cudaStream_t>(stream));
+}
+
+int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+            const float* w, const float* bias, void* o, void* o_s, float* lse, void* lin_state, void* ws,
+            size_t ws_bytes, sla_stream_t stream) {
+  if (!q || !k || !v || !lut || !o || !lse) return SLA_ERR_NULL;
+  int rc = check_common(s);
+  if (rc != SLA_OK) return rc;
+  if (!all_aligned({q, k, v, o, o_s, lin_state, ws})) return SLA_ERR_BAD_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (s->flags & SLA_FLAG_SPARSE_ONLY) {
+    FwdParams p = make_fwd(s, q, k, v, lut, o, nullptr, lse, nullptr, nullptr);
+    return run_sparse_fwd_mma(s, p, false, st);
+  }
+  if (!w || !lin_state || !ws) return SLA_ERR_NULL;
+  WsLinearState wl = ws_linear_state(s);
+  if (ws_bytes < wl.total + ws_fwd_extra(s)) return SLA_ERR_WS_TOO_SMALL;
+  unsigned char* base = static_cast<unsigned char*>(ws);
+  void* wbits = base + wl.total;
+  rc = convert_proj(s, w, bias, wbits, st);
+  if (rc != SLA_OK) return rc;
+  rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wl.partial), wl.nch, wl.rows, st);
+  if (rc != SLA_OK) return rc;
+  FwdParams p = make_fwd(s, q, k, v, lut, o, o_s, lse, lin_state, wbits);
+  return run_sparse_fwd_mma(s, p, true, st);
+}
+
+int sla_sparse_bwd(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s,
+                   const float* lse, const void* do_s, const int32_t* lut, const int32_t* col_offsets,
+                   const int32_t* col_index, void* dq, void* dk, void* dv, float* delta, int accumulate,
+                   sla_stream_t stream) {
+  if (!q || !k || !v || !o_s || !lse || !do_s || !lut || !col_offsets || !col_index || !dq || !dk || !dv ||
+      !delta)
+    return SLA_ERR_NULL;
+  int rc = check_common(s);
+  if (rc != SLA_OK) return rc;
+  if (!all_aligned({q, k, v, o_s, do_s, dq, dk, dv})) return SLA_ERR_BAD_ALIGN;
+  BwdParams p;
+  p.q = q; p.k = k; p.v = v; p.o_s = o_s; p.d_o = do_s; p.lse = lse; p.delta = delta; p.lut = lut;
+  p.col_offsets = col_offsets; p.col_index = col_index; p.dq = dq; p.dk = dk; p.dv = dv;
+  p.L = s->L; p.mb = ceil_div(s->L, s->BLKQ); p.nb = ceil_div(s->L, s->BLKK); p.topk = s->topk;
+  p.scale = softmax_scale(s); p.scale_log2 = p.scale * kLog2e; p.accumulate = accumulate;
+  return run_sparse_bwd_mma(s, p, static_cast<cudaStream_t>(stream));
+}
+
+int sla_bwd(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s, const float* lse,
+            const void* d_o, const int32_t* lut, const int32_t* col_offsets, const int32_t* col_index,
+            const float* w, const void* lin_state, void* dq, void* dk, void* dv, float* dw, float* dbias,
+            void* ws, size_t ws_bytes, sla_stream_t stream) {
+  if (!ws) return SLA_ERR_NULL;
+  int rc = check_common(s);
+  if (rc != SLA_OK) return rc;
+  WsBwd wb = ws_bwd(s);
+  // delta lives at the end of the workspace
+  size_t delta_off = wb.total;
+  size_t need = delta_off + round256(size_t(s->B) * s->H * s->L * 4);
+  if (ws_bytes < need) return SLA_ERR_WS_TOO_SMALL;
+  unsigned char* base = static_cast<unsigned char*>(ws);
+  float* delta = reinterpret_cast<float*>(base + delta_off);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int accumulate = 0;
+  if (!(s->flags & SLA_FLAG_SPARSE_ONLY)) {
+    if (!w || !lin_state || !dw || !dbias || !q || !k || !v || !d_o || !dq || !dk || !dv) return SLA_ERR_NULL;
+    if (!all_aligned({q, k, v, d_o, dq, dk, dv, lin_state, ws})) return SLA_ERR_BAD_ALIGN;
+    rc = convert_proj(s, w, nullptr, base + wb.wbits, st);
+    if (rc != SLA_OK) return rc;
+    LinBwdParams lp;
+    lp.q = q; lp.k = k; lp.v = v; lp.d_o = d_o; lp.lin_state = lin_state; lp.wbits = base + wb.wbits; lp.w = w;
+    lp.dq = dq; lp.dk = dk; lp.dv = dv;
+    lp.g_partial = reinterpret_cast<float*>(base + wb.g_partial);
+    lp.dh = base + wb.dh;
+    lp.dz = reinterpret_cast<float*>(base + wb.dz);
+    lp.dw_part = reinterpret_cast<float*>(base + wb.dw_part);
+    lp.dw = dw; lp.dbias = dbias; lp.L = s->L; lp.nch = wb.nch; lp.rows = wb.rows;
+    rc = run_linear_bwd(s, lp, st);
+    if (rc != SLA_OK) return rc;
+    accumulate = 1;
+  }
+  return sla_sparse_bwd(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, delta, accumulate,
+                        stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,56 @@
+// Internal launch interfaces shared by the translation units of libsla_b200.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/sla_b200.h"
+
+namespace sla {
+
+struct FwdParams {
+  const void *q, *k, *v;
+  const int32_t* lut;
+  void* o;                // final output (or o_s when the linear branch is skipped)
+  void* o_s;              // optional copy of the sparse branch output (needed by the backward)
+  float* lse;
+  const void* lin_state;  // [BH][D*D + D] 16-bit: H then z
+  const void* wbits;      // [D*D + D] 16-bit: W then bias
+  int L, mb, topk;
+  float scale_log2;       // softmax scale * log2(e)
+};
+
+struct BwdParams {
+  const void *q, *k, *v, *o_s, *d_o;
+  const float* lse;
+  float* delta;
+  const int32_t* lut;
+  const int32_t* col_offsets;
+  const int32_t* col_index;
+  void *dq, *dk, *dv;
+  int L, mb, nb, topk;
+  float scale, scale_log2;
+  int accumulate;         // dq/dk/dv already hold the linear branch's contribution
+};
+
+struct LinBwdParams {
+  const void *q, *k, *v, *d_o;
+  const void* lin_state;  // H, z (16-bit)
+  const void* wbits;      // W (16-bit)
+  const float* w;         // W fp32
+  void *dq, *dk, *dv;     // written (not accumulated) with the linear branch's gradients
+  float* g_partial;       // [BH][NCH][D*D + 2D]
+  void* dh;               // [BH][D*D] 16-bit
+  float* dz;              // [BH][D]
+  float* dw_part;         // [BH][D*D + D]
+  float *dw, *dbias;
+  int L, nch, rows;
+};
+
+int convert_proj(const sla_shape* s, const float* w, const float* bias, void* out, cudaStream_t st);
+int run_sparse_fwd_mma(const sla_shape* s, const FwdParams& p, bool lin, cudaStream_t st);
+int run_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, float* partial,
+                     int nch, int rows, cudaStream_t st);
+int run_sparse_bwd_mma(const sla_shape* s, const BwdParams& p, cudaStream_t st);
+int run_linear_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_t st);
+
+}  // namespace sla

@@ -1,0 +1,318 @@
+// Backward of the linear branch and of proj_l (the reference leaves this to PyTorch autograd of
+// sparse_linear_attention/core.py:90-100). With dY the gradient of the module output:
+//   do_l = dY W                      dnum = do_l / den          dden = -sum_d(do_l * o_l) / den
+//   dphi_q = dnum H^T + dden z       dq_lin = phi'(q) dphi_q
+//   G = sum_l dY_l^T (phi_q,l / den_l)                       (one D x D reduction per head)
+//   dH = G^T W,  dW = sum_heads G H,  dz = sum_l dden_l phi_q,l,  db = sum_l dY_l
+//   dphi_k = v dH^T + dz             dk_lin = phi'(k) dphi_k    dv_lin = phi_k dH
+// Pass A (per query rows) writes dq_lin and per-chunk partials of G, dz, db; a per-head reduction
+// turns them into dH, dz and the head's share of dW, db; pass B (per key rows) writes dk_lin, dv_lin.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace sla {
+
+// ---------------------------------------------------------------------------------------------
+// Pass A
+// ---------------------------------------------------------------------------------------------
+template <typename T, int D, int FEAT>
+__global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams p) {
+  constexpr int NW = D / 16, NT = NW * 32, KS = D / 16;
+  constexpr int TILE = D * D * 2;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* sH = smem;
+  unsigned char* sW = sH + TILE;
+  unsigned char* sQ = sW + TILE;    // Q rows, then dq staging, then phi(q)/den
+  unsigned char* sdY = sQ + TILE;
+  float* s_z = reinterpret_cast<float*>(sdY + TILE);  // [D]
+  float* s_rowc = s_z + D;                            // [D] dden*den per row of the tile
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int ch = blockIdx.x, bh = blockIdx.y;
+  const int L = p.L;
+  const size_t head_off = static_cast<size_t>(bh) * L * D;
+  const T* qg = static_cast<const T*>(p.q) + head_off;
+  const T* dyg = static_cast<const T*>(p.d_o) + head_off;
+  T* dqg = static_cast<T*>(p.dq) + head_off;
+  const T* hs = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (D * D + D);
+  const T* wb = static_cast<const T*>(p.wbits);
+  const uint32_t sH_a = smem_u32(sH), sW_a = smem_u32(sW), sQ_a = smem_u32(sQ), sdY_a = smem_u32(sdY);
+  const int m0 = warp * 16;
+
+  load_tile_async<D, D>(sH_a, hs, 0, D, tid, NT);
+  load_tile_async<D, D>(sW_a, wb, 0, D, tid, NT);
+  cp_async_commit();
+  for (int i = tid; i < D; i += NT) s_z[i] = Elem<T>::to_f(hs[D * D + i]);
+
+  float gacc[D / 8][4];  // rows [16*warp, +16) of G[n][i]
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) gacc[j][0] = gacc[j][1] = gacc[j][2] = gacc[j][3] = 0.f;
+  float vec_acc = 0.f;   // thread tid < D: dz[tid]; tid >= D: db[tid - D]
+
+  const int row_begin = ch * p.rows, row_end = min(L, row_begin + p.rows);
+  for (int row0 = row_begin; row0 < row_end; row0 += D) {
+    load_tile_async<D, D>(sQ_a, qg, row0, L, tid, NT);
+    load_tile_async<D, D>(sdY_a, dyg, row0, L, tid, NT);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    uint32_t pq[KS][4];
+    {
+      uint32_t qf[KS][4];
+      load_a_frags<D, KS>(qf, sQ_a, m0, 0, lane);
+      feature_map_frags<T, KS, FEAT>(pq, qf);
+    }
+    float acc[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    gemm_b_kn<T, D, D / 8, KS>(acc, pq, sH_a, 0, 0, lane);  // num = phi(q) H
+    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        float2 ph = Elem<T>::unpack2(pq[kk][r]);
+        int col = 16 * kk + (r >> 1) * 8 + 2 * t;
+        float a = round_to<T>(ph.x * s_z[col]) + round_to<T>(ph.y * s_z[col + 1]);
+        if (r & 1) d1 += a; else d0 += a;
+      }
+    }
+    d0 = round_to<T>(1e-5f + round_to<T>(quad_sum(d0)));
+    d1 = round_to<T>(1e-5f + round_to<T>(quad_sum(d1)));
+    const float rd0 = 1.f / d0, rd1 = 1.f / d1;
+    uint32_t ol[KS][4];  // o_l = num / den in T
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      acc[j][0] = round_to<T>(acc[j][0]) * rd0;
+      acc[j][1] = round_to<T>(acc[j][1]) * rd0;
+      acc[j][2] = round_to<T>(acc[j][2]) * rd1;
+      acc[j][3] = round_to<T>(acc[j][3]) * rd1;
+    }
+    acc_to_a_frags<T, KS>(ol, acc);
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    gemm_at_b_kn<T, D, D / 8, KS>(acc, sdY_a, m0, sW_a, lane);  // do_l = dY W
+    float dd0 = 0.f, dd1 = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+      float2 o0 = Elem<T>::unpack2(ol[kk][0]), o1 = Elem<T>::unpack2(ol[kk][1]);
+      float2 o2 = Elem<T>::unpack2(ol[kk][2]), o3 = Elem<T>::unpack2(ol[kk][3]);
+      dd0 += acc[2 * kk][0] * o0.x + acc[2 * kk][1] * o0.y + acc[2 * kk + 1][0] * o2.x + acc[2 * kk + 1][1] * o2.y;
+      dd1 += acc[2 * kk][2] * o1.x + acc[2 * kk][3] * o1.y + acc[2 * kk + 1][2] * o3.x + acc[2 * kk + 1][3] * o3.y;
+    }
+    const float dden0 = -quad_sum(dd0) * rd0, dden1 = -quad_sum(dd1) * rd1;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      acc[j][0] *= rd0; acc[j][1] *= rd0; acc[j][2] *= rd1; acc[j][3] *= rd1;  // dnum
+    }
+    uint32_t dn[KS][4];
+    acc_to_a_frags<T, KS>(dn, acc);
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      int col = 8 * j + 2 * t;
+      acc[j][0] = dden0 * s_z[col]; acc[j][1] = dden0 * s_z[col + 1];
+      acc[j][2] = dden1 * s_z[col]; acc[j][3] = dden1 * s_z[col + 1];
+    }
+    gemm_b_nk<T, D, D / 8, KS>(acc, dn, sH_a, 0, 0, lane);  // dphi_q = dnum H^T + dden z
+    feature_map_bwd_frags<T, KS, FEAT>(acc, pq);
+    // dq_lin: stage in this warp's rows of the Q tile (its fragments are no longer needed) and flush
+    store_acc_to_tile<T, D, D / 8>(sQ, acc, m0, lane);
+    flush16<T, D>(sQ, m0, dqg, row0 + m0, L, lane, false);
+    // phi(q)/den for the G reduction, and the row constants for dz
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        float2 ph = Elem<T>::unpack2(pq[kk][r]);
+        float rd = (r & 1) ? rd1 : rd0;
+        pq[kk][r] = Elem<T>::pack2(ph.x * rd, ph.y * rd);
+      }
+    }
+    store_a_frags_to_tile<D, KS>(sQ, pq, m0, 0, lane);
+    if (t == 0) {
+      s_rowc[m0 + g] = dden0 * d0;
+      s_rowc[m0 + g + 8] = dden1 * d1;
+    }
+    __syncthreads();
+    // G[n][i] += sum_m dY[m][n] * (phi_q/den)[m][i]
+    gemm_atrans_b_kn<T, D, D / 8, KS>(gacc, sdY_a, m0, sQ_a, lane);
+    if (tid < D) {
+      float s = 0.f;
+      int chunk = tid >> 3, e = tid & 7;
+      for (int m = 0; m < D; ++m) {
+        const T* a = reinterpret_cast<const T*>(sQ + tile_off<D>(m, chunk)) + e;
+        s += s_rowc[m] * Elem<T>::to_f(*a);
+      }
+      vec_acc += s;
+    } else {
+      int n = tid - D;
+      float s = 0.f;
+      int chunk = n >> 3, e = n & 7;
+      for (int m = 0; m < D; ++m) {
+        const T* a = reinterpret_cast<const T*>(sdY + tile_off<D>(m, chunk)) + e;
+        s += Elem<T>::to_f(*a);
+      }
+      vec_acc += s;
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  float* out = p.g_partial + (static_cast<size_t>(bh) * p.nch + ch) * (D * D + 2 * D);
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) {
+    int r0 = m0 + g, c = 8 * j + 2 * t;
+    *reinterpret_cast<float2*>(out + r0 * D + c) = make_float2(gacc[j][0], gacc[j][1]);
+    *reinterpret_cast<float2*>(out + (r0 + 8) * D + c) = make_float2(gacc[j][2], gacc[j][3]);
+  }
+  out[D * D + tid] = vec_acc;  // [0,D): dz, [D,2D): db
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-head reduction: G -> dH (T), dz, and the head's dW, db.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(1024) linear_bwd_reduce_kernel(LinBwdParams p, int D) {
+  extern __shared__ __align__(16) float sG[];  // [D][D]
+  const int bh = blockIdx.x, tid = threadIdx.x;
+  const int dd = D * D, n = dd + 2 * D;
+  const float* part = p.g_partial + static_cast<size_t>(bh) * p.nch * n;
+  for (int i = tid; i < dd; i += 1024) {
+    float s = 0.f;
+    for (int c = 0; c < p.nch; ++c) s += part[static_cast<size_t>(c) * n + i];
+    sG[i] = s;
+  }
+  float* dwp = p.dw_part + static_cast<size_t>(bh) * (dd + D);
+  for (int i = tid; i < 2 * D; i += 1024) {
+    float s = 0.f;
+    for (int c = 0; c < p.nch; ++c) s += part[static_cast<size_t>(c) * n + dd + i];
+    if (i < D) p.dz[static_cast<size_t>(bh) * D + i] = s;
+    else dwp[dd + i - D] = s;
+  }
+  __syncthreads();
+  const T* hs = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (dd + D);
+  T* dh = static_cast<T*>(p.dh) + static_cast<size_t>(bh) * dd;
+  for (int o = tid; o < dd; o += 1024) {
+    int a = o / D, b = o % D;
+    // dH[i=a][j=b] = sum_n G[n][a] W[n][b]
+    float s = 0.f;
+    for (int nn = 0; nn < D; ++nn) s = fmaf(sG[nn * D + a], p.w[nn * D + b], s);
+    dh[o] = Elem<T>::from_f(s);
+    // dW_head[n=a][k=b] = sum_i G[a][i] H[i][b]
+    float u = 0.f;
+    for (int i = 0; i < D; ++i) u = fmaf(sG[a * D + i], Elem<T>::to_f(hs[i * D + b]), u);
+    dwp[o] = u;
+  }
+}
+
+__global__ void dw_final_kernel(const float* __restrict__ dw_part, float* __restrict__ dw,
+                                float* __restrict__ dbias, int bh, int dd, int d) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= dd + d) return;
+  float s = 0.f;
+  for (int h = 0; h < bh; ++h) s += dw_part[static_cast<size_t>(h) * (dd + d) + i];
+  if (i < dd) dw[i] = s; else dbias[i - dd] = s;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Pass B: dk_lin, dv_lin for 64 key rows per CTA.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int D, int FEAT>
+__global__ void __launch_bounds__(128) linear_bwd_kv_kernel(LinBwdParams p) {
+  constexpr int NT = 128, KS = D / 16;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* sdH = smem;                  // [D][D]
+  unsigned char* sK = sdH + D * D * 2;        // [64][D]
+  unsigned char* sV = sK + 64 * D * 2;        // [64][D]
+  float* s_dz = reinterpret_cast<float*>(sV + 64 * D * 2);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t = lane & 3;
+  const int bh = blockIdx.y, row0 = blockIdx.x * 64;
+  const int L = p.L;
+  const size_t head_off = static_cast<size_t>(bh) * L * D;
+  const T* kg = static_cast<const T*>(p.k) + head_off;
+  const T* vg = static_cast<const T*>(p.v) + head_off;
+  const T* dh = static_cast<const T*>(p.dh) + static_cast<size_t>(bh) * D * D;
+  const uint32_t sdH_a = smem_u32(sdH), sK_a = smem_u32(sK), sV_a = smem_u32(sV);
+  const int m0 = warp * 16;
+  load_tile_async<D, D>(sdH_a, dh, 0, D, tid, NT);
+  load_tile_async<D, 64>(sK_a, kg, row0, L, tid, NT);
+  load_tile_async<D, 64>(sV_a, vg, row0, L, tid, NT);
+  cp_async_commit();
+  for (int i = tid; i < D; i += NT) s_dz[i] = p.dz[static_cast<size_t>(bh) * D + i];
+  cp_async_wait<0>();
+  __syncthreads();
+
+  uint32_t pk[KS][4];
+  {
+    uint32_t kf[KS][4];
+    load_a_frags<D, KS>(kf, sK_a, m0, 0, lane);
+    feature_map_frags<T, KS, FEAT>(pk, kf);
+  }
+  float acc[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) {
+    int col = 8 * j + 2 * t;
+    acc[j][0] = s_dz[col]; acc[j][1] = s_dz[col + 1];
+    acc[j][2] = s_dz[col]; acc[j][3] = s_dz[col + 1];
+  }
+  gemm_at_b_nk<T, D, D / 8, KS>(acc, sV_a, m0, sdH_a, lane);  // dphi_k = v dH^T + dz
+  feature_map_bwd_frags<T, KS, FEAT>(acc, pk);
+  store_acc_to_tile<T, D, D / 8>(sK, acc, m0, lane);
+  flush16<T, D>(sK, m0, static_cast<T*>(p.dk) + head_off, row0 + m0, L, lane, false);
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  gemm_b_kn<T, D, D / 8, KS>(acc, pk, sdH_a, 0, 0, lane);  // dv_lin = phi(k) dH
+  store_acc_to_tile<T, D, D / 8>(sV, acc, m0, lane);
+  flush16<T, D>(sV, m0, static_cast<T*>(p.dv) + head_off, row0 + m0, L, lane, false);
+}
+
+template <typename T, int D, int FEAT>
+static int launch_lin_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_t st) {
+  const int bh = s->B * s->H, dd = D * D;
+  {
+    auto kern = linear_bwd_q_kernel<T, D, FEAT>;
+    int smem = 4 * dd * 2 + 2 * D * 4;
+    SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<dim3(p.nch, bh), D / 16 * 32, smem, st>>>(p);
+    SLA_LAUNCH_OK();
+  }
+  {
+    auto kern = linear_bwd_reduce_kernel<T>;
+    int smem = dd * 4;
+    SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<bh, 1024, smem, st>>>(p, D);
+    SLA_LAUNCH_OK();
+    dw_final_kernel<<<ceil_div(dd + D, 256), 256, 0, st>>>(p.dw_part, p.dw, p.dbias, bh, dd, D);
+    SLA_LAUNCH_OK();
+  }
+  {
+    auto kern = linear_bwd_kv_kernel<T, D, FEAT>;
+    int smem = dd * 2 + 2 * 64 * D * 2 + D * 4;
+    SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<dim3(ceil_div(s->L, 64), bh), 128, smem, st>>>(p);
+    SLA_LAUNCH_OK();
+  }
+  return SLA_OK;
+}
+
+template <typename T, int D>
+static int dispatch_lin_feat(const sla_shape* s, const LinBwdParams& p, cudaStream_t st) {
+  switch (s->feature_map) {
+    case SLA_PHI_SOFTMAX: return launch_lin_bwd<T, D, SLA_PHI_SOFTMAX>(s, p, st);
+    case SLA_PHI_RELU: return launch_lin_bwd<T, D, SLA_PHI_RELU>(s, p, st);
+    default: return launch_lin_bwd<T, D, SLA_PHI_ELU>(s, p, st);
+  }
+}
+
+int run_linear_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_t st) {
+  if (s->dtype == SLA_BF16) {
+    if (s->D == 64) return dispatch_lin_feat<__nv_bfloat16, 64>(s, p, st);
+    return dispatch_lin_feat<__nv_bfloat16, 128>(s, p, st);
+  }
+  if (s->D == 64) return dispatch_lin_feat<__half, 64>(s, p, st);
+  return dispatch_lin_feat<__half, 128>(s, p, st);
+}
+
+}  // namespace sla

@@ -1,0 +1,207 @@
+"""Operator level of sla_b200: the reference's L1 names on top of the C-ABI library.
+
+* ``get_block_map(q, k, topk_ratio, BLKQ, BLKK) -> (sparse_map, lut, topk)`` mirrors
+  sparse_linear_attention/utils.py:55-67 (int8 map, int64 LUT, python int).
+* ``_attention.apply(q, k, v, sparse_map, lut, topk, BLOCK_M, BLOCK_N, qk_scale=None)`` mirrors the
+  autograd.Function of sparse_linear_attention/kernel.py:240-320.
+* ``block_map`` / ``sla_attention`` are the fused forms the modules use (int32 LUT, column lists for
+  the backward, linear branch + proj_l inside the kernels).
+
+PyTorch is used for device memory, streams and autograd bookkeeping only; all arithmetic happens in
+libsla_b200.so. Nothing here falls back to PyTorch math.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import SlaShape, check, lib
+
+_DT = {torch.bfloat16: _lib.SLA_BF16, torch.float16: _lib.SLA_FP16, torch.float32: _lib.SLA_FP32}
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require_cuda(*ts: torch.Tensor):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("sla_b200 operators need CUDA tensors (there is no CPU path)")
+
+
+def make_shape(B, H, L, D, BLKQ, BLKK, topk, dtype=torch.bfloat16, feature="softmax", flags=0,
+               qk_scale: Optional[float] = None) -> SlaShape:
+    if feature not in _lib.PHI:
+        raise NotImplementedError(f"Not supported feature map {feature}.")
+    return SlaShape(B, H, L, D, BLKQ, BLKK, topk, _DT[dtype], _lib.PHI[feature], flags,
+                    0.0 if qk_scale is None else float(qk_scale))
+
+
+def _workspace(shape: SlaShape, op: int, device) -> torch.Tensor:
+    n = int(lib.sla_workspace_bytes(C.byref(shape), op))
+    return torch.empty(max(n, 256), dtype=torch.uint8, device=device)
+
+
+@dataclass
+class BlockMap:
+    """Result of block-mask prediction in the library's own format."""
+    lut: torch.Tensor                     # (B,H,M_BLOCKS,topk) int32, ascending per row
+    topk: int
+    n_blocks: int
+    sparse_map: Optional[torch.Tensor]    # (B,H,M_BLOCKS,N_BLOCKS) int8
+    col_offsets: Optional[torch.Tensor]   # (B,H,N_BLOCKS+1) int32
+    col_index: Optional[torch.Tensor]     # (B,H,M_BLOCKS*topk) int32
+
+
+def block_map(q: torch.Tensor, k: torch.Tensor, topk_ratio: float, BLKQ: int = 64, BLKK: int = 64,
+              want_map: bool = False, want_cols: bool = False) -> BlockMap:
+    _require_cuda(q, k)
+    assert q.is_contiguous() and k.is_contiguous()
+    if q.dtype not in _DT or k.dtype != q.dtype:
+        raise TypeError(f"unsupported dtype {q.dtype}")
+    B, H, L, D = q.shape
+    mb, nb = (L + BLKQ - 1) // BLKQ, (L + BLKK - 1) // BLKK
+    topk = _lib.topk_count(nb, topk_ratio)
+    shape = SlaShape(B, H, L, D, BLKQ, BLKK, topk, _lib.SLA_BF16, 0, 0, 0.0)
+    dev = q.device
+    lut = torch.empty((B, H, mb, max(topk, 0)), dtype=torch.int32, device=dev)
+    smap = torch.empty((B, H, mb, nb), dtype=torch.int8, device=dev) if (want_map or want_cols) else None
+    co = torch.empty((B, H, nb + 1), dtype=torch.int32, device=dev) if want_cols else None
+    ci = torch.empty((B, H, mb * max(topk, 0)), dtype=torch.int32, device=dev) if want_cols else None
+    ws = _workspace(shape, _lib.OP_BLOCK_MAP, dev)
+    check(lib.sla_block_map(C.byref(shape), _DT[q.dtype], _p(q), _p(k), _p(lut), _p(smap), _p(co), _p(ci),
+                            _p(ws), ws.numel(), _stream(q)))
+    return BlockMap(lut, topk, nb, smap, co, ci)
+
+
+def column_lists(sparse_map: torch.Tensor, L: int, BLKQ: int, BLKK: int, topk: int):
+    """Per-KV-block query-block lists from a 0/1 block map (for maps made elsewhere)."""
+    _require_cuda(sparse_map)
+    B, H, mb, nb = sparse_map.shape
+    shape = SlaShape(B, H, L, 64, BLKQ, BLKK, topk, _lib.SLA_BF16, 0, 0, 0.0)
+    co = torch.empty((B, H, nb + 1), dtype=torch.int32, device=sparse_map.device)
+    ci = torch.empty((B, H, mb * topk), dtype=torch.int32, device=sparse_map.device)
+    check(lib.sla_column_lists(C.byref(shape), _p(sparse_map.contiguous()), _p(co), _p(ci), _stream(sparse_map)))
+    return co, ci
+
+
+def get_block_map(q, k, topk_ratio, BLKQ=64, BLKK=64):
+    """Drop-in for sparse_linear_attention.utils.get_block_map (utils.py:55-67): returns
+    (sparse_map int8, lut int64, topk). The LUT rows are sorted ascending (the reference's order is
+    unspecified). The tensors remember the library-format twin (int32 LUT, column lists) so that a
+    following ``_attention.apply`` does not rebuild them."""
+    bm = block_map(q, k, topk_ratio, BLKQ, BLKK, want_map=True, want_cols=True)
+    lut64 = bm.lut.to(torch.int64)
+    lut64._sla_block_map = bm
+    bm.sparse_map._sla_block_map = bm
+    return bm.sparse_map, lut64, bm.topk
+
+
+class _attention(torch.autograd.Function):
+    """Drop-in for sparse_linear_attention.kernel._attention (kernel.py:240-320)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, k_block_id, lut, topk, BLOCK_M, BLOCK_N, qk_scale=None):
+        assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+        assert k_block_id.is_contiguous() and lut.is_contiguous()
+        assert BLOCK_M == 64 or BLOCK_M == 128
+        assert BLOCK_N == 64
+        _require_cuda(q, k, v, lut)
+        B, H, L, D = q.shape
+        bm = getattr(lut, "_sla_block_map", None)
+        lut32 = bm.lut if bm is not None else lut.to(torch.int32)
+        shape = make_shape(B, H, L, D, BLOCK_M, BLOCK_N, topk, q.dtype, flags=_lib.FLAG_SPARSE_ONLY,
+                           qk_scale=qk_scale)
+        o_s = torch.empty_like(v)
+        lse = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32)
+        check(lib.sla_sparse_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(lut32), _p(o_s), _p(lse), _stream(q)))
+        ctx.save_for_backward(q, k, v, k_block_id, lut32, lse, o_s)
+        ctx.sla_shape = shape
+        ctx.sla_bm = bm
+        return o_s
+
+    @staticmethod
+    def backward(ctx, do_s):
+        q, k, v, k_block_id, lut32, lse, o_s = ctx.saved_tensors
+        do_s = do_s.contiguous()
+        shape = ctx.sla_shape
+        bm = ctx.sla_bm
+        if bm is not None and bm.col_offsets is not None:
+            co, ci = bm.col_offsets, bm.col_index
+        else:
+            co, ci = column_lists(k_block_id, shape.L, shape.BLKQ, shape.BLKK, shape.topk)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty_like(lse)
+        check(lib.sla_sparse_bwd(C.byref(shape), _p(q), _p(k), _p(v), _p(o_s), _p(lse), _p(do_s), _p(lut32),
+                                 _p(co), _p(ci), _p(dq), _p(dk), _p(dv), _p(delta), 0, _stream(q)))
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+class _SLAFused(torch.autograd.Function):
+    """core.py:88-100 (sparse branch + feature maps + linear branch + proj_l + sum) as one operator."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, weight, bias, bm: BlockMap, BLKQ, BLKK, feature, need_grad, impl_flags):
+        B, H, L, D = q.shape
+        shape = make_shape(B, H, L, D, BLKQ, BLKK, bm.topk, q.dtype, feature, flags=impl_flags)
+        dev = q.device
+        o = torch.empty_like(q)
+        o_s = torch.empty_like(q) if need_grad else None
+        lse = torch.empty((B, H, L), dtype=torch.float32, device=dev)
+        lin_state = torch.empty((B, H, D * D + D), dtype=q.dtype, device=dev)
+        ws = _workspace(shape, _lib.OP_FWD, dev)
+        check(lib.sla_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o), _p(o_s),
+                          _p(lse), _p(lin_state), _p(ws), ws.numel(), _stream(q)))
+        if need_grad:
+            ctx.save_for_backward(q, k, v, o_s, lse, lin_state, weight, bm.lut, bm.col_offsets, bm.col_index)
+            ctx.sla_shape = shape
+            ctx.has_bias = bias is not None
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o_s, lse, lin_state, weight, lut, co, ci = ctx.saved_tensors
+        shape = ctx.sla_shape
+        d_o = d_o.contiguous()
+        D = shape.D
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dw = torch.empty((D, D), dtype=torch.float32, device=q.device)
+        db = torch.empty((D,), dtype=torch.float32, device=q.device)
+        ws = _workspace(shape, _lib.OP_BWD, q.device)
+        check(lib.sla_bwd(C.byref(shape), _p(q), _p(k), _p(v), _p(o_s), _p(lse), _p(d_o), _p(lut), _p(co), _p(ci),
+                          _p(weight), _p(lin_state), _p(dq), _p(dk), _p(dv), _p(dw), _p(db), _p(ws), ws.numel(),
+                          _stream(q)))
+        return dq, dk, dv, dw, (db if ctx.has_bias else None), None, None, None, None, None, None
+
+
+def sla_attention(q, k, v, weight, bias, bm: BlockMap, BLKQ=64, BLKK=64, feature="softmax",
+                  impl_flags: int = 0):
+    """o = o_s + proj_l(o_l) for q, k, v already in the 16-bit compute dtype."""
+    _require_cuda(q, k, v, weight)
+    need_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (q, k, v, weight, bias))
+    if need_grad and bm.col_offsets is None:
+        raise RuntimeError("the block map was built without column lists (want_cols=True) but a backward is needed")
+    return _SLAFused.apply(q, k, v, weight, bias, bm, BLKQ, BLKK, feature, need_grad, impl_flags)
+
+
+def sage_sla_attention(q, k, v, weight, bias, bm: BlockMap, feature="softmax"):
+    """SageSLA/core.py:100-158: quantized sparse branch + linear branch + proj_l. Forward only."""
+    _require_cuda(q, k, v, weight)
+    B, H, L, D = q.shape
+    shape = make_shape(B, H, L, D, 128, 64, bm.topk, q.dtype, feature)
+    o = torch.empty_like(q)
+    lin_state = torch.empty((B, H, D * D + D), dtype=q.dtype, device=q.device)
+    ws = _workspace(shape, _lib.OP_SAGE_FWD, q.device)
+    check(lib.sage_sla_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o),
+                           _p(lin_state), _p(ws), ws.numel(), _stream(q)))
+    return o

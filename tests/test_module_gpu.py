@@ -1,0 +1,125 @@
+"""GPU parity of the whole module (SparseLinearAttention forward + backward through the C ABI)
+against the reference's golden vectors and the CPU oracle; tolerance cosine >= 0.999, relL1 <= 1e-2."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import DT, assert_close_parity, load_golden, unpack
+
+pytestmark = pytest.mark.gpu
+
+MODULE = ["module_bf16_softmax", "module_fp16_relu", "module_fp32in_elu_blkq128"]
+
+
+def _module(D, ratio, feat, BLKQ, BLKK, use_bf16, w, b):
+    import sla_b200
+    m = sla_b200.SparseLinearAttention(D, ratio, feat, BLKQ, BLKK, use_bf16=use_bf16).cuda()
+    with torch.no_grad():
+        m.proj_l.weight.copy_(w)
+        m.proj_l.bias.copy_(b)
+    return m
+
+
+@pytest.mark.parametrize("name", MODULE)
+def test_module_vs_reference_golden(name):
+    g = load_golden(name)
+    B, H, L, D, BLKQ, BLKK, _, _ = g["meta"].tolist()
+    in_dt = DT[str(g["in_dtype"])]
+    use_bf16 = str(g["compute"]) == "bf16"
+    m = _module(D, float(g["ratio"]), str(g["feature"]), BLKQ, BLKK, use_bf16,
+                torch.from_numpy(g["w"]), torch.from_numpy(g["bias"]))
+    q, k, v = (unpack(g[n], in_dt).cuda().requires_grad_(True) for n in ("q", "k", "v"))
+    o, sparsity = m(q, k, v, return_sparsity=True)
+    assert o.dtype == in_dt and sparsity == float(g["sparsity"])
+    assert_close_parity(o.detach().float().cpu(), unpack(g["o"], in_dt).float(), what=name + ".o")
+    o.backward(unpack(g["do"], in_dt).cuda())
+    for t, n in ((q, "dq"), (k, "dk"), (v, "dv")):
+        assert t.grad.dtype == in_dt
+        assert_close_parity(t.grad.float().cpu(), unpack(g[n], in_dt).float(), what=f"{name}.{n}")
+    assert_close_parity(m.proj_l.weight.grad.cpu(), torch.from_numpy(g["dw"]), l1_max=2e-2, what=name + ".dw")
+    assert_close_parity(m.proj_l.bias.grad.cpu(), torch.from_numpy(g["db"]), l1_max=2e-2, what=name + ".db")
+
+
+def test_module_c1_configuration():
+    """B=1,H=2,L=1024,D=64 fp32 inputs from seed 0, BLKQ=BLKK=64, topk=0.25, softmax, W~N(0,0.02)."""
+    g = load_golden("module_c1")
+    torch.manual_seed(0)
+    q, k, v = torch.randn(1, 2, 1024, 64), torch.randn(1, 2, 1024, 64), torch.randn(1, 2, 1024, 64)
+    w = torch.randn(64, 64) * 0.02
+    m = _module(64, 0.25, "softmax", 64, 64, True, w, torch.zeros(64))
+    with torch.no_grad():
+        o = m(q.cuda(), k.cuda(), v.cuda())
+    assert o.dtype == torch.float32
+    assert_close_parity(o.cpu(), torch.from_numpy(g["o"]), what="c1.o")
+
+
+def test_zero_init_means_sparse_only():
+    """proj_l is zero-initialised (core.py:64-67): a fresh module returns exactly the sparse branch."""
+    import sla_b200
+    from sla_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    q, k, v = (torch.randn(1, 2, 1000, 128, generator=g).bfloat16().cuda() for _ in range(3))
+    m = sla_b200.SparseLinearAttention(128, 0.2).cuda()
+    with torch.no_grad():
+        o = m(q, k, v)
+    smap, lut, topk = ops.get_block_map(q, k, 0.2, 64, 64)
+    o_s = ops._attention.apply(q, k, v, smap, lut, topk, 64, 64)
+    assert torch.equal(o, o_s)
+
+
+@pytest.mark.parametrize("feat,D,BLKQ,L", [("softmax", 128, 64, 1536), ("relu", 64, 128, 1100), ("elu", 128, 128, 900)])
+def test_module_vs_oracle_autograd(feat, D, BLKQ, L):
+    from oracle import sla_oracle as O
+    g = torch.Generator().manual_seed(L)
+    B, H = 1, 2
+    q, k, v, do = (torch.randn(B, H, L, D, generator=g).bfloat16() for _ in range(4))
+    w = torch.randn(D, D, generator=g) * 0.05
+    b = torch.randn(D, generator=g) * 0.05
+    m = _module(D, 0.3, feat, BLKQ, 64, True, w, b)
+    qg, kg, vg = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o = m(qg, kg, vg)
+    o.backward(do.cuda())
+    o_ref, parts = O.sla_forward(q, k, v, w, b, 0.3, feat, BLKQ, 64, torch.bfloat16, return_parts=True)
+    assert_close_parity(o.detach().float().cpu(), o_ref.float(), what="o")
+    qd, kd, vd = (t.double().requires_grad_(True) for t in (q, k, v))
+    wd, bd = w.double().requires_grad_(True), b.double().requires_grad_(True)
+    O.sla_forward_fp(qd, kd, vd, wd, bd, parts["sparse_map"], feat, BLKQ, 64).backward(do.double())
+    assert_close_parity(qg.grad.float().cpu(), qd.grad, what="dq")
+    assert_close_parity(kg.grad.float().cpu(), kd.grad, what="dk")
+    assert_close_parity(vg.grad.float().cpu(), vd.grad, what="dv")
+    assert_close_parity(m.proj_l.weight.grad.cpu(), wd.grad, l1_max=2e-2, what="dw")
+    assert_close_parity(m.proj_l.bias.grad.cpu(), bd.grad, l1_max=2e-2, what="db")
+
+
+def test_determinism_and_readme_shape():
+    """README usage shape (B=2,H=4,L=4096,D=128, topk=0.2): runs, is bitwise repeatable, finite."""
+    import sla_b200
+    from sla_b200 import synthetic
+    w = synthetic.WORKLOADS["c2"]
+    q, k, v, do = synthetic.make_inputs(w, "cuda")
+    W, b = synthetic.make_proj(w, "cuda")
+    m = _module(128, 0.2, "softmax", 64, 64, True, W, b)
+    outs = []
+    for _ in range(2):
+        qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+        o = m(qg, kg, vg)
+        o.backward(do)
+        outs.append((o.detach(), qg.grad, kg.grad, vg.grad))
+        m.proj_l.weight.grad = None
+    for a, bb in zip(*outs):
+        assert torch.isfinite(a.float()).all() and torch.equal(a, bb)
+
+
+def test_full_size_linearity_in_v_c3_head():
+    """Full-size property on one L=32760 head: the operator is linear in V for a fixed block map, and
+    with V = const every output row equals that constant (softmax rows sum to one)."""
+    from sla_b200 import ops, synthetic
+    w = synthetic.WORKLOADS["c3"]
+    q, k, v, _ = synthetic.make_inputs(w, "cuda", units=[3], with_do=False)
+    smap, lut, topk = ops.get_block_map(q, k, w.topk, 64, 64)
+    ones = torch.full_like(v, 0.5)
+    o1 = ops._attention.apply(q, k, ones, smap, lut, topk, 64, 64)
+    assert float((o1.float() - 0.5).abs().max()) < 4e-3
+    a = ops._attention.apply(q, k, v, smap, lut, topk, 64, 64).float()
+    b = ops._attention.apply(q, k, (2 * v), smap, lut, topk, 64, 64).float()
+    assert_close_parity(b.cpu(), (2 * a).cpu(), cos_min=0.99999, l1_max=1e-3, what="linearity")
