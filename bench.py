@@ -1,0 +1,419 @@
+#!/usr/bin/env python
+"""Benchmark of the SLA attention hot path (forward + backward of SparseLinearAttention).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3] [--impl ours|reference]
+
+A step is one pass of the whole hot path over one batch of synthetic input: block-mask prediction,
+fused sparse + linear forward, and the full backward, through the module API. One JSON line is
+printed by rank 0. `value` is the dense-attention-equivalent TFLOP/s of the reference's own benchmark
+formula (evaluate/bench_kernel.py:93-99: 4*B*H*L^2*D per forward, x3.5 for forward+backward), summed
+over all ranks; ms per step, the sparse-actual TFLOP/s and the forward-only figures are extra keys.
+
+N > 1: launched under torchrun, one rank per GPU. Rank r owns batch element r of a global batch of N
+(each batch element = the workload's H heads): (batch x head) sharding with no collective on the
+attention path, so per-GPU work is fixed ("scaling": "weak").
+
+--impl reference times the CPU restatement of the reference's algorithm (oracle/) on the host cores,
+rank 0 only, each step a bounded sample (one head) of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch
+
+
+def _peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p["bf16_tflops_sustained"], "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, smax, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def timed(fn, steps, warmup, sync):
+    """W untimed warm-ups, then exactly `steps` calls between two events on the current stream."""
+    for _ in range(warmup):
+        fn()
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    sync()
+    return e0.elapsed_time(e1) / steps  # ms per call
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the oracle restatement of the reference on host cores, on a bounded sample (one head)
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_step(w, sample, backward=True):
+    from oracle import sla_oracle as O
+    q, k, v, do, W, b = sample
+    t0 = time.perf_counter()
+    _, lut, _ = O.get_block_map(q, k, w.topk, w.BLKQ, w.BLKK)   # on the given dtype (core.py:83)
+    qf, kf, vf = (t.float().requires_grad_(backward) for t in (q, k, v))
+    Wp, bp = W.clone().requires_grad_(backward), b.clone().requires_grad_(backward)
+    o = O.sla_forward_gather_fp(qf, kf, vf, Wp, bp, lut, w.feature, w.BLKQ, w.BLKK)
+    if backward:
+        o.backward(do.float())
+    return time.perf_counter() - t0
+
+
+def cpu_sample(w):
+    from sla_b200 import synthetic
+    q, k, v, do = synthetic.make_inputs(w, "cpu", units=[0])
+    W, b = synthetic.make_proj(w, "cpu")
+    return q, k, v, do, W, b
+
+
+def run_reference_arm(args, w, rank):
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    sample = cpu_sample(w)
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_step(w, sample)
+    ts = [cpu_reference_step(w, sample) for _ in range(args.steps)]
+    sec = sum(ts) / len(ts)
+    flops_unit = w.dense_equiv_flops(True) / w.units
+    val = flops_unit / sec / 1e12
+    line = {
+        "impl": "reference", "metric": "sla_fwd_bwd_dense_equiv_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "B": w.B, "H": w.H, "L": w.L, "D": w.D, "BLKQ": w.BLKQ, "BLKK": w.BLKK,
+                   "topk": w.topk, "feature_map": w.feature},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": f"1 of {w.units} (batch,head) units, forward+backward incl. block map, per step"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# optional GPU baselines measured beside our arm (N = 1): reference Triton SLA, FlashAttention
+# ------------------------------------------------------------------------------------------------
+def load_reference_package():
+    import importlib.util
+    root = os.path.join(ROOT, "baseline", "_ref", "sparse_linear_attention")
+    if not os.path.isdir(root):
+        return None
+    spec = importlib.util.spec_from_file_location("sla_reference", os.path.join(root, "__init__.py"),
+                                                  submodule_search_locations=[root])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["sla_reference"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def gpu_baselines(w, q, k, v, do, W, b, steps, warmup):
+    out = {}
+    sync = torch.cuda.synchronize
+    try:
+        ref = load_reference_package()
+        if ref is None:
+            out["reference_triton"] = {"unavailable": "baseline/_ref not present"}
+        else:
+            m = ref.SparseLinearAttention(w.D, w.topk, w.feature, w.BLKQ, w.BLKK).cuda()
+            with torch.no_grad():
+                m.proj_l.weight.copy_(W)
+                m.proj_l.bias.copy_(b)
+            qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+
+            def fwd():
+                with torch.no_grad():
+                    m(q, k, v)
+
+            def fwdbwd():
+                o = m(qg, kg, vg)
+                o.backward(do)
+                qg.grad = kg.grad = vg.grad = None
+
+            f = timed(fwd, steps, warmup, sync)
+            fb = timed(fwdbwd, steps, warmup, sync)
+            out["reference_triton"] = {"fwd_ms": f, "fwd_bwd_ms": fb,
+                                       "fwd_bwd_dense_equiv_tflops": w.dense_equiv_flops(True) / fb / 1e9}
+    except Exception as e:  # noqa: BLE001
+        out["reference_triton"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    try:
+        from flash_attn.flash_attn_interface import flash_attn_func
+        qf, kf, vf, dof = (t.transpose(1, 2).contiguous() for t in (q, k, v, do))
+        qf, kf, vf = (t.requires_grad_(True) for t in (qf, kf, vf))
+
+        def ffwd():
+            with torch.no_grad():
+                flash_attn_func(qf, kf, vf)
+
+        def ffb():
+            o = flash_attn_func(qf, kf, vf)
+            o.backward(dof)
+            qf.grad = kf.grad = vf.grad = None
+
+        f = timed(ffwd, max(2, steps // 2), 2, sync)
+        fb = timed(ffb, max(2, steps // 2), 2, sync)
+        out["flash_attn_dense"] = {"fwd_ms": f, "fwd_bwd_ms": fb,
+                                   "fwd_bwd_tflops": w.dense_equiv_flops(True) / fb / 1e9}
+    except Exception as e:  # noqa: BLE001
+        out["flash_attn_dense"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3")
+    ap.add_argument("--no-baselines", action="store_true", help="skip the on-GPU reference/flash-attn timings")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--legacy-mma", action="store_true", help="force the mma.sync kernels")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    from sla_b200 import synthetic
+    w = synthetic.WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference_arm(args, w, rank)
+        return
+
+    import torch.distributed as dist
+    import sla_b200
+    from sla_b200 import _lib, ops
+
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path for the product)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # rank r owns batch element r: units [r*units, (r+1)*units) of the global (batch x head) index
+    unit_ids = [rank * w.units + u for u in range(w.units)]
+    q, k, v, do = synthetic.make_inputs(w, dev, units=unit_ids)
+    q, k, v, do = (t.view(w.B, w.H, w.L, w.D) for t in (q, k, v, do))
+    W, b = synthetic.make_proj(w, dev)
+    m = sla_b200.SparseLinearAttention(w.D, w.topk, w.feature, w.BLKQ, w.BLKK).to(dev)
+    with torch.no_grad():
+        m.proj_l.weight.copy_(W)
+        m.proj_l.bias.copy_(b)
+    if args.legacy_mma:
+        m.impl_flags |= _lib.FLAG_LEGACY_MMA
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+
+    def step_fwd():
+        with torch.no_grad():
+            return m(q, k, v)
+
+    def step_fwdbwd():
+        o = m(qg, kg, vg)
+        o.backward(do)
+        qg.grad = kg.grad = vg.grad = None
+        m.proj_l.weight.grad = m.proj_l.bias.grad = None
+
+    # ---- main timed region: exactly K forward+backward steps ----
+    sampler = ClockSampler(local_rank)
+    for _ in range(args.warmup):
+        step_fwdbwd()
+    sync()
+    l0 = _lib.lib.sla_launch_count()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_fwdbwd()
+    e1.record()
+    sync()
+    clocks = sampler.stop()
+    launches = _lib.lib.sla_launch_count() - l0
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    fwd_ms = timed(step_fwd, args.steps, 2, sync)
+    if world > 1:
+        t = torch.tensor([fwd_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        fwd_ms = float(t.item())
+
+    # ---- end to end through the module API with HOST buffers ----
+    hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, do))
+    ho, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
+
+    def step_e2e():
+        dq_, dk_, dv_, ddo = (h.to(dev, non_blocking=True) for h in (hq, hk, hv, hdo))
+        dq_.requires_grad_(True); dk_.requires_grad_(True); dv_.requires_grad_(True)
+        o = m(dq_, dk_, dv_)
+        o.backward(ddo)
+        ho.copy_(o.detach(), non_blocking=True)
+        hdq.copy_(dq_.grad, non_blocking=True)
+        hdk.copy_(dk_.grad, non_blocking=True)
+        hdv.copy_(dv_.grad, non_blocking=True)
+        m.proj_l.weight.grad = m.proj_l.bias.grad = None
+
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = timed(step_e2e, e2e_steps, 2, sync)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    tensor_bytes = q.numel() * q.element_size()
+
+    # ---- the dominant kernels timed alone (CUDA events on the launching stream) ----
+    peaks = _peaks()
+    import ctypes as C
+    bm = ops.block_map(q, k, w.topk, w.BLKQ, w.BLKK, want_cols=True)
+    flags = _lib.FLAG_SPARSE_ONLY | (_lib.FLAG_LEGACY_MMA if args.legacy_mma else 0)
+    shape = ops.make_shape(w.B, w.H, w.L, w.D, w.BLKQ, w.BLKK, bm.topk, torch.bfloat16, w.feature, flags=flags)
+    o_s = torch.empty_like(q)
+    lse = torch.empty((w.B, w.H, w.L), dtype=torch.float32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def k_fwd():
+        _lib.check(_lib.lib.sla_sparse_fwd(C.byref(shape), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                           bm.lut.data_ptr(), o_s.data_ptr(), lse.data_ptr(), st))
+
+    dq_, dk_, dv_ = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    delta = torch.empty_like(lse)
+
+    def k_bwd():
+        _lib.check(_lib.lib.sla_sparse_bwd(C.byref(shape), q.data_ptr(), k.data_ptr(), v.data_ptr(), o_s.data_ptr(),
+                                           lse.data_ptr(), do.data_ptr(), bm.lut.data_ptr(),
+                                           bm.col_offsets.data_ptr(), bm.col_index.data_ptr(), dq_.data_ptr(),
+                                           dk_.data_ptr(), dv_.data_ptr(), delta.data_ptr(), 0, st))
+
+    def k_map():
+        ops.block_map(q, k, w.topk, w.BLKQ, w.BLKK, want_cols=True)
+
+    kf_ms = timed(k_fwd, args.steps, 3, torch.cuda.synchronize)
+    kb_ms = timed(k_bwd, args.steps, 3, torch.cuda.synchronize)
+    km_ms = timed(k_map, args.steps, 3, torch.cuda.synchronize)
+    fwd_flops = w.sparse_flops(False)
+    bwd_flops = w.sparse_flops(True) - fwd_flops
+    kernels = {
+        "sparse_fwd": {"ms": kf_ms, "tflops": fwd_flops / kf_ms / 1e9},
+        "sparse_bwd_dq_dkdv": {"ms": kb_ms, "tflops": bwd_flops / kb_ms / 1e9},
+        "block_map": {"ms": km_ms, "gbs": 2 * tensor_bytes / km_ms / 1e6},
+    }
+    dom = "sparse_bwd_dq_dkdv" if kb_ms >= kf_ms else "sparse_fwd"
+    achieved = kernels[dom]["tflops"]
+    roofline = {"kernel": dom, "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
+                "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                "peak_source": peaks["source"] + " burst (kernel timed alone)",
+                "algorithmic_flops_per_launch": bwd_flops if dom != "sparse_fwd" else fwd_flops}
+
+    dense_fb = w.dense_equiv_flops(True)
+    n_units_total = world * w.units
+    value = world * dense_fb / ms / 1e9
+    line = {
+        "metric": "sla_fwd_bwd_dense_equiv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w.name, "B_per_gpu": w.B, "H": w.H, "L": w.L, "D": w.D, "BLKQ": w.BLKQ,
+                   "BLKK": w.BLKK, "topk": w.topk, "topk_blocks": w.topk_blocks, "feature_map": w.feature,
+                   "global_units": n_units_total, "parallelism": f"bh-shard x{world}",
+                   "l2": "inputs larger than L2 (q,k,v,dO,o,dq,dk,dv = %.0f MB)" % (8 * tensor_bytes / 1e6),
+                   "impl": "mma.sync" if args.legacy_mma else "default"},
+        "fwd_ms": fwd_ms, "fwd_bwd_ms": ms,
+        "fwd_dense_equiv_tflops": world * w.dense_equiv_flops(False) / fwd_ms / 1e9,
+        "sparse_actual_tflops": world * (w.sparse_flops(True) + w.linear_flops(True)) / ms / 1e9,
+        "e2e": {"value": world * dense_fb / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": 4 * tensor_bytes, "d2h_bytes_per_step": 4 * tensor_bytes},
+        "gpu_launches": int(launches), "clocks": clocks, "kernels": kernels, "roofline": roofline,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample = cpu_sample(w)
+        cpu_reference_step(w, sample)
+        ts, t_end = [], time.perf_counter() + 15.0
+        while len(ts) < 2 or (time.perf_counter() < t_end and len(ts) < 8):
+            ts.append(cpu_reference_step(w, sample))
+        sec = sum(ts) / len(ts)
+        line["cpu_baseline"] = {"value": dense_fb / w.units / sec / 1e12, "unit": "TFLOP/s",
+                                "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"1 of {w.units} (batch,head) units x {len(ts)} repeats, "
+                                          f"forward+backward incl. block map ({sec:.2f} s each)"}
+    if rank == 0 and world == 1 and not args.no_baselines:
+        line["gpu_baselines"] = gpu_baselines(w, q, k, v, do, W, b, max(3, args.steps // 2), 3)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -376,3 +376,42 @@ def sage_sparse_fwd(q, k, v, lut, BLKQ=128, BLKK=64, qk_scale=None, p_scale: flo
                 p8 = (p * p_scale).to(torch.float8_e4m3fn).float()
                 o[b, h, r0:r1] = (p8 @ vs) / (l * p_scale) * sv[b, h][None, :]
     return o
+
+
+# ----------------------------------------------------------------------------------------------
+# Block-gather evaluation of the whole module, differentiable (the timed CPU baseline)
+# ----------------------------------------------------------------------------------------------
+def sla_forward_gather_fp(q, k, v, weight, bias, lut, feature="softmax", BLKQ=64, BLKK=64, qk_scale=None):
+    """core.py:88-100 for a fixed LUT in the dtype given (fp32), vectorised over the query blocks of
+    one head at a time: K/V blocks are gathered per LUT row (kernel.py:55-76), the softmax is taken
+    over the gathered keys, and the linear branch (core.py:90-96) and proj_l (core.py:98-99) follow.
+    Differentiable with torch.autograd; cost is proportional to the selected pairs, so it is usable
+    at full sequence length on the host cores."""
+    B, H, L, D = q.shape
+    if qk_scale is None:
+        qk_scale = D ** -0.5
+    mb = (L + BLKQ - 1) // BLKQ
+    nb = (L + BLKK - 1) // BLKK
+    topk = lut.shape[-1]
+    padq, padk = mb * BLKQ - L, nb * BLKK - L
+    key_pos = torch.arange(nb * BLKK).view(nb, BLKK)
+    outs = []
+    for b in range(B):
+        row = []
+        for h in range(H):
+            qh, kh, vh = q[b, h], k[b, h], v[b, h]
+            qb = F.pad(qh, (0, 0, 0, padq)).view(mb, BLKQ, D)
+            kb = F.pad(kh, (0, 0, 0, padk)).view(nb, BLKK, D)
+            vb = F.pad(vh, (0, 0, 0, padk)).view(nb, BLKK, D)
+            idx = lut[b, h].long()                                   # (mb, topk)
+            ks = kb[idx].reshape(mb, topk * BLKK, D)
+            vs = vb[idx].reshape(mb, topk * BLKK, D)
+            valid = (key_pos[idx].reshape(mb, 1, topk * BLKK) < L)
+            s = torch.bmm(qb, ks.transpose(1, 2)) * qk_scale
+            s = s.masked_fill(~valid, float("-inf"))
+            o_s = torch.bmm(torch.softmax(s, dim=-1), vs).reshape(mb * BLKQ, D)[:L]
+            cq, ck = feature_map(qh, feature), feature_map(kh, feature)
+            o_l = calc_linear(cq, ck, vh)
+            row.append(o_s + o_l @ weight.t() + bias)
+        outs.append(torch.stack(row))
+    return torch.stack(outs)
