@@ -75,6 +75,10 @@ SLA_API int sla_version(void);
 SLA_API const char* sla_status_string(int status);
 /* Text of the last CUDA runtime error seen by the calling thread inside this library. */
 SLA_API const char* sla_last_cuda_error(void);
+/* The tcgen05 kernels bound every device-side wait; when one runs out the kernel records a code in
+ * a device word and stops working. This call synchronises the device, returns the code (0 = none) in
+ * *code and optionally clears it. */
+SLA_API int sla_poll_device_error(int* code, int clear);
 /* Diagnostic: number of kernels this library has launched in the process so far. */
 SLA_API long long sla_launch_count(void);
 

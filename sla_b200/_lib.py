@@ -18,7 +18,7 @@ FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA = 1, 2
 
 # every symbol include/sla_b200.h declares
 EXPORTS = (
-    "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_topk_count", "sla_workspace_bytes",
+    "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_topk_count", "sla_workspace_bytes",
     "sla_block_map", "sla_column_lists", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_fwd", "sla_bwd",
     "sage_sla_fwd",
 )
@@ -51,6 +51,8 @@ def _load() -> C.CDLL:
     lib.sla_status_string.argtypes = [C.c_int]
     lib.sla_last_cuda_error.restype = C.c_char_p
     lib.sla_launch_count.restype = C.c_longlong
+    lib.sla_poll_device_error.restype = C.c_int
+    lib.sla_poll_device_error.argtypes = [C.POINTER(C.c_int), C.c_int]
     lib.sla_topk_count.restype = C.c_int
     lib.sla_topk_count.argtypes = [C.c_int, C.c_double]
     lib.sla_workspace_bytes.restype = C.c_size_t
@@ -87,6 +89,13 @@ def check(status: int) -> None:
     if status == -10:
         raise NotImplementedError(f"sla_b200 status {status}: {text}")
     raise SlaError(status, text)
+
+
+def poll_device_error(clear: bool = True) -> int:
+    """Synchronise and return the device error code of the tcgen05 kernels (0 = none)."""
+    code = C.c_int(0)
+    check(lib.sla_poll_device_error(C.byref(code), 1 if clear else 0))
+    return code.value
 
 
 def topk_count(n_blocks: int, ratio: float) -> int:

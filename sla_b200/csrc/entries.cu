@@ -42,7 +42,13 @@ int sla_sparse_fwd(const sla_shape* s, const void* q, const void* k, const void*
   if (rc != SLA_OK) return rc;
   if (!all_aligned({q, k, v, o_s})) return SLA_ERR_BAD_ALIGN;
   FwdParams p = make_fwd(s, q, k, v, lut, o_s, nullptr, lse, nullptr, nullptr);
-  return run_sparse_fwd_mma(s, p, false, static_cast<cudaStream_t>(stream));
+  if (s->flags & SLA_FLAG_LEGACY_MMA) return run_sparse_fwd_mma(s, p, false, static_cast<cudaStream_t>(stream));
+  return run_sparse_fwd_tc(s, p, static_cast<cudaStream_t>(stream));
+}
+
+int sla_poll_device_error(int* code, int clear) {
+  if (!code) return SLA_ERR_NULL;
+  return read_tc_error(code, clear != 0);
 }
 
 int sla_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, void* ws,
@@ -65,9 +71,10 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   if (rc != SLA_OK) return rc;
   if (!all_aligned({q, k, v, o, o_s, lin_state, ws})) return SLA_ERR_BAD_ALIGN;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool legacy = (s->flags & SLA_FLAG_LEGACY_MMA) != 0;
   if (s->flags & SLA_FLAG_SPARSE_ONLY) {
     FwdParams p = make_fwd(s, q, k, v, lut, o, nullptr, lse, nullptr, nullptr);
-    return run_sparse_fwd_mma(s, p, false, st);
+    return legacy ? run_sparse_fwd_mma(s, p, false, st) : run_sparse_fwd_tc(s, p, st);
   }
   if (!w || !lin_state || !ws) return SLA_ERR_NULL;
   WsLinearState wl = ws_linear_state(s);
@@ -79,7 +86,14 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wl.partial), wl.nch, wl.rows, st);
   if (rc != SLA_OK) return rc;
   FwdParams p = make_fwd(s, q, k, v, lut, o, o_s, lse, lin_state, wbits);
-  return run_sparse_fwd_mma(s, p, true, st);
+  if (legacy) return run_sparse_fwd_mma(s, p, true, st);
+  // tcgen05 sparse branch into o_s (or into o when the caller keeps no copy), then the streaming
+  // read-out adds the projected linear branch in place
+  FwdParams ps = make_fwd(s, q, k, v, lut, o_s ? o_s : o, nullptr, lse, nullptr, nullptr);
+  rc = run_sparse_fwd_tc(s, ps, st);
+  if (rc != SLA_OK) return rc;
+  p.o_s = o_s ? o_s : o;
+  return run_linear_readout(s, p, st);
 }
 
 int sla_sparse_bwd(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s,

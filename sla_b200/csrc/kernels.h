@@ -48,6 +48,9 @@ struct LinBwdParams {
 
 int convert_proj(const sla_shape* s, const float* w, const float* bias, void* out, cudaStream_t st);
 int run_sparse_fwd_mma(const sla_shape* s, const FwdParams& p, bool lin, cudaStream_t st);
+int run_sparse_fwd_tc(const sla_shape* s, const FwdParams& p, cudaStream_t st);
+int run_linear_readout(const sla_shape* s, const FwdParams& p, cudaStream_t st);
+int read_tc_error(int* out, bool clear);
 int run_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, float* partial,
                      int nch, int rows, cudaStream_t st);
 int run_sparse_bwd_mma(const sla_shape* s, const BwdParams& p, cudaStream_t st);

@@ -1,0 +1,436 @@
+// Block-sparse attention forward on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+// Same mathematics as sparse_linear_attention/kernel.py:21-82 (online softmax over the KV blocks a
+// LUT row selects, exp2 domain, LSE = m + log2 l).
+//
+// One CTA owns a 128-row query tile: one query block when BLKQ = 128, or two adjacent 64-row query
+// blocks when BLKQ = 64. In the second case the CTA walks the UNION of the two (ascending) LUT rows
+// and each entry carries two bits saying which half of the tile selected it; the other half gets
+// P = 0 for that entry. This keeps every MMA at M = 128 (full tensor-core rate) while the mask
+// granularity stays 64 x 64.
+//
+// Roles (192 threads):
+//   warps 0-3  softmax: thread r owns tile row r == TMEM lane r. Reads S from TMEM, keeps m, l,
+//              writes P (16-bit) back over S, rescales O in TMEM only when the running maximum grew
+//              by more than 2^8 since the last rescale, normalises and stores O at the end.
+//   warp 4     TMA producer: Q once, then K_j / V_j tiles into a 2-stage ring (128B-swizzled).
+//   warp 5     MMA issuer: S_j = Q K_j^T (SS) into one of two S buffers, O += P_j V_j (TS).
+// Tensor memory (256 columns): O [0, D), S0 [D, D+64), S1 [D+64, D+128); P_j aliases S_j.
+// Two CTAs fit on an SM (about 103 KB of shared memory and 256 TMEM columns each), so one CTA's softmax
+// overlaps the other's MMAs.
+//
+// Every wait on an mbarrier is bounded; on expiry the CTA records a code in a device error word,
+// stops issuing work, and leaves through the common teardown (TMEM is freed).
+#include <type_traits>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace sla {
+namespace tc {
+
+struct TcFwdParams {
+  const int32_t* lut;
+  float* lse;
+  int* err;
+  int L, mb, topk, n_tiles;
+  float scale_log2;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+enum : int {
+  kErrQ = 101, kErrKFull = 102, kErrVFull = 103, kErrEmpty = 104, kErrSFull = 105, kErrPFull = 106,
+  kErrPvDone = 107, kErrDrain = 108
+};
+
+template <typename T, int D, int BM>
+__global__ void __launch_bounds__(192, 2)
+sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                     TcFwdParams p) {
+  constexpr int SLABS = D / 64;                 // 64-column (128-byte) slabs per row
+  constexpr int Q_SLAB = 128 * 128;             // bytes of one Q slab (128 rows x 128 B)
+  constexpr int KV_SLAB = 64 * 128;             // bytes of one K/V slab (64 rows x 128 B)
+  constexpr int Q_BYTES = SLABS * Q_SLAB;
+  constexpr int KV_BYTES = SLABS * KV_SLAB;
+  constexpr int FMT = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr uint32_t IDESC_S = idesc_f16(FMT, 128, 64, 0, 0);
+  constexpr uint32_t IDESC_PV = idesc_f16(FMT, 128, D, 0, 1);
+  constexpr uint32_t TMEM_COLS = 256;
+  constexpr int COL_O = 0, COL_S = D;
+  constexpr float kRescaleThreshold = 8.0f;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[12];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_n_entries;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x, bh = blockIdx.y;
+  const int L = p.L;
+
+  // 1024-byte aligned tile area (required by the 128B swizzle pattern)
+  const uint32_t raw_a = smem_u32(smem_raw);
+  const uint32_t base_a = (raw_a + 1023u) & ~1023u;
+  uint8_t* base_p = smem_raw + (base_a - raw_a);
+  const uint32_t sQ = base_a;
+  const uint32_t sK0 = sQ + Q_BYTES;            // stage s at sK0 + s * KV_BYTES
+  const uint32_t sV0 = sK0 + 2 * KV_BYTES;
+  int32_t* ulist = reinterpret_cast<int32_t*>(base_p + Q_BYTES + 4 * KV_BYTES);
+
+  const uint32_t bar0 = smem_u32(&bars[0]);
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  // 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 kv_empty | 7,8 s_full | 9,10 p_full | 11 pv_done
+  constexpr int B_Q = 0, B_K = 1, B_V = 3, B_E = 5, B_S = 7, B_P = 9, B_PV = 11;
+
+  if (tid == 0) {
+    s_abort = *reinterpret_cast<volatile int*>(p.err) != 0;  // an earlier CTA failed: do no work
+    mbar_init(BAR(B_Q), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(BAR(B_K + s), 1);
+      mbar_init(BAR(B_V + s), 1);
+      mbar_init(BAR(B_E + s), 1);
+      mbar_init(BAR(B_S + s), 1);
+      mbar_init(BAR(B_P + s), 128);
+    }
+    mbar_init(BAR(B_PV), 1);
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 4 && lane == 0) {
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmO);
+    // entry list: block index | bit 28 (upper half of the tile selects it) | bit 29 (lower half)
+    if (BM == 128) {
+      const int32_t* row = p.lut + (static_cast<size_t>(bh) * p.mb + tile) * p.topk;
+      for (int i = 0; i < p.topk; ++i) ulist[i] = row[i] | (3 << 28);
+      s_n_entries = p.topk;
+    } else {
+      const int ia = 2 * tile, ib = 2 * tile + 1;
+      const int32_t* ra = p.lut + (static_cast<size_t>(bh) * p.mb + ia) * p.topk;
+      const int32_t* rb = ra + p.topk;
+      const int nbv = ib < p.mb ? p.topk : 0;
+      int a = 0, b = 0, n = 0;
+      while (a < p.topk || b < nbv) {
+        int va = a < p.topk ? ra[a] : 0x7fffffff;
+        int vb = b < nbv ? rb[b] : 0x7fffffff;
+        if (va == vb) { ulist[n++] = va | (3 << 28); ++a; ++b; }
+        else if (va < vb) { ulist[n++] = va | (1 << 28); ++a; }
+        else { ulist[n++] = vb | (2 << 28); ++b; }
+      }
+      s_n_entries = n;
+    }
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+  const int n_ent = s_n_entries;
+  volatile int* abortp = &s_abort;
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0 && !*abortp) {
+      mbar_expect_tx(BAR(B_Q), Q_BYTES);
+      for (int c = 0; c < SLABS; ++c) tma_load_3d(sQ + c * Q_SLAB, &tmQ, BAR(B_Q), c * 64, tile * 128, bh);
+      int issued = 0;
+      for (int j = 0; j < n_ent; ++j) {
+        const int s = j & 1;
+        if (j >= 2 && !mbar_wait(BAR(B_E + s), ((j >> 1) - 1) & 1, kErrEmpty, p.err)) { *abortp = 1; break; }
+        if (*abortp) break;
+        const int row0 = (ulist[j] & 0x0fffffff) * 64;
+        mbar_expect_tx(BAR(B_K + s), KV_BYTES);
+        for (int c = 0; c < SLABS; ++c) tma_load_3d(sK0 + s * KV_BYTES + c * KV_SLAB, &tmK, BAR(B_K + s), c * 64, row0, bh);
+        mbar_expect_tx(BAR(B_V + s), KV_BYTES);
+        for (int c = 0; c < SLABS; ++c) tma_load_3d(sV0 + s * KV_BYTES + c * KV_SLAB, &tmV, BAR(B_V + s), c * 64, row0, bh);
+        issued = j + 1;
+      }
+      if (*abortp) {
+        // let the copies already in flight land before the CTA's shared memory goes away
+        mbar_wait(BAR(B_Q), 0, kErrDrain, p.err);
+        for (int j = max(0, issued - 2); j < issued; ++j) {
+          mbar_wait(BAR(B_K + (j & 1)), (j >> 1) & 1, kErrDrain, p.err);
+          mbar_wait(BAR(B_V + (j & 1)), (j >> 1) & 1, kErrDrain, p.err);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0 && !*abortp) {
+      auto issue_s = [&](int j) {
+        const uint32_t kb = sK0 + (j & 1) * KV_BYTES;
+        const uint32_t d = tmem + COL_S + (j & 1) * 64;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) , in = (kk & 3) * 32;
+          uint64_t da = smem_desc_sw128(sQ + off * Q_SLAB + in, 16, 1024);
+          uint64_t db = smem_desc_sw128(kb + off * KV_SLAB + in, 16, 1024);
+          mma_ss(d, da, db, IDESC_S, kk > 0 ? 1u : 0u);
+        }
+      };
+      bool ok = mbar_wait(BAR(B_Q), 0, kErrQ, p.err) && mbar_wait(BAR(B_K), 0, kErrKFull, p.err);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        tc_commit(BAR(B_S));
+      }
+      for (int j = 0; ok && j < n_ent; ++j) {
+        if (j + 1 < n_ent) {
+          ok = mbar_wait(BAR(B_K + ((j + 1) & 1)), ((j + 1) >> 1) & 1, kErrKFull, p.err);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(j + 1);
+          tc_commit(BAR(B_S + ((j + 1) & 1)));
+        }
+        ok = mbar_wait(BAR(B_P + (j & 1)), (j >> 1) & 1, kErrPFull, p.err) &&
+             mbar_wait(BAR(B_V + (j & 1)), (j >> 1) & 1, kErrVFull, p.err);
+        if (!ok || *abortp) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t vb = sV0 + (j & 1) * KV_BYTES;
+        const uint32_t pa = tmem + COL_S + (j & 1) * 64;   // P_j: 16-bit pairs packed over S_j
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          // B = V_j rows [16 kk, +16): MN-major, 8-row groups 1024 B apart, 64-column slabs KV_SLAB apart
+          uint64_t db = smem_desc_sw128(vb + kk * 2048, KV_SLAB, 1024);
+          mma_ts(tmem + COL_O, pa + kk * 8, db, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(BAR(B_E + (j & 1)));
+        tc_commit(BAR(B_PV));
+      }
+      if (!ok) *abortp = 1;
+    }
+  } else {
+    // ------------------------------ softmax warps ------------------------------
+    const int row = tid;                                   // tile row == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int half = BM == 128 ? 0 : (warp >> 1);
+    const float sc = p.scale_log2;
+    float m_true = -INFINITY, m_used = -INFINITY, l = 0.f;
+    bool ok = !*abortp;
+    for (int j = 0; ok && j < n_ent; ++j) {
+      const int b = j & 1;
+      if (!mbar_wait(BAR(B_S + b), (j >> 1) & 1, kErrSFull, p.err)) { ok = false; break; }
+      if (*abortp) { ok = false; break; }
+      tc_fence_after();
+      const int entry = ulist[j];
+      const bool active = BM == 128 || ((entry >> (28 + half)) & 1);
+      const uint32_t s_addr = tmem + lane_addr + COL_S + b * 64;
+      uint32_t pk[32];
+      if (active) {
+        uint32_t sv[64];
+        tmem_ld_x64(s_addr, sv);
+        tmem_wait_ld();
+        const int valid = L - (entry & 0x0fffffff) * 64;     // keys of this block that exist (kernel.py:57)
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          float x = __uint_as_float(sv[c]) * sc;
+          if (valid < 64 && c >= valid) x = -INFINITY;       // kernel.py:61-62
+          sv[c] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
+        m_true = fmaxf(m_true, mx);
+        const bool need = m_true > m_used + kRescaleThreshold;   // also true on the first active block
+        if (j > 0 && __any_sync(0xffffffffu, need)) {
+          // O holds sum_{j' < j} P V with the old reference maximum: wait for PV_{j-1}, then scale it
+          if (!mbar_wait(BAR(B_PV), (j - 1) & 1, kErrPvDone, p.err)) { ok = false; break; }
+          tc_fence_after();
+          const float alpha = need ? ex2(m_used - m_true) : 1.0f;
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t ov[32];
+            tmem_ld_x32(tmem + lane_addr + COL_O + c0, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
+            tmem_st_x32(tmem + lane_addr + COL_O + c0, ov);
+          }
+        }
+        if (need) {
+          l *= ex2(m_used - m_true);
+          m_used = m_true;
+        }
+        float rs = 0.f;
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          float p0 = ex2(__uint_as_float(sv[c]) - m_used);
+          float p1 = ex2(__uint_as_float(sv[c + 1]) - m_used);
+          rs += p0 + p1;
+          pk[c >> 1] = Elem<T>::pack2(p0, p1);              // P rounded to T before P.V (kernel.py:71)
+        }
+        l += rs;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) pk[c] = 0u;
+      }
+      tmem_st_x32(s_addr, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(BAR(B_P + b));
+    }
+    if (ok && n_ent > 0) ok = mbar_wait(BAR(B_PV), (n_ent - 1) & 1, kErrPvDone, p.err);
+    if (!ok) *abortp = 1;
+    // all four softmax warps agree on whether the tile is good before touching the Q buffer
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    if (!*abortp) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      const int grow = tile * 128 + row;
+      if (grow < L) p.lse[static_cast<size_t>(bh) * L + grow] = m_used + log2f(l);   // kernel.py:81
+      // O / l -> T, staged in the (idle) Q buffer in the same 128B-swizzled slab layout, then one TMA
+      // store per slab; rows past the end of the sequence are clipped by the copy engine.
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t ov[32];
+        tmem_ld_x32(tmem + lane_addr + COL_O + c0, ov);
+        tmem_wait_ld();
+        const uint32_t slab = sQ + (c0 >> 6) * Q_SLAB + row * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t w0 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
+          uint32_t w1 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
+          uint32_t w2 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
+          uint32_t w3 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
+          const int chunk = ((c0 & 63) >> 3) + q4;
+          const uint32_t addr = slab + ((chunk ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");
+      if (tid == 0) {
+        for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO, sQ + c * Q_SLAB, c * 64, tile * 128, bh);
+        tma_store_commit();
+        tma_store_wait_all();
+      }
+    }
+  }
+  // ------------------------------ teardown ------------------------------
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+}  // namespace tc
+
+// The error word lives in this translation unit; other tcgen05 kernels receive its address.
+__device__ int g_tc_error_word = 0;
+
+int* tc_error_word() {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_tc_error_word);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess) {
+      if (e != cudaSuccess) set_last_cuda_error(e);
+      return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+int make_tmap_3d(CUtensorMap* out, const void* base, int dtype, int D, int L, int BH, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return SLA_ERR_CUDA;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(BH)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(L) * D * 2};
+  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, dtype == SLA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_cuda_error(cudaErrorInvalidValue);
+    return SLA_ERR_CUDA;
+  }
+  return SLA_OK;
+}
+
+template <typename T, int D, int BM>
+static int launch_tc(const sla_shape* s, const FwdParams& fp, cudaStream_t st) {
+  const int bh = s->B * s->H;
+  CUtensorMap tq, tk, tv, to;
+  int rc;
+  if ((rc = make_tmap_3d(&tq, fp.q, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tk, fp.k, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tv, fp.v, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&to, fp.o, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  tc::TcFwdParams p;
+  p.err = tc_error_word();
+  if (p.err == nullptr) return SLA_ERR_CUDA;
+  p.lut = fp.lut; p.lse = fp.lse; p.L = s->L; p.mb = fp.mb; p.topk = fp.topk;
+  p.n_tiles = ceil_div(s->L, 128);
+  p.scale_log2 = fp.scale_log2;
+  auto kern = tc::sparse_fwd_tc_kernel<T, D, BM>;
+  const int tiles_bytes = 128 * D * 2 + 4 * 64 * D * 2;
+  const int smem = 1024 + tiles_bytes + 2 * fp.topk * 4 + 16;
+  if (smem > 113 * 1024) return SLA_ERR_BAD_TOPK;
+  SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  kern<<<dim3(p.n_tiles, bh), 192, smem, st>>>(tq, tk, tv, to, p);
+  SLA_LAUNCH_OK();
+  return SLA_OK;
+}
+
+int run_sparse_fwd_tc(const sla_shape* s, const FwdParams& p, cudaStream_t st) {
+#define SLA_TC(TT)                                                                     \
+  if (s->D == 64) return s->BLKQ == 64 ? launch_tc<TT, 64, 64>(s, p, st) : launch_tc<TT, 64, 128>(s, p, st); \
+  return s->BLKQ == 64 ? launch_tc<TT, 128, 64>(s, p, st) : launch_tc<TT, 128, 128>(s, p, st);
+  if (s->dtype == SLA_BF16) { SLA_TC(__nv_bfloat16) }
+  SLA_TC(__half)
+#undef SLA_TC
+}
+
+int read_tc_error(int* out, bool clear) {
+  int v = 0;
+  SLA_CUDA_OK(cudaMemcpyFromSymbol(&v, g_tc_error_word, sizeof(int)));
+  if (clear && v != 0) {
+    int z = 0;
+    SLA_CUDA_OK(cudaMemcpyToSymbol(g_tc_error_word, &z, sizeof(int)));
+  }
+  *out = v;
+  return SLA_OK;
+}
+
+}  // namespace sla

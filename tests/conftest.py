@@ -21,3 +21,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _no_device_side_timeouts(request):
+    """After every GPU test: no bounded device-side wait may have run out."""
+    yield
+    if "gpu" in request.keywords:
+        import torch
+        if torch.cuda.is_available():
+            from sla_b200 import _lib
+            code = _lib.poll_device_error(clear=True)
+            assert code == 0, f"a tcgen05 kernel reported a timed-out wait (code {code})"
