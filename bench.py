@@ -348,13 +348,13 @@ def main():
                                            bm.lut.data_ptr(), o_s.data_ptr(), lse.data_ptr(), st))
 
     dq_, dk_, dv_ = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
-    delta = torch.empty_like(lse)
+    bws = ops._workspace(shape, _lib.OP_SPARSE_BWD, dev)
 
     def k_bwd():
         _lib.check(_lib.lib.sla_sparse_bwd(C.byref(shape), q.data_ptr(), k.data_ptr(), v.data_ptr(), o_s.data_ptr(),
                                            lse.data_ptr(), do.data_ptr(), bm.lut.data_ptr(),
                                            bm.col_offsets.data_ptr(), bm.col_index.data_ptr(), dq_.data_ptr(),
-                                           dk_.data_ptr(), dv_.data_ptr(), delta.data_ptr(), 0, st))
+                                           dk_.data_ptr(), dv_.data_ptr(), bws.data_ptr(), bws.numel(), st))
 
     def k_map():
         ops.block_map(q, k, w.topk, w.BLKQ, w.BLKK, want_cols=True)

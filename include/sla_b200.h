@@ -55,7 +55,7 @@ enum sla_status {
 enum sla_dtype { SLA_BF16 = 0, SLA_FP16 = 1, SLA_FP32 = 2 };
 enum sla_feature { SLA_PHI_SOFTMAX = 0, SLA_PHI_RELU = 1, SLA_PHI_ELU = 2 };
 enum sla_op { SLA_OP_BLOCK_MAP = 0, SLA_OP_FWD = 1, SLA_OP_BWD = 2, SLA_OP_LINEAR_STATE = 3,
-              SLA_OP_SAGE_FWD = 4 };
+              SLA_OP_SAGE_FWD = 4, SLA_OP_SPARSE_BWD = 5 };
 enum sla_flags {
   SLA_FLAG_SPARSE_ONLY = 1, /* skip the linear branch and proj_l (the `_attention` operator) */
   SLA_FLAG_LEGACY_MMA = 2   /* use the mma.sync kernels instead of the tcgen05 ones */
@@ -110,12 +110,12 @@ SLA_API int sla_sparse_fwd(const sla_shape* shape, const void* q, const void* k,
                    const int32_t* lut, void* o_s, float* lse, sla_stream_t stream);
 
 /* Replaces sparse_linear_attention/kernel.py:277-320 _attention.backward (+ kernels :85-237).
- * delta (B,H,L) fp32 is written by the call. If `accumulate` is non-zero dq/dk/dv already hold
- * a contribution (the linear branch's) that is added to the sparse one. */
+ * Workspace: sla_workspace_bytes(shape, SLA_OP_SPARSE_BWD) (row statistics: delta of
+ * kernel.py:102-105 next to lse). dq, dk, dv are overwritten. */
 SLA_API int sla_sparse_bwd(const sla_shape* shape, const void* q, const void* k, const void* v,
                    const void* o_s, const float* lse, const void* do_s, const int32_t* lut,
                    const int32_t* col_offsets, const int32_t* col_index, void* dq, void* dk,
-                   void* dv, float* delta, int accumulate, sla_stream_t stream);
+                   void* dv, void* ws, size_t ws_bytes, sla_stream_t stream);
 
 /* Replaces the feature map on k and the two state reductions of
  * sparse_linear_attention/core.py:91,93-94 (kvsum, ksum). Writes lin_state. */

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(_HERE, "libsla_b200.so")
 
 SLA_BF16, SLA_FP16, SLA_FP32 = 0, 1, 2
 PHI = {"softmax": 0, "relu": 1, "elu": 2}
-OP_BLOCK_MAP, OP_FWD, OP_BWD, OP_LINEAR_STATE, OP_SAGE_FWD = 0, 1, 2, 3, 4
+OP_BLOCK_MAP, OP_FWD, OP_BWD, OP_LINEAR_STATE, OP_SAGE_FWD, OP_SPARSE_BWD = 0, 1, 2, 3, 4, 5
 FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA = 1, 2
 
 # every symbol include/sla_b200.h declares
@@ -64,7 +64,7 @@ def _load() -> C.CDLL:
     lib.sla_sparse_fwd.restype = C.c_int
     lib.sla_sparse_fwd.argtypes = [sp, vp, vp, vp, i32p, vp, f32p, vp]
     lib.sla_sparse_bwd.restype = C.c_int
-    lib.sla_sparse_bwd.argtypes = [sp, vp, vp, vp, vp, f32p, vp, i32p, i32p, i32p, vp, vp, vp, f32p, C.c_int, vp]
+    lib.sla_sparse_bwd.argtypes = [sp, vp, vp, vp, vp, f32p, vp, i32p, i32p, i32p, vp, vp, vp, vp, C.c_size_t, vp]
     lib.sla_linear_state.restype = C.c_int
     lib.sla_linear_state.argtypes = [sp, vp, vp, vp, vp, C.c_size_t, vp]
     lib.sla_fwd.restype = C.c_int

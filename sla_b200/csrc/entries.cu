@@ -96,59 +96,78 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   return run_linear_readout(s, p, st);
 }
 
+static int sparse_bwd_impl(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s,
+                           const float* lse, const void* do_s, const int32_t* lut, const int32_t* col_offsets,
+                           const int32_t* col_index, void* dq, void* dk, void* dv, unsigned char* ws,
+                           int accumulate_legacy, cudaStream_t st) {
+  WsSparseBwd w = ws_sparse_bwd(s);
+  BwdParams p;
+  p.q = q; p.k = k; p.v = v; p.o_s = o_s; p.d_o = do_s; p.lse = lse;
+  p.delta = reinterpret_cast<float*>(ws + w.delta); p.lut = lut;
+  p.col_offsets = col_offsets; p.col_index = col_index; p.dq = dq; p.dk = dk; p.dv = dv;
+  p.L = s->L; p.mb = ceil_div(s->L, s->BLKQ); p.nb = ceil_div(s->L, s->BLKK); p.topk = s->topk;
+  p.scale = softmax_scale(s); p.scale_log2 = p.scale * kLog2e; p.accumulate = accumulate_legacy;
+  if (!(s->flags & SLA_FLAG_LEGACY_MMA)) {
+    int rc = run_sparse_bwd_tc(s, p, ws + w.stats, st);
+    if (rc != SLA_ERR_BAD_SHAPE) return rc;   // lists too long for the tcgen05 kernel's shared memory
+  }
+  return run_sparse_bwd_mma(s, p, st);
+}
+
 int sla_sparse_bwd(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s,
                    const float* lse, const void* do_s, const int32_t* lut, const int32_t* col_offsets,
-                   const int32_t* col_index, void* dq, void* dk, void* dv, float* delta, int accumulate,
+                   const int32_t* col_index, void* dq, void* dk, void* dv, void* ws, size_t ws_bytes,
                    sla_stream_t stream) {
-  if (!q || !k || !v || !o_s || !lse || !do_s || !lut || !col_offsets || !col_index || !dq || !dk || !dv ||
-      !delta)
+  if (!q || !k || !v || !o_s || !lse || !do_s || !lut || !col_offsets || !col_index || !dq || !dk || !dv || !ws)
     return SLA_ERR_NULL;
   int rc = check_common(s);
   if (rc != SLA_OK) return rc;
-  if (!all_aligned({q, k, v, o_s, do_s, dq, dk, dv})) return SLA_ERR_BAD_ALIGN;
-  BwdParams p;
-  p.q = q; p.k = k; p.v = v; p.o_s = o_s; p.d_o = do_s; p.lse = lse; p.delta = delta; p.lut = lut;
-  p.col_offsets = col_offsets; p.col_index = col_index; p.dq = dq; p.dk = dk; p.dv = dv;
-  p.L = s->L; p.mb = ceil_div(s->L, s->BLKQ); p.nb = ceil_div(s->L, s->BLKK); p.topk = s->topk;
-  p.scale = softmax_scale(s); p.scale_log2 = p.scale * kLog2e; p.accumulate = accumulate;
-  return run_sparse_bwd_mma(s, p, static_cast<cudaStream_t>(stream));
+  if (!all_aligned({q, k, v, o_s, do_s, dq, dk, dv, ws})) return SLA_ERR_BAD_ALIGN;
+  if (ws_bytes < ws_sparse_bwd(s).total) return SLA_ERR_WS_TOO_SMALL;
+  return sparse_bwd_impl(s, q, k, v, o_s, lse, do_s, lut, col_offsets, col_index, dq, dk, dv,
+                         static_cast<unsigned char*>(ws), 0, static_cast<cudaStream_t>(stream));
 }
 
 int sla_bwd(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s, const float* lse,
             const void* d_o, const int32_t* lut, const int32_t* col_offsets, const int32_t* col_index,
             const float* w, const void* lin_state, void* dq, void* dk, void* dv, float* dw, float* dbias,
             void* ws, size_t ws_bytes, sla_stream_t stream) {
-  if (!ws) return SLA_ERR_NULL;
+  if (!q || !k || !v || !o_s || !lse || !d_o || !lut || !col_offsets || !col_index || !dq || !dk || !dv || !ws)
+    return SLA_ERR_NULL;
   int rc = check_common(s);
   if (rc != SLA_OK) return rc;
+  if (!all_aligned({q, k, v, o_s, d_o, dq, dk, dv, lin_state, ws})) return SLA_ERR_BAD_ALIGN;
   WsBwd wb = ws_bwd(s);
-  // delta lives at the end of the workspace
-  size_t delta_off = wb.total;
-  size_t need = delta_off + round256(size_t(s->B) * s->H * s->L * 4);
-  if (ws_bytes < need) return SLA_ERR_WS_TOO_SMALL;
+  if (ws_bytes < wb.total + ws_sparse_bwd(s).total) return SLA_ERR_WS_TOO_SMALL;
   unsigned char* base = static_cast<unsigned char*>(ws);
-  float* delta = reinterpret_cast<float*>(base + delta_off);
+  unsigned char* sparse_ws = base + wb.total;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int accumulate = 0;
-  if (!(s->flags & SLA_FLAG_SPARSE_ONLY)) {
-    if (!w || !lin_state || !dw || !dbias || !q || !k || !v || !d_o || !dq || !dk || !dv) return SLA_ERR_NULL;
-    if (!all_aligned({q, k, v, d_o, dq, dk, dv, lin_state, ws})) return SLA_ERR_BAD_ALIGN;
-    rc = convert_proj(s, w, nullptr, base + wb.wbits, st);
-    if (rc != SLA_OK) return rc;
-    LinBwdParams lp;
-    lp.q = q; lp.k = k; lp.v = v; lp.d_o = d_o; lp.lin_state = lin_state; lp.wbits = base + wb.wbits; lp.w = w;
-    lp.dq = dq; lp.dk = dk; lp.dv = dv;
-    lp.g_partial = reinterpret_cast<float*>(base + wb.g_partial);
-    lp.dh = base + wb.dh;
-    lp.dz = reinterpret_cast<float*>(base + wb.dz);
-    lp.dw_part = reinterpret_cast<float*>(base + wb.dw_part);
-    lp.dw = dw; lp.dbias = dbias; lp.L = s->L; lp.nch = wb.nch; lp.rows = wb.rows;
+  if (s->flags & SLA_FLAG_SPARSE_ONLY)
+    return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 0, st);
+  if (!w || !lin_state || !dw || !dbias) return SLA_ERR_NULL;
+  const bool legacy = (s->flags & SLA_FLAG_LEGACY_MMA) != 0;
+  rc = convert_proj(s, w, nullptr, base + wb.wbits, st);
+  if (rc != SLA_OK) return rc;
+  LinBwdParams lp;
+  lp.q = q; lp.k = k; lp.v = v; lp.d_o = d_o; lp.lin_state = lin_state; lp.wbits = base + wb.wbits; lp.w = w;
+  lp.dq = dq; lp.dk = dk; lp.dv = dv;
+  lp.g_partial = reinterpret_cast<float*>(base + wb.g_partial);
+  lp.dh = base + wb.dh;
+  lp.dz = reinterpret_cast<float*>(base + wb.dz);
+  lp.dw_part = reinterpret_cast<float*>(base + wb.dw_part);
+  lp.dw = dw; lp.dbias = dbias; lp.L = s->L; lp.nch = wb.nch; lp.rows = wb.rows;
+  if (legacy) {
+    // linear branch first (overwrites), then the mma.sync sparse kernels add their part
+    lp.accumulate = 0;
     rc = run_linear_bwd(s, lp, st);
     if (rc != SLA_OK) return rc;
-    accumulate = 1;
+    return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 1, st);
   }
-  return sla_sparse_bwd(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, delta, accumulate,
-                        stream);
+  // tcgen05 sparse kernels overwrite dq, dk, dv; the linear branch then adds its part
+  rc = sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 0, st);
+  if (rc != SLA_OK) return rc;
+  lp.accumulate = 1;
+  return run_linear_bwd(s, lp, st);
 }
 
 }  // extern "C"

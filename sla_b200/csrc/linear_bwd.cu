@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams 
     feature_map_bwd_frags<T, KS, FEAT>(acc, pq);
     // dq_lin: stage in this warp's rows of the Q tile (its fragments are no longer needed) and flush
     store_acc_to_tile<T, D, D / 8>(sQ, acc, m0, lane);
-    flush16<T, D>(sQ, m0, dqg, row0 + m0, L, lane, false);
+    flush16<T, D>(sQ, m0, dqg, row0 + m0, L, lane, p.accumulate != 0);
     // phi(q)/den for the G reduction, and the row constants for dz
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
@@ -260,12 +260,12 @@ __global__ void __launch_bounds__(128) linear_bwd_kv_kernel(LinBwdParams p) {
   gemm_at_b_nk<T, D, D / 8, KS>(acc, sV_a, m0, sdH_a, lane);  // dphi_k = v dH^T + dz
   feature_map_bwd_frags<T, KS, FEAT>(acc, pk);
   store_acc_to_tile<T, D, D / 8>(sK, acc, m0, lane);
-  flush16<T, D>(sK, m0, static_cast<T*>(p.dk) + head_off, row0 + m0, L, lane, false);
+  flush16<T, D>(sK, m0, static_cast<T*>(p.dk) + head_off, row0 + m0, L, lane, p.accumulate != 0);
 #pragma unroll
   for (int j = 0; j < D / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   gemm_b_kn<T, D, D / 8, KS>(acc, pk, sdH_a, 0, 0, lane);  // dv_lin = phi(k) dH
   store_acc_to_tile<T, D, D / 8>(sV, acc, m0, lane);
-  flush16<T, D>(sV, m0, static_cast<T*>(p.dv) + head_off, row0 + m0, L, lane, false);
+  flush16<T, D>(sV, m0, static_cast<T*>(p.dv) + head_off, row0 + m0, L, lane, p.accumulate != 0);
 }
 
 template <typename T, int D, int FEAT>

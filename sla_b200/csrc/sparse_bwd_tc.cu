@@ -1,0 +1,458 @@
+// Backward of the block-sparse branch on tcgen05 / TMEM / TMA (mathematics:
+// sparse_linear_attention/kernel.py:85-237).
+//
+// One kernel template, two instantiations:
+//   KVS = false  "dQ":    a CTA owns a 128-row query tile (Q, dO stationary in shared memory) and
+//                         streams the selected K_j, V_j blocks.   T1 = Q K_j^T, T2 = dO V_j^T,
+//                         dS = P * (T2 - delta),  dQ += dS K_j.
+//   KVS = true   "dK/dV": a CTA owns a 128-key tile (two adjacent KV blocks; K, V stationary) and
+//                         streams 64-row slices Q_i, dO_i of the query blocks that selected either
+//                         block.                 T1 = K Q_i^T, T2 = V dO_i^T (transposed scores),
+//                         dV += P^T dO_i,  dK += dS^T Q_i.
+// As in the forward, a 128-row tile that spans two 64-row blocks walks the UNION of the two blocks'
+// (ascending) lists; two mask bits per entry say which half selected it and the other half
+// contributes zeros, so all MMAs run at M = 128 while the mask stays 64 x 64.
+//
+// Roles (320 threads, one CTA per SM):
+//   warps 0-3 / 4-7  two compute groups; group w handles entries j = w (mod 2) in TMEM buffer w:
+//                    reads T1, T2, forms P and dS (no cross-entry state in the backward), writes them
+//                    back as 16-bit A operands over T1 / T2.
+//   warp 8           TMA producer (stationary tiles once, then a ring of streamed tiles + row stats)
+//   warp 9           MMA issuer.
+// TMEM: acc1 [0,D) (dQ or dK), acc2 [D,2D) (dV, KVS only), then per buffer T1 (64 cols), T2 (64 cols).
+// Row statistics (lse, delta) come from a padded (B*H, Lpad, 2) fp32 array written by a small
+// preprocessing kernel (delta = rowsum(o_s * dO), kernel.py:102-105; padding rows hold lse = +inf).
+// All waits are bounded; see tc_common.cuh.
+#include <type_traits>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace sla {
+namespace tc {
+
+struct TcBwdParams {
+  const int32_t* list;       // dQ: lut (B*H, mb, topk)          KVS: col_index (B*H, mb*topk)
+  const int32_t* offsets;    // dQ: unused                        KVS: col_offsets (B*H, nb+1)
+  const float2* stats;       // (B*H, Lpad) {lse, delta}
+  int* err;
+  int L, Lpad, mb, nb, topk;
+  float scale, scale_log2;
+};
+
+__device__ __forceinline__ float ex2b(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+enum : int { kBErrX = 201, kBErrYFull = 202, kBErrYEmpty = 203, kBErrTFull = 204, kBErrCFull = 205,
+             kBErrAcc = 206, kBErrDrain = 207 };
+
+template <typename T, int D, int BM, bool KVS>
+__global__ void __launch_bounds__(320, 1)
+sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
+                     const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
+                     const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
+                     TcBwdParams p) {
+  constexpr int SLABS = D / 64;
+  constexpr int X_SLAB = 128 * 128, Y_SLAB = 64 * 128;
+  constexpr int X_BYTES = SLABS * X_SLAB, Y_BYTES = SLABS * Y_SLAB;
+  constexpr int NS = D == 128 ? 4 : 6;                       // ring stages
+  constexpr int STAT_BYTES = 64 * 8;
+  constexpr int SL = KVS ? BM / 64 : 1;                      // 64-row slices per list entry
+  constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr uint32_t IDESC_T = idesc_f16(FMT, 128, 64, 0, 0);
+  constexpr uint32_t IDESC_ACC = idesc_f16(FMT, 128, D, 0, 1);
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr int COL_ACC1 = 0, COL_ACC2 = D, COL_T = KVS ? 2 * D : D;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * NS + 6];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_n_entries;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x, bh = blockIdx.y;
+  const int L = p.L;
+
+  const uint32_t raw_a = smem_u32(smem_raw);
+  const uint32_t base_a = (raw_a + 1023u) & ~1023u;
+  uint8_t* base_p = smem_raw + (base_a - raw_a);
+  const uint32_t sX1 = base_a, sX2 = sX1 + X_BYTES;
+  const uint32_t sY0 = sX2 + X_BYTES;                        // stage s: Y1 at sY0 + s*2*Y_BYTES, Y2 right after
+  const uint32_t sStat0 = sY0 + NS * 2 * Y_BYTES;            // stage s: 64 x {lse, delta}
+  const float2* stat_p = reinterpret_cast<const float2*>(base_p + 2 * X_BYTES + NS * 2 * Y_BYTES);
+  int32_t* ulist = reinterpret_cast<int32_t*>(base_p + 2 * X_BYTES + NS * 2 * Y_BYTES + NS * STAT_BYTES);
+
+  const uint32_t bar0 = smem_u32(&bars[0]);
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  // 0 x_full | 1..NS y_full | NS+1..2NS y_empty | then t_full[2], c_full[2], acc_done
+  constexpr int B_X = 0, B_YF = 1, B_YE = 1 + NS, B_T = 1 + 2 * NS, B_C = 3 + 2 * NS, B_ACC = 5 + 2 * NS;
+
+  if (tid == 0) {
+    s_abort = *reinterpret_cast<volatile int*>(p.err) != 0;
+    mbar_init(BAR(B_X), 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(BAR(B_YF + s), 1);
+      mbar_init(BAR(B_YE + s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(BAR(B_T + b), 1);
+      mbar_init(BAR(B_C + b), 128);
+    }
+    mbar_init(BAR(B_ACC), 1);
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 8 && lane == 0) {
+    prefetch_tmap(&tmX1); prefetch_tmap(&tmX2); prefetch_tmap(&tmY1); prefetch_tmap(&tmY2);
+    prefetch_tmap(&tmO1); prefetch_tmap(&tmO2);
+    // entry list: index | bit 28 (first half of the tile selected it) | bit 29 (second half)
+    const int32_t *ra, *rb;
+    int na, nb2;
+    if (!KVS) {
+      if (BM == 128) {
+        ra = p.list + (static_cast<size_t>(bh) * p.mb + tile) * p.topk; na = p.topk; rb = ra; nb2 = 0;
+      } else {
+        ra = p.list + (static_cast<size_t>(bh) * p.mb + 2 * tile) * p.topk; na = p.topk;
+        rb = ra + p.topk; nb2 = 2 * tile + 1 < p.mb ? p.topk : 0;
+      }
+    } else {
+      const int32_t* off = p.offsets + static_cast<size_t>(bh) * (p.nb + 1);
+      const int32_t* ci = p.list + static_cast<size_t>(bh) * p.mb * p.topk;
+      const int j0 = 2 * tile;
+      ra = ci + off[j0]; na = off[j0 + 1] - off[j0];
+      if (j0 + 1 < p.nb) { rb = ci + off[j0 + 1]; nb2 = off[j0 + 2] - off[j0 + 1]; } else { rb = ra; nb2 = 0; }
+    }
+    int a = 0, b = 0, n = 0;
+    const int full = (!KVS && BM == 128) ? 3 : 1;
+    while (a < na || b < nb2) {
+      int va = a < na ? ra[a] : 0x7fffffff;
+      int vb = b < nb2 ? rb[b] : 0x7fffffff;
+      if (va == vb) { ulist[n++] = va | (3 << 28); ++a; ++b; }
+      else if (va < vb) { ulist[n++] = va | (full << 28); ++a; }
+      else { ulist[n++] = vb | (2 << 28); ++b; }
+    }
+    s_n_entries = n;
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+  const int n_ent = s_n_entries * SL;            // streamed 64-row tiles
+  volatile int* abortp = &s_abort;
+
+  // global row of the streamed tile j
+  auto y_row0 = [&](int j) {
+    const int e = ulist[j / SL] & 0x0fffffff;
+    return KVS ? e * BM + (j % SL) * 64 : e * 64;
+  };
+
+  if (warp == 8) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0 && !*abortp) {
+      mbar_expect_tx(BAR(B_X), 2 * X_BYTES);
+      for (int c = 0; c < SLABS; ++c) {
+        tma_load_3d(sX1 + c * X_SLAB, &tmX1, BAR(B_X), c * 64, tile * 128, bh);
+        tma_load_3d(sX2 + c * X_SLAB, &tmX2, BAR(B_X), c * 64, tile * 128, bh);
+      }
+      int issued = 0;
+      for (int j = 0; j < n_ent; ++j) {
+        const int s = j % NS, use = j / NS;
+        if (use > 0 && !mbar_wait(BAR(B_YE + s), (use - 1) & 1, kBErrYEmpty, p.err)) { *abortp = 1; break; }
+        if (*abortp) break;
+        const int row0 = y_row0(j);
+        const uint32_t y1 = sY0 + s * 2 * Y_BYTES, y2 = y1 + Y_BYTES;
+        mbar_expect_tx(BAR(B_YF + s), 2 * Y_BYTES + (KVS ? STAT_BYTES : 0));
+        for (int c = 0; c < SLABS; ++c) {
+          tma_load_3d(y1 + c * Y_SLAB, &tmY1, BAR(B_YF + s), c * 64, row0, bh);
+          tma_load_3d(y2 + c * Y_SLAB, &tmY2, BAR(B_YF + s), c * 64, row0, bh);
+        }
+        if (KVS)
+          bulk_load_1d(sStat0 + s * STAT_BYTES, p.stats + static_cast<size_t>(bh) * p.Lpad + row0, STAT_BYTES,
+                       BAR(B_YF + s));
+        issued = j + 1;
+      }
+      if (*abortp) {
+        mbar_wait(BAR(B_X), 0, kBErrDrain, p.err);
+        for (int j = max(0, issued - NS); j < issued; ++j) mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrDrain, p.err);
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0 && !*abortp) {
+      auto issue_t = [&](int j) {
+        const int s = j % NS, b = j & 1;
+        const uint32_t y1 = sY0 + s * 2 * Y_BYTES, y2 = y1 + Y_BYTES;
+        const uint32_t t1 = tmem + COL_T + b * 128, t2 = t1 + 64;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = kk >> 2, in = (kk & 3) * 32;
+          mma_ss(t1, smem_desc_sw128(sX1 + off * X_SLAB + in, 16, 1024), smem_desc_sw128(y1 + off * Y_SLAB + in, 16, 1024),
+                 IDESC_T, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = kk >> 2, in = (kk & 3) * 32;
+          mma_ss(t2, smem_desc_sw128(sX2 + off * X_SLAB + in, 16, 1024), smem_desc_sw128(y2 + off * Y_SLAB + in, 16, 1024),
+                 IDESC_T, kk > 0 ? 1u : 0u);
+        }
+      };
+      bool ok = mbar_wait(BAR(B_X), 0, kBErrX, p.err);
+      for (int j = 0; ok && j < 2 && j < n_ent; ++j) {
+        ok = mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrYFull, p.err);
+        if (!ok) break;
+        tc_fence_after();
+        issue_t(j);
+        tc_commit(BAR(B_T + (j & 1)));
+      }
+      for (int j = 0; ok && j < n_ent; ++j) {
+        const int s = j % NS, b = j & 1;
+        ok = mbar_wait(BAR(B_C + b), (j >> 1) & 1, kBErrCFull, p.err);
+        if (!ok || *abortp) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t y1 = sY0 + s * 2 * Y_BYTES, y2 = y1 + Y_BYTES;
+        const uint32_t a1 = tmem + COL_T + b * 128, a2 = a1 + 64;   // 16-bit operands written by the compute group
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          if (KVS) {
+            mma_ts(tmem + COL_ACC2, a1 + kk * 8, smem_desc_sw128(y2 + kk * 2048, Y_SLAB, 1024), IDESC_ACC,
+                   (j > 0 || kk > 0) ? 1u : 0u);               // dV += P^T dO_i       (kernel.py:220)
+            mma_ts(tmem + COL_ACC1, a2 + kk * 8, smem_desc_sw128(y1 + kk * 2048, Y_SLAB, 1024), IDESC_ACC,
+                   (j > 0 || kk > 0) ? 1u : 0u);               // dK += dS^T Q_i       (kernel.py:225)
+          } else {
+            mma_ts(tmem + COL_ACC1, a2 + kk * 8, smem_desc_sw128(y1 + kk * 2048, Y_SLAB, 1024), IDESC_ACC,
+                   (j > 0 || kk > 0) ? 1u : 0u);               // dQ += dS K_j         (kernel.py:163)
+          }
+        }
+        tc_commit(BAR(B_YE + s));
+        if (j + 2 < n_ent) {
+          ok = mbar_wait(BAR(B_YF + (j + 2) % NS), ((j + 2) / NS) & 1, kBErrYFull, p.err);
+          if (!ok) break;
+          tc_fence_after();
+          issue_t(j + 2);
+          tc_commit(BAR(B_T + b));
+        }
+      }
+      if (ok) tc_commit(BAR(B_ACC));
+      if (!ok) *abortp = 1;
+    }
+  } else {
+    // ------------------------------ compute groups ------------------------------
+    const int wg = warp >> 2;                               // 0 or 1
+    const int row = tid & 127;                              // tile row == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int half = row >> 6;
+    const float sc = p.scale_log2;
+    const int grow = tile * 128 + row;                      // global query row (dQ) or key row (KVS)
+    float my_lse = INFINITY, my_delta = 0.f;
+    if (!KVS) {
+      float2 st = p.stats[static_cast<size_t>(bh) * p.Lpad + min(grow, p.Lpad - 1)];
+      if (grow < L) { my_lse = st.x; my_delta = st.y; }
+    }
+    const bool key_ok = grow < L;                           // KVS: keys past the end give P = 0 (kernel.py:216)
+    bool ok = !*abortp;
+    for (int j = wg; ok && j < n_ent; j += 2) {
+      if (!mbar_wait(BAR(B_T + wg), (j >> 1) & 1, kBErrTFull, p.err)) { ok = false; break; }
+      if (*abortp) { ok = false; break; }
+      if (KVS && !mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrYFull, p.err)) { ok = false; break; }  // row stats landed
+      tc_fence_after();
+      const int entry = ulist[j / SL];
+      const bool active = (!KVS && BM == 128) || ((entry >> (28 + half)) & 1);
+      const uint32_t t1 = tmem + lane_addr + COL_T + wg * 128, t2 = t1 + 64;
+      const int valid = KVS ? 64 : L - (entry & 0x0fffffff) * 64;   // dQ: keys of this block that exist
+      const float2* stc = stat_p + (j % NS) * 64;
+      if (active) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t sv[32], dv[32];
+          tmem_ld_x32(t1 + h * 32, sv);
+          tmem_ld_x32(t2 + h * 32, dv);
+          tmem_wait_ld();
+          uint32_t pp[16], ds[16];
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            float pv[2], dsv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int col = h * 32 + c + e;
+              float lse_c, del_c;
+              if (KVS) { float2 st = stc[col]; lse_c = st.x; del_c = st.y; } else { lse_c = my_lse; del_c = my_delta; }
+              float pe = ex2b(__uint_as_float(sv[c + e]) * sc - lse_c);
+              if (KVS ? !key_ok : (valid < 64 && col >= valid)) pe = 0.f;   // kernel.py:157 / :216
+              pv[e] = pe;
+              dsv[e] = pe * (__uint_as_float(dv[c + e]) - del_c);          // kernel.py:161 / :224
+            }
+            pp[c >> 1] = Elem<T>::pack2(pv[0], pv[1]);
+            ds[c >> 1] = Elem<T>::pack2(dsv[0], dsv[1]);
+          }
+          if (KVS) tmem_st_x16(t1 + h * 16, pp);
+          tmem_st_x16(t2 + h * 16, ds);
+        }
+      } else {
+        uint32_t z[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) z[c] = 0u;
+        if (KVS) tmem_st_x32(t1, z);
+        tmem_st_x32(t2, z);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(BAR(B_C + wg));
+    }
+    if (ok && n_ent > 0) ok = mbar_wait(BAR(B_ACC), 0, kBErrAcc, p.err);
+    if (ok) ok = mbar_wait(BAR(B_X), 0, kBErrX, p.err);   // the stationary tiles (reused as staging) have landed
+    if (!ok) *abortp = 1;
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    if (!*abortp) {
+      tc_fence_after();
+      // accumulators -> T, staged over the (idle) stationary tiles in the swizzled slab layout, then
+      // TMA stores; rows past the end of the sequence are clipped by the copy engine.
+      const int c_lo = KVS ? 0 : wg * (D / 2), c_hi = KVS ? D : (wg + 1) * (D / 2);
+      const uint32_t acc = tmem + lane_addr + (KVS && wg == 1 ? COL_ACC2 : COL_ACC1);
+      const uint32_t stage = (KVS && wg == 1) ? sX2 : sX1;
+      const float mul = (KVS && wg == 1) ? 1.0f : p.scale;   // dQ, dK carry the softmax scale (kernel.py:164,236)
+      for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
+        uint32_t ov[32];
+        if (n_ent > 0) {
+          tmem_ld_x32(acc + c0, ov);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) ov[c] = 0u;          // nothing selected this tile: gradient is zero
+        }
+        const uint32_t slab = stage + (c0 >> 6) * X_SLAB + row * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t w0 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 0]) * mul, __uint_as_float(ov[q4 * 8 + 1]) * mul);
+          uint32_t w1 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 2]) * mul, __uint_as_float(ov[q4 * 8 + 3]) * mul);
+          uint32_t w2 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 4]) * mul, __uint_as_float(ov[q4 * 8 + 5]) * mul);
+          uint32_t w3 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 6]) * mul, __uint_as_float(ov[q4 * 8 + 7]) * mul);
+          const int chunk = ((c0 & 63) >> 3) + q4;
+          const uint32_t addr = slab + ((chunk ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 256;\n" ::: "memory");
+      if (tid == 0) {
+        for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO1, sX1 + c * X_SLAB, c * 64, tile * 128, bh);
+        if (KVS)
+          for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO2, sX2 + c * X_SLAB, c * 64, tile * 128, bh);
+        tma_store_commit();
+        tma_store_wait_all();
+      }
+    }
+  }
+  // ------------------------------ teardown ------------------------------
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+}  // namespace tc
+
+// delta = rowsum(o_s * dO) (kernel.py:102-105) and lse, interleaved into a padded (B*H, Lpad) array;
+// rows in [L, Lpad) get lse = +inf, delta = 0 so that they contribute P = 0.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ o_s, const T* __restrict__ d_o,
+                                                       const float* __restrict__ lse, float2* __restrict__ stats,
+                                                       float* __restrict__ delta_out, int L, int Lpad) {
+  constexpr int EPL = D / 32;
+  const int bh = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = blockIdx.x * 8 + warp;
+  if (r >= Lpad) return;
+  float s = 0.f;
+  if (r < L) {
+    const T* a = o_s + (static_cast<size_t>(bh) * L + r) * D + lane * EPL;
+    const T* b = d_o + (static_cast<size_t>(bh) * L + r) * D + lane * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; e += 2) {
+      float2 x = Elem<T>::unpack2(*reinterpret_cast<const uint32_t*>(a + e));
+      float2 y = Elem<T>::unpack2(*reinterpret_cast<const uint32_t*>(b + e));
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+  s = warp_sum(s);
+  if (lane == 0) {
+    float l = r < L ? lse[static_cast<size_t>(bh) * L + r] : INFINITY;
+    stats[static_cast<size_t>(bh) * Lpad + r] = make_float2(l, r < L ? s : 0.f);
+    if (r < L && delta_out) delta_out[static_cast<size_t>(bh) * L + r] = s;
+  }
+}
+
+template <typename T, int D, int BM, bool KVS>
+static int launch_bwd_tc(const sla_shape* s, const BwdParams& bp, const float2* stats, int Lpad, cudaStream_t st) {
+  const int bh = s->B * s->H;
+  CUtensorMap x1, x2, y1, y2, o1, o2;
+  int rc;
+  const void *X1 = KVS ? bp.k : bp.q, *X2 = KVS ? bp.v : bp.d_o, *Y1 = KVS ? bp.q : bp.k, *Y2 = KVS ? bp.d_o : bp.v;
+  void *O1 = KVS ? bp.dk : bp.dq, *O2 = KVS ? bp.dv : bp.dq;
+  if ((rc = make_tmap_3d(&x1, X1, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&x2, X2, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&y1, Y1, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&y2, Y2, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&o1, O1, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&o2, O2, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  tc::TcBwdParams p;
+  p.list = KVS ? bp.col_index : bp.lut;
+  p.offsets = bp.col_offsets;
+  p.stats = stats;
+  p.err = tc_error_word();
+  if (p.err == nullptr) return SLA_ERR_CUDA;
+  p.L = s->L; p.Lpad = Lpad; p.mb = bp.mb; p.nb = bp.nb; p.topk = bp.topk;
+  p.scale = bp.scale; p.scale_log2 = bp.scale_log2;
+  constexpr int NS = D == 128 ? 4 : 6;
+  const int max_entries = KVS ? 2 * bp.mb : 2 * bp.topk;
+  const int smem = 1024 + 2 * 128 * D * 2 + NS * 2 * 64 * D * 2 + NS * 512 + max_entries * 4 + 16;
+  if (smem > 227 * 1024) return SLA_ERR_BAD_SHAPE;
+  auto kern = tc::sparse_bwd_tc_kernel<T, D, BM, KVS>;
+  SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  const int tiles = KVS ? ceil_div(bp.nb, 2) : ceil_div(s->L, 128);
+  kern<<<dim3(tiles, bh), 320, smem, st>>>(x1, x2, y1, y2, o1, o2, p);
+  SLA_LAUNCH_OK();
+  return SLA_OK;
+}
+
+template <typename T, int D, int BM>
+static int run_bwd_tc_typed(const sla_shape* s, const BwdParams& bp, float2* stats, int Lpad, cudaStream_t st) {
+  const int bh = s->B * s->H;
+  bwd_prep_kernel<T, D><<<dim3(ceil_div(Lpad, 8), bh), 256, 0, st>>>(
+      static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L, Lpad);
+  SLA_LAUNCH_OK();
+  int rc = launch_bwd_tc<T, D, BM, false>(s, bp, stats, Lpad, st);
+  if (rc != SLA_OK) return rc;
+  return launch_bwd_tc<T, D, BM, true>(s, bp, stats, Lpad, st);
+}
+
+// `stats` must hold B*H*Lpad float2 with Lpad = ceil(L/128)*128.
+int run_sparse_bwd_tc(const sla_shape* s, const BwdParams& bp, void* stats, cudaStream_t st) {
+  const int Lpad = ceil_div(s->L, 128) * 128;
+  float2* sp = static_cast<float2*>(stats);
+#define SLA_TCB(TT)                                                                                         \
+  if (s->D == 64)                                                                                           \
+    return s->BLKQ == 64 ? run_bwd_tc_typed<TT, 64, 64>(s, bp, sp, Lpad, st) : run_bwd_tc_typed<TT, 64, 128>(s, bp, sp, Lpad, st); \
+  return s->BLKQ == 64 ? run_bwd_tc_typed<TT, 128, 64>(s, bp, sp, Lpad, st) : run_bwd_tc_typed<TT, 128, 128>(s, bp, sp, Lpad, st);
+  if (s->dtype == SLA_BF16) { SLA_TCB(__nv_bfloat16) }
+  SLA_TCB(__half)
+#undef SLA_TCB
+}
+
+}  // namespace sla

@@ -88,6 +88,23 @@ inline WsBwd ws_bwd(const sla_shape* s) {
   return w;
 }
 
+// ---- sparse backward: padded row statistics {lse, delta} and the plain delta array ----
+struct WsSparseBwd {
+  size_t stats;   // float2 [BH][Lpad], Lpad = ceil(L/128)*128
+  size_t delta;   // fp32 [BH][L]
+  size_t total;
+};
+inline WsSparseBwd ws_sparse_bwd(const sla_shape* s) {
+  WsSparseBwd w;
+  size_t bh = size_t(s->B) * s->H;
+  size_t lpad = size_t(ws_ceil_div(s->L, 128)) * 128;
+  size_t o = 0;
+  w.stats = o; o += ws_round(bh * lpad * 8);
+  w.delta = o; o += ws_round(bh * size_t(s->L) * 4);
+  w.total = o;
+  return w;
+}
+
 // ---- SageSLA quantized forward ----
 struct WsSage {
   size_t lin;      // linear-state partials (same layout as WsLinearState)

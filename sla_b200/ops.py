@@ -140,9 +140,9 @@ class _attention(torch.autograd.Function):
         else:
             co, ci = column_lists(k_block_id, shape.L, shape.BLKQ, shape.BLKK, shape.topk)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        delta = torch.empty_like(lse)
+        ws = _workspace(shape, _lib.OP_SPARSE_BWD, q.device)
         check(lib.sla_sparse_bwd(C.byref(shape), _p(q), _p(k), _p(v), _p(o_s), _p(lse), _p(do_s), _p(lut32),
-                                 _p(co), _p(ci), _p(dq), _p(dk), _p(dv), _p(delta), 0, _stream(q)))
+                                 _p(co), _p(ci), _p(dq), _p(dk), _p(dv), _p(ws), ws.numel(), _stream(q)))
         return dq, dk, dv, None, None, None, None, None, None
 
 
