@@ -79,6 +79,9 @@ SLA_API const char* sla_last_cuda_error(void);
  * a device word and stops working. This call synchronises the device, returns the code (0 = none) in
  * *code and optionally clears it. */
 SLA_API int sla_poll_device_error(int* code, int clear);
+/* Diagnostic: give the backward tcgen05 kernels a device buffer of 2 x 1024 int64 into which the
+ * first CTA of each kernel records SM-clock timestamps of its pipeline events; NULL switches it off. */
+SLA_API int sla_debug_set_trace(void* device_buffer);
 /* Diagnostic: number of kernels this library has launched in the process so far. */
 SLA_API long long sla_launch_count(void);
 

@@ -18,7 +18,7 @@ FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA = 1, 2
 
 # every symbol include/sla_b200.h declares
 EXPORTS = (
-    "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_topk_count", "sla_workspace_bytes",
+    "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_debug_set_trace", "sla_topk_count", "sla_workspace_bytes",
     "sla_block_map", "sla_column_lists", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_fwd", "sla_bwd",
     "sage_sla_fwd",
 )
@@ -51,6 +51,8 @@ def _load() -> C.CDLL:
     lib.sla_status_string.argtypes = [C.c_int]
     lib.sla_last_cuda_error.restype = C.c_char_p
     lib.sla_launch_count.restype = C.c_longlong
+    lib.sla_debug_set_trace.restype = C.c_int
+    lib.sla_debug_set_trace.argtypes = [C.c_void_p]
     lib.sla_poll_device_error.restype = C.c_int
     lib.sla_poll_device_error.argtypes = [C.POINTER(C.c_int), C.c_int]
     lib.sla_topk_count.restype = C.c_int

@@ -46,6 +46,11 @@ int sla_sparse_fwd(const sla_shape* s, const void* q, const void* k, const void*
   return run_sparse_fwd_tc(s, p, static_cast<cudaStream_t>(stream));
 }
 
+int sla_debug_set_trace(void* device_buffer) {
+  set_trace_buffer(static_cast<long long*>(device_buffer));
+  return SLA_OK;
+}
+
 int sla_poll_device_error(int* code, int clear) {
   if (!code) return SLA_ERR_NULL;
   return read_tc_error(code, clear != 0);

@@ -52,6 +52,7 @@ int run_sparse_fwd_mma(const sla_shape* s, const FwdParams& p, bool lin, cudaStr
 int run_sparse_fwd_tc(const sla_shape* s, const FwdParams& p, cudaStream_t st);
 int run_linear_readout(const sla_shape* s, const FwdParams& p, cudaStream_t st);
 int read_tc_error(int* out, bool clear);
+void set_trace_buffer(long long* p);
 int run_sparse_bwd_tc(const sla_shape* s, const BwdParams& p, void* stats, cudaStream_t st);
 int run_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, float* partial,
                      int nch, int rows, cudaStream_t st);

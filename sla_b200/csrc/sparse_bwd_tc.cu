@@ -13,12 +13,13 @@
 // (ascending) lists; two mask bits per entry say which half selected it and the other half
 // contributes zeros, so all MMAs run at M = 128 while the mask stays 64 x 64.
 //
-// Roles (320 threads, one CTA per SM):
-//   warps 0-3 / 4-7  two compute groups; group w handles entries j = w (mod 2) in TMEM buffer w:
-//                    reads T1, T2, forms P and dS (no cross-entry state in the backward), writes them
-//                    back as 16-bit A operands over T1 / T2.
-//   warp 8           TMA producer (stationary tiles once, then a ring of streamed tiles + row stats)
-//   warp 9           MMA issuer.
+// Roles (576 threads, one CTA per SM):
+//   warps 0-15  four compute groups of 128 threads (thread = tile row = TMEM lane). Group g works on
+//               entries j = g & 1 (mod 2) in TMEM buffer g & 1 and on the 32 score columns
+//               [32 (g >> 1), +32): it reads T1, T2, forms P and dS (the backward has no cross-entry or
+//               cross-column state) and writes them back as 16-bit A operands over its own columns.
+//   warp 16     TMA producer (stationary tiles once, then a ring of streamed tiles + row stats)
+//   warp 17     MMA issuer.
 // TMEM: acc1 [0,D) (dQ or dK), acc2 [D,2D) (dV, KVS only), then per buffer T1 (64 cols), T2 (64 cols).
 // Row statistics (lse, delta) come from a padded (B*H, Lpad, 2) fp32 array written by a small
 // preprocessing kernel (delta = rowsum(o_s * dO), kernel.py:102-105; padding rows hold lse = +inf).
@@ -37,7 +38,8 @@ struct TcBwdParams {
   const int32_t* offsets;    // dQ: unused                        KVS: col_offsets (B*H, nb+1)
   const float2* stats;       // (B*H, Lpad) {lse, delta}
   int* err;
-  int L, Lpad, mb, nb, topk;
+  long long* trace;          // optional timeline of CTA (0,0): [role 0..3][entry < 64][4 events], SM clock cycles
+  int L, Lpad, mb, nb, topk, max_entries;
   float scale, scale_log2;
 };
 
@@ -52,11 +54,15 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
                : "memory");
 }
 
+__device__ __forceinline__ void trace_ev(long long* tr, int role, int j, int ev) {
+  if (tr != nullptr && j < 64) tr[(role * 64 + j) * 4 + ev] = clock64();
+}
+
 enum : int { kBErrX = 201, kBErrYFull = 202, kBErrYEmpty = 203, kBErrTFull = 204, kBErrCFull = 205,
              kBErrAcc = 206, kBErrDrain = 207 };
 
 template <typename T, int D, int BM, bool KVS>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(576, 1)
 sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                      const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
                      const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
@@ -106,44 +112,55 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(BAR(B_T + b), 1);
-      mbar_init(BAR(B_C + b), 128);
+      mbar_init(BAR(B_C + b), 256);
     }
     mbar_init(BAR(B_ACC), 1);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
-  if (warp == 8 && lane == 0) {
-    prefetch_tmap(&tmX1); prefetch_tmap(&tmX2); prefetch_tmap(&tmY1); prefetch_tmap(&tmY2);
-    prefetch_tmap(&tmO1); prefetch_tmap(&tmO2);
-    // entry list: index | bit 28 (first half of the tile selected it) | bit 29 (second half)
-    const int32_t *ra, *rb;
+  if (warp == 16) {
+    if (lane == 0) {
+      prefetch_tmap(&tmX1); prefetch_tmap(&tmX2); prefetch_tmap(&tmY1); prefetch_tmap(&tmY2);
+      prefetch_tmap(&tmO1); prefetch_tmap(&tmO2);
+    }
+    // Entry list: index | bit 28 (first half of the tile selected it) | bit 29 (second half). The two
+    // source lists are copied to shared memory with coalesced loads before the serial merge.
+    const int32_t *ga, *gb;
     int na, nb2;
     if (!KVS) {
       if (BM == 128) {
-        ra = p.list + (static_cast<size_t>(bh) * p.mb + tile) * p.topk; na = p.topk; rb = ra; nb2 = 0;
+        ga = p.list + (static_cast<size_t>(bh) * p.mb + tile) * p.topk; na = p.topk; gb = ga; nb2 = 0;
       } else {
-        ra = p.list + (static_cast<size_t>(bh) * p.mb + 2 * tile) * p.topk; na = p.topk;
-        rb = ra + p.topk; nb2 = 2 * tile + 1 < p.mb ? p.topk : 0;
+        ga = p.list + (static_cast<size_t>(bh) * p.mb + 2 * tile) * p.topk; na = p.topk;
+        gb = ga + p.topk; nb2 = 2 * tile + 1 < p.mb ? p.topk : 0;
       }
     } else {
       const int32_t* off = p.offsets + static_cast<size_t>(bh) * (p.nb + 1);
       const int32_t* ci = p.list + static_cast<size_t>(bh) * p.mb * p.topk;
       const int j0 = 2 * tile;
-      ra = ci + off[j0]; na = off[j0 + 1] - off[j0];
-      if (j0 + 1 < p.nb) { rb = ci + off[j0 + 1]; nb2 = off[j0 + 2] - off[j0 + 1]; } else { rb = ra; nb2 = 0; }
+      const int o0 = off[j0], o1 = off[j0 + 1];
+      ga = ci + o0; na = o1 - o0;
+      if (j0 + 1 < p.nb) { gb = ci + o1; nb2 = off[j0 + 2] - o1; } else { gb = ga; nb2 = 0; }
     }
-    int a = 0, b = 0, n = 0;
-    const int full = (!KVS && BM == 128) ? 3 : 1;
-    while (a < na || b < nb2) {
-      int va = a < na ? ra[a] : 0x7fffffff;
-      int vb = b < nb2 ? rb[b] : 0x7fffffff;
-      if (va == vb) { ulist[n++] = va | (3 << 28); ++a; ++b; }
-      else if (va < vb) { ulist[n++] = va | (full << 28); ++a; }
-      else { ulist[n++] = vb | (2 << 28); ++b; }
+    int32_t* ra = ulist + p.max_entries;
+    int32_t* rb = ra + na;
+    for (int i = lane; i < na; i += 32) ra[i] = ga[i];
+    for (int i = lane; i < nb2; i += 32) rb[i] = gb[i];
+    __syncwarp();
+    if (lane == 0) {
+      int a = 0, b = 0, n = 0;
+      const int full = (!KVS && BM == 128) ? 3 : 1;
+      while (a < na || b < nb2) {
+        int va = a < na ? ra[a] : 0x7fffffff;
+        int vb = b < nb2 ? rb[b] : 0x7fffffff;
+        if (va == vb) { ulist[n++] = va | (3 << 28); ++a; ++b; }
+        else if (va < vb) { ulist[n++] = va | (full << 28); ++a; }
+        else { ulist[n++] = vb | (2 << 28); ++b; }
+      }
+      s_n_entries = n;
     }
-    s_n_entries = n;
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
@@ -153,6 +170,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   const uint32_t tmem = s_tmem_base;
   const int n_ent = s_n_entries * SL;            // streamed 64-row tiles
   volatile int* abortp = &s_abort;
+  long long* tr = (tile == 0 && bh == 0) ? p.trace : nullptr;
 
   // global row of the streamed tile j
   auto y_row0 = [&](int j) {
@@ -160,7 +178,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     return KVS ? e * BM + (j % SL) * 64 : e * 64;
   };
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0 && !*abortp) {
       mbar_expect_tx(BAR(B_X), 2 * X_BYTES);
@@ -173,6 +191,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         const int s = j % NS, use = j / NS;
         if (use > 0 && !mbar_wait(BAR(B_YE + s), (use - 1) & 1, kBErrYEmpty, p.err)) { *abortp = 1; break; }
         if (*abortp) break;
+        trace_ev(tr, 0, j, 0);
         const int row0 = y_row0(j);
         const uint32_t y1 = sY0 + s * 2 * Y_BYTES, y2 = y1 + Y_BYTES;
         mbar_expect_tx(BAR(B_YF + s), 2 * Y_BYTES + (KVS ? STAT_BYTES : 0));
@@ -190,25 +209,22 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         for (int j = max(0, issued - NS); j < issued; ++j) mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrDrain, p.err);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0 && !*abortp) {
+      const uint32_t x1_lo = desc_lo(sX1, 16), x2_lo = desc_lo(sX2, 16);
       auto issue_t = [&](int j) {
         const int s = j % NS, b = j & 1;
-        const uint32_t y1 = sY0 + s * 2 * Y_BYTES, y2 = y1 + Y_BYTES;
+        const uint32_t y1_lo = desc_lo(sY0 + s * 2 * Y_BYTES, 16), y2_lo = desc_lo(sY0 + s * 2 * Y_BYTES + Y_BYTES, 16);
         const uint32_t t1 = tmem + COL_T + b * 128, t2 = t1 + 64;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = kk >> 2, in = (kk & 3) * 32;
-          mma_ss(t1, smem_desc_sw128(sX1 + off * X_SLAB + in, 16, 1024), smem_desc_sw128(y1 + off * Y_SLAB + in, 16, 1024),
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss(t1, x1_lo + (((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4), y1_lo + (((kk >> 2) * Y_SLAB + (kk & 3) * 32) >> 4),
                  IDESC_T, kk > 0 ? 1u : 0u);
-        }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = kk >> 2, in = (kk & 3) * 32;
-          mma_ss(t2, smem_desc_sw128(sX2 + off * X_SLAB + in, 16, 1024), smem_desc_sw128(y2 + off * Y_SLAB + in, 16, 1024),
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss(t2, x2_lo + (((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4), y2_lo + (((kk >> 2) * Y_SLAB + (kk & 3) * 32) >> 4),
                  IDESC_T, kk > 0 ? 1u : 0u);
-        }
       };
       bool ok = mbar_wait(BAR(B_X), 0, kBErrX, p.err);
       for (int j = 0; ok && j < 2 && j < n_ent; ++j) {
@@ -220,24 +236,29 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       }
       for (int j = 0; ok && j < n_ent; ++j) {
         const int s = j % NS, b = j & 1;
+        trace_ev(tr, 1, j, 0);
         ok = mbar_wait(BAR(B_C + b), (j >> 1) & 1, kBErrCFull, p.err);
         if (!ok || *abortp) { ok = false; break; }
+        trace_ev(tr, 1, j, 1);
         tc_fence_after();
-        const uint32_t y1 = sY0 + s * 2 * Y_BYTES, y2 = y1 + Y_BYTES;
-        const uint32_t a1 = tmem + COL_T + b * 128, a2 = a1 + 64;   // 16-bit operands written by the compute group
+        // streamed tiles as MN-major B operands: 8-row groups 1024 B apart, 64-column slabs Y_SLAB apart
+        const uint32_t y1_lo = desc_lo(sY0 + s * 2 * Y_BYTES, Y_SLAB), y2_lo = desc_lo(sY0 + s * 2 * Y_BYTES + Y_BYTES, Y_SLAB);
+        const uint32_t a1 = tmem + COL_T + b * 128, a2 = a1 + 64;   // 16-bit operands written by the compute groups
+        const uint32_t acc_on = j > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
+          // 16-bit operand columns: elements [0,32) packed at +0..15, elements [32,64) at +32..47
+          const uint32_t ao = (kk >> 1) * 32 + (kk & 1) * 8;
+          const uint32_t ko = (kk * 2048) >> 4;
           if (KVS) {
-            mma_ts(tmem + COL_ACC2, a1 + kk * 8, smem_desc_sw128(y2 + kk * 2048, Y_SLAB, 1024), IDESC_ACC,
-                   (j > 0 || kk > 0) ? 1u : 0u);               // dV += P^T dO_i       (kernel.py:220)
-            mma_ts(tmem + COL_ACC1, a2 + kk * 8, smem_desc_sw128(y1 + kk * 2048, Y_SLAB, 1024), IDESC_ACC,
-                   (j > 0 || kk > 0) ? 1u : 0u);               // dK += dS^T Q_i       (kernel.py:225)
+            mma_ts(tmem + COL_ACC2, a1 + ao, y2_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dV += P^T dO_i  (kernel.py:220)
+            mma_ts(tmem + COL_ACC1, a2 + ao, y1_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dK += dS^T Q_i (kernel.py:225)
           } else {
-            mma_ts(tmem + COL_ACC1, a2 + kk * 8, smem_desc_sw128(y1 + kk * 2048, Y_SLAB, 1024), IDESC_ACC,
-                   (j > 0 || kk > 0) ? 1u : 0u);               // dQ += dS K_j         (kernel.py:163)
+            mma_ts(tmem + COL_ACC1, a2 + ao, y1_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dQ += dS K_j   (kernel.py:163)
           }
         }
         tc_commit(BAR(B_YE + s));
+        trace_ev(tr, 1, j, 2);
         if (j + 2 < n_ent) {
           ok = mbar_wait(BAR(B_YF + (j + 2) % NS), ((j + 2) / NS) & 1, kBErrYFull, p.err);
           if (!ok) break;
@@ -245,13 +266,15 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
           issue_t(j + 2);
           tc_commit(BAR(B_T + b));
         }
+        trace_ev(tr, 1, j, 3);
       }
       if (ok) tc_commit(BAR(B_ACC));
       if (!ok) *abortp = 1;
     }
   } else {
     // ------------------------------ compute groups ------------------------------
-    const int wg = warp >> 2;                               // 0 or 1
+    const int wg = warp >> 2;                               // 0..3
+    const int buf = wg & 1, ch = wg >> 1;                   // TMEM buffer, column half
     const int row = tid & 127;                              // tile row == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int half = row >> 6;
@@ -264,78 +287,80 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     }
     const bool key_ok = grow < L;                           // KVS: keys past the end give P = 0 (kernel.py:216)
     bool ok = !*abortp;
-    for (int j = wg; ok && j < n_ent; j += 2) {
-      if (!mbar_wait(BAR(B_T + wg), (j >> 1) & 1, kBErrTFull, p.err)) { ok = false; break; }
+    for (int j = buf; ok && j < n_ent; j += 2) {
+      long long* trc = ((warp & 3) == 0 && lane == 0) ? tr : nullptr;
+      trace_ev(trc, 2 + ch, j, 0);
+      if (!mbar_wait(BAR(B_T + buf), (j >> 1) & 1, kBErrTFull, p.err)) { ok = false; break; }
       if (*abortp) { ok = false; break; }
+      trace_ev(trc, 2 + ch, j, 1);
       if (KVS && !mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrYFull, p.err)) { ok = false; break; }  // row stats landed
       tc_fence_after();
       const int entry = ulist[j / SL];
       const bool active = (!KVS && BM == 128) || ((entry >> (28 + half)) & 1);
-      const uint32_t t1 = tmem + lane_addr + COL_T + wg * 128, t2 = t1 + 64;
+      const uint32_t t1 = tmem + lane_addr + COL_T + buf * 128 + ch * 32, t2 = t1 + 64;
       const int valid = KVS ? 64 : L - (entry & 0x0fffffff) * 64;   // dQ: keys of this block that exist
-      const float2* stc = stat_p + (j % NS) * 64;
+      const float4* stc = reinterpret_cast<const float4*>(stat_p + (j % NS) * 64 + ch * 32);
+      uint32_t pp[16], ds[16];
       if (active) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_x32(t1, sv);
+        tmem_ld_x32(t2, dv);
+        tmem_wait_ld();
+        trace_ev(trc, 2 + ch, j, 2);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t sv[32], dv[32];
-          tmem_ld_x32(t1 + h * 32, sv);
-          tmem_ld_x32(t2 + h * 32, dv);
-          tmem_wait_ld();
-          uint32_t pp[16], ds[16];
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            float pv[2], dsv[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int col = h * 32 + c + e;
-              float lse_c, del_c;
-              if (KVS) { float2 st = stc[col]; lse_c = st.x; del_c = st.y; } else { lse_c = my_lse; del_c = my_delta; }
-              float pe = ex2b(__uint_as_float(sv[c + e]) * sc - lse_c);
-              if (KVS ? !key_ok : (valid < 64 && col >= valid)) pe = 0.f;   // kernel.py:157 / :216
-              pv[e] = pe;
-              dsv[e] = pe * (__uint_as_float(dv[c + e]) - del_c);          // kernel.py:161 / :224
-            }
-            pp[c >> 1] = Elem<T>::pack2(pv[0], pv[1]);
-            ds[c >> 1] = Elem<T>::pack2(dsv[0], dsv[1]);
+        for (int c = 0; c < 32; c += 2) {
+          float lse0, del0, lse1, del1;
+          if (KVS) { float4 st = stc[c >> 1]; lse0 = st.x; del0 = st.y; lse1 = st.z; del1 = st.w; }
+          else { lse0 = lse1 = my_lse; del0 = del1 = my_delta; }
+          float p0 = ex2b(__uint_as_float(sv[c]) * sc - lse0);
+          float p1 = ex2b(__uint_as_float(sv[c + 1]) * sc - lse1);
+          if (KVS) { if (!key_ok) p0 = p1 = 0.f; }                         // kernel.py:216
+          else if (valid < 64) {                                            // kernel.py:157
+            if (ch * 32 + c >= valid) p0 = 0.f;
+            if (ch * 32 + c + 1 >= valid) p1 = 0.f;
           }
-          if (KVS) tmem_st_x16(t1 + h * 16, pp);
-          tmem_st_x16(t2 + h * 16, ds);
+          pp[c >> 1] = Elem<T>::pack2(p0, p1);
+          ds[c >> 1] = Elem<T>::pack2(p0 * (__uint_as_float(dv[c]) - del0),
+                                      p1 * (__uint_as_float(dv[c + 1]) - del1));   // kernel.py:161 / :224
         }
       } else {
-        uint32_t z[32];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) z[c] = 0u;
-        if (KVS) tmem_st_x32(t1, z);
-        tmem_st_x32(t2, z);
+        for (int c = 0; c < 16; ++c) pp[c] = ds[c] = 0u;
       }
+      if (KVS) tmem_st_x16(t1, pp);
+      tmem_st_x16(t2, ds);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(BAR(B_C + wg));
+      mbar_arrive(BAR(B_C + buf));
+      trace_ev(trc, 2 + ch, j, 3);
     }
     if (ok && n_ent > 0) ok = mbar_wait(BAR(B_ACC), 0, kBErrAcc, p.err);
     if (ok) ok = mbar_wait(BAR(B_X), 0, kBErrX, p.err);   // the stationary tiles (reused as staging) have landed
     if (!ok) *abortp = 1;
-    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    asm volatile("bar.sync 1, 512;\n" ::: "memory");
     if (!*abortp) {
       tc_fence_after();
       // accumulators -> T, staged over the (idle) stationary tiles in the swizzled slab layout, then
       // TMA stores; rows past the end of the sequence are clipped by the copy engine.
-      const int c_lo = KVS ? 0 : wg * (D / 2), c_hi = KVS ? D : (wg + 1) * (D / 2);
-      const uint32_t acc = tmem + lane_addr + (KVS && wg == 1 ? COL_ACC2 : COL_ACC1);
-      const uint32_t stage = (KVS && wg == 1) ? sX2 : sX1;
-      const float mul = (KVS && wg == 1) ? 1.0f : p.scale;   // dQ, dK carry the softmax scale (kernel.py:164,236)
-      for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
-        uint32_t ov[32];
+      // dQ: group g converts columns [g D/4, +D/4) of acc1. KVS: groups 0,1 halves of acc1 (dK), 2,3 of acc2 (dV).
+      const bool second = KVS && wg >= 2;
+      const int span = KVS ? D / 2 : D / 4;
+      const int c_lo = (KVS ? (wg & 1) : wg) * span, c_hi = c_lo + span;
+      const uint32_t acc = tmem + lane_addr + (second ? COL_ACC2 : COL_ACC1);
+      const uint32_t stage = second ? sX2 : sX1;
+      const float mul = second ? 1.0f : p.scale;   // dQ, dK carry the softmax scale (kernel.py:164,236)
+      for (int c0 = c_lo; c0 < c_hi; c0 += 16) {
+        uint32_t ov[16];
         if (n_ent > 0) {
-          tmem_ld_x32(acc + c0, ov);
+          tmem_ld_x16(acc + c0, ov);
           tmem_wait_ld();
         } else {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) ov[c] = 0u;          // nothing selected this tile: gradient is zero
+          for (int c = 0; c < 16; ++c) ov[c] = 0u;          // nothing selected this tile: gradient is zero
         }
         const uint32_t slab = stage + (c0 >> 6) * X_SLAB + row * 128;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+        for (int q4 = 0; q4 < 2; ++q4) {
           uint32_t w0 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 0]) * mul, __uint_as_float(ov[q4 * 8 + 1]) * mul);
           uint32_t w1 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 2]) * mul, __uint_as_float(ov[q4 * 8 + 3]) * mul);
           uint32_t w2 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 4]) * mul, __uint_as_float(ov[q4 * 8 + 5]) * mul);
@@ -347,7 +372,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         }
       }
       fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 256;\n" ::: "memory");
+      asm volatile("bar.sync 1, 512;\n" ::: "memory");
       if (tid == 0) {
         for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO1, sX1 + c * X_SLAB, c * 64, tile * 128, bh);
         if (KVS)
@@ -361,13 +386,17 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 17) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
 }
 
 }  // namespace tc
+
+// Diagnostic timeline buffer (2 x 1024 int64), set through sla_debug_set_trace.
+static long long* g_trace_buffer = nullptr;
+void set_trace_buffer(long long* p) { g_trace_buffer = p; }
 
 // delta = rowsum(o_s * dO) (kernel.py:102-105) and lse, interleaved into a padded (B*H, Lpad) array;
 // rows in [L, Lpad) get lse = +inf, delta = 0 so that they contribute P = 0.
@@ -417,16 +446,18 @@ static int launch_bwd_tc(const sla_shape* s, const BwdParams& bp, const float2* 
   p.stats = stats;
   p.err = tc_error_word();
   if (p.err == nullptr) return SLA_ERR_CUDA;
+  p.trace = g_trace_buffer ? g_trace_buffer + (KVS ? 1024 : 0) : nullptr;
   p.L = s->L; p.Lpad = Lpad; p.mb = bp.mb; p.nb = bp.nb; p.topk = bp.topk;
   p.scale = bp.scale; p.scale_log2 = bp.scale_log2;
   constexpr int NS = D == 128 ? 4 : 6;
   const int max_entries = KVS ? 2 * bp.mb : 2 * bp.topk;
-  const int smem = 1024 + 2 * 128 * D * 2 + NS * 2 * 64 * D * 2 + NS * 512 + max_entries * 4 + 16;
+  p.max_entries = max_entries;
+  const int smem = 1024 + 2 * 128 * D * 2 + NS * 2 * 64 * D * 2 + NS * 512 + 2 * max_entries * 4 + 16;
   if (smem > 227 * 1024) return SLA_ERR_BAD_SHAPE;
   auto kern = tc::sparse_bwd_tc_kernel<T, D, BM, KVS>;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int tiles = KVS ? ceil_div(bp.nb, 2) : ceil_div(s->L, 128);
-  kern<<<dim3(tiles, bh), 320, smem, st>>>(x1, x2, y1, y2, o1, o2, p);
+  kern<<<dim3(tiles, bh), 576, smem, st>>>(x1, x2, y1, y2, o1, o2, p);
   SLA_LAUNCH_OK();
   return SLA_OK;
 }

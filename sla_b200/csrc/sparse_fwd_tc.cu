@@ -66,7 +66,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   constexpr float kRescaleThreshold = 8.0f;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[12];
+  __shared__ __align__(8) uint64_t bars[14];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_n_entries;
   __shared__ int s_abort;
@@ -86,8 +86,8 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  // 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 kv_empty | 7,8 s_full | 9,10 p_full | 11 pv_done
-  constexpr int B_Q = 0, B_K = 1, B_V = 3, B_E = 5, B_S = 7, B_P = 9, B_PV = 11;
+  // 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 v_empty | 7,8 s_full | 9,10 p_full | 11 pv_done | 12,13 k_empty
+  constexpr int B_Q = 0, B_K = 1, B_V = 3, B_E = 5, B_S = 7, B_P = 9, B_PV = 11, B_KE = 12;
 
   if (tid == 0) {
     s_abort = *reinterpret_cast<volatile int*>(p.err) != 0;  // an earlier CTA failed: do no work
@@ -96,6 +96,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(BAR(B_K + s), 1);
       mbar_init(BAR(B_V + s), 1);
       mbar_init(BAR(B_E + s), 1);
+      mbar_init(BAR(B_KE + s), 1);
       mbar_init(BAR(B_S + s), 1);
       mbar_init(BAR(B_P + s), 128);
     }
@@ -103,30 +104,39 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     fence_barrier_init();
     fence_proxy_async_smem();
   }
-  if (warp == 4 && lane == 0) {
-    prefetch_tmap(&tmQ);
-    prefetch_tmap(&tmK);
-    prefetch_tmap(&tmV);
-    prefetch_tmap(&tmO);
-    // entry list: block index | bit 28 (upper half of the tile selects it) | bit 29 (lower half)
-    if (BM == 128) {
-      const int32_t* row = p.lut + (static_cast<size_t>(bh) * p.mb + tile) * p.topk;
-      for (int i = 0; i < p.topk; ++i) ulist[i] = row[i] | (3 << 28);
-      s_n_entries = p.topk;
-    } else {
-      const int ia = 2 * tile, ib = 2 * tile + 1;
-      const int32_t* ra = p.lut + (static_cast<size_t>(bh) * p.mb + ia) * p.topk;
-      const int32_t* rb = ra + p.topk;
-      const int nbv = ib < p.mb ? p.topk : 0;
-      int a = 0, b = 0, n = 0;
-      while (a < p.topk || b < nbv) {
-        int va = a < p.topk ? ra[a] : 0x7fffffff;
-        int vb = b < nbv ? rb[b] : 0x7fffffff;
-        if (va == vb) { ulist[n++] = va | (3 << 28); ++a; ++b; }
-        else if (va < vb) { ulist[n++] = va | (1 << 28); ++a; }
-        else { ulist[n++] = vb | (2 << 28); ++b; }
+  if (warp == 4) {
+    if (lane == 0) {
+      prefetch_tmap(&tmQ);
+      prefetch_tmap(&tmK);
+      prefetch_tmap(&tmV);
+      prefetch_tmap(&tmO);
+    }
+    // Entry list: block index | bit 28 (upper half of the tile selects it) | bit 29 (lower half).
+    // The LUT rows are first copied to shared memory with coalesced loads; a serial merge straight
+    // from global memory would cost one DRAM/L2 round trip per element.
+    int32_t* raw = ulist + 2 * p.topk;
+    const int rows = BM == 128 ? 1 : ((2 * tile + 1 < p.mb) ? 2 : 1);
+    const int32_t* src = p.lut + (static_cast<size_t>(bh) * p.mb + (BM == 128 ? tile : 2 * tile)) * p.topk;
+    for (int i = lane; i < rows * p.topk; i += 32) raw[i] = src[i];
+    __syncwarp();
+    if (lane == 0) {
+      if (BM == 128) {
+        for (int i = 0; i < p.topk; ++i) ulist[i] = raw[i] | (3 << 28);
+        s_n_entries = p.topk;
+      } else {
+        const int32_t* ra = raw;
+        const int32_t* rb = raw + p.topk;
+        const int nbv = rows == 2 ? p.topk : 0;
+        int a = 0, b = 0, n = 0;
+        while (a < p.topk || b < nbv) {
+          int va = a < p.topk ? ra[a] : 0x7fffffff;
+          int vb = b < nbv ? rb[b] : 0x7fffffff;
+          if (va == vb) { ulist[n++] = va | (3 << 28); ++a; ++b; }
+          else if (va < vb) { ulist[n++] = va | (1 << 28); ++a; }
+          else { ulist[n++] = vb | (2 << 28); ++b; }
+        }
+        s_n_entries = n;
       }
-      s_n_entries = n;
     }
   }
   if (warp == 5) {
@@ -145,39 +155,49 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (lane == 0 && !*abortp) {
       mbar_expect_tx(BAR(B_Q), Q_BYTES);
       for (int c = 0; c < SLABS; ++c) tma_load_3d(sQ + c * Q_SLAB, &tmQ, BAR(B_Q), c * 64, tile * 128, bh);
-      int issued = 0;
-      for (int j = 0; j < n_ent; ++j) {
-        const int s = j & 1;
-        if (j >= 2 && !mbar_wait(BAR(B_E + s), ((j >> 1) - 1) & 1, kErrEmpty, p.err)) { *abortp = 1; break; }
-        if (*abortp) break;
-        const int row0 = (ulist[j] & 0x0fffffff) * 64;
-        mbar_expect_tx(BAR(B_K + s), KV_BYTES);
-        for (int c = 0; c < SLABS; ++c) tma_load_3d(sK0 + s * KV_BYTES + c * KV_SLAB, &tmK, BAR(B_K + s), c * 64, row0, bh);
-        mbar_expect_tx(BAR(B_V + s), KV_BYTES);
-        for (int c = 0; c < SLABS; ++c) tma_load_3d(sV0 + s * KV_BYTES + c * KV_SLAB, &tmV, BAR(B_V + s), c * 64, row0, bh);
-        issued = j + 1;
+      // K tiles run one entry ahead of V tiles: a K stage is free as soon as S_j has been computed,
+      // a V stage only after P_j V_j.
+      int issued_k = 0, issued_v = 0;
+      for (int t = 0; t <= n_ent; ++t) {
+        if (t < n_ent) {
+          const int s = t & 1;
+          if (t >= 2 && !mbar_wait(BAR(B_KE + s), ((t >> 1) - 1) & 1, kErrEmpty, p.err)) { *abortp = 1; break; }
+          if (*abortp) break;
+          const int row0 = (ulist[t] & 0x0fffffff) * 64;
+          mbar_expect_tx(BAR(B_K + s), KV_BYTES);
+          for (int c = 0; c < SLABS; ++c) tma_load_3d(sK0 + s * KV_BYTES + c * KV_SLAB, &tmK, BAR(B_K + s), c * 64, row0, bh);
+          issued_k = t + 1;
+        }
+        if (t >= 1) {
+          const int j = t - 1, s = j & 1;
+          if (j >= 2 && !mbar_wait(BAR(B_E + s), ((j >> 1) - 1) & 1, kErrEmpty, p.err)) { *abortp = 1; break; }
+          if (*abortp) break;
+          const int row0 = (ulist[j] & 0x0fffffff) * 64;
+          mbar_expect_tx(BAR(B_V + s), KV_BYTES);
+          for (int c = 0; c < SLABS; ++c) tma_load_3d(sV0 + s * KV_BYTES + c * KV_SLAB, &tmV, BAR(B_V + s), c * 64, row0, bh);
+          issued_v = j + 1;
+        }
       }
       if (*abortp) {
         // let the copies already in flight land before the CTA's shared memory goes away
         mbar_wait(BAR(B_Q), 0, kErrDrain, p.err);
-        for (int j = max(0, issued - 2); j < issued; ++j) {
-          mbar_wait(BAR(B_K + (j & 1)), (j >> 1) & 1, kErrDrain, p.err);
-          mbar_wait(BAR(B_V + (j & 1)), (j >> 1) & 1, kErrDrain, p.err);
-        }
+        for (int j = max(0, issued_k - 2); j < issued_k; ++j) mbar_wait(BAR(B_K + (j & 1)), (j >> 1) & 1, kErrDrain, p.err);
+        for (int j = max(0, issued_v - 2); j < issued_v; ++j) mbar_wait(BAR(B_V + (j & 1)), (j >> 1) & 1, kErrDrain, p.err);
       }
     }
   } else if (warp == 5) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0 && !*abortp) {
+      const uint32_t q_lo = desc_lo(sQ, 16);
       auto issue_s = [&](int j) {
-        const uint32_t kb = sK0 + (j & 1) * KV_BYTES;
+        const uint32_t k_lo = desc_lo(sK0 + (j & 1) * KV_BYTES, 16);
         const uint32_t d = tmem + COL_S + (j & 1) * 64;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) , in = (kk & 3) * 32;
-          uint64_t da = smem_desc_sw128(sQ + off * Q_SLAB + in, 16, 1024);
-          uint64_t db = smem_desc_sw128(kb + off * KV_SLAB + in, 16, 1024);
-          mma_ss(d, da, db, IDESC_S, kk > 0 ? 1u : 0u);
+          // k-step kk: 32 bytes further inside the 128-byte swizzle atom, next slab every 4 steps
+          constexpr int dummy = 0; (void)dummy;
+          mma_ss(d, q_lo + (((kk >> 2) * Q_SLAB + (kk & 3) * 32) >> 4), k_lo + (((kk >> 2) * KV_SLAB + (kk & 3) * 32) >> 4),
+                 IDESC_S, kk > 0 ? 1u : 0u);
         }
       };
       bool ok = mbar_wait(BAR(B_Q), 0, kErrQ, p.err) && mbar_wait(BAR(B_K), 0, kErrKFull, p.err);
@@ -185,6 +205,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tc_fence_after();
         issue_s(0);
         tc_commit(BAR(B_S));
+        tc_commit(BAR(B_KE));
       }
       for (int j = 0; ok && j < n_ent; ++j) {
         if (j + 1 < n_ent) {
@@ -193,19 +214,18 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tc_fence_after();
           issue_s(j + 1);
           tc_commit(BAR(B_S + ((j + 1) & 1)));
+          tc_commit(BAR(B_KE + ((j + 1) & 1)));
         }
         ok = mbar_wait(BAR(B_P + (j & 1)), (j >> 1) & 1, kErrPFull, p.err) &&
              mbar_wait(BAR(B_V + (j & 1)), (j >> 1) & 1, kErrVFull, p.err);
         if (!ok || *abortp) { ok = false; break; }
         tc_fence_after();
-        const uint32_t vb = sV0 + (j & 1) * KV_BYTES;
+        // B = V_j rows [16 kk, +16): MN-major, 8-row groups 1024 B apart, 64-column slabs KV_SLAB apart
+        const uint32_t v_lo = desc_lo(sV0 + (j & 1) * KV_BYTES, KV_SLAB);
         const uint32_t pa = tmem + COL_S + (j & 1) * 64;   // P_j: 16-bit pairs packed over S_j
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          // B = V_j rows [16 kk, +16): MN-major, 8-row groups 1024 B apart, 64-column slabs KV_SLAB apart
-          uint64_t db = smem_desc_sw128(vb + kk * 2048, KV_SLAB, 1024);
-          mma_ts(tmem + COL_O, pa + kk * 8, db, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < 4; ++kk)
+          mma_ts(tmem + COL_O, pa + kk * 8, v_lo + ((kk * 2048) >> 4), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(BAR(B_E + (j & 1)));
         tc_commit(BAR(B_PV));
       }
@@ -405,7 +425,7 @@ static int launch_tc(const sla_shape* s, const FwdParams& fp, cudaStream_t st) {
   p.scale_log2 = fp.scale_log2;
   auto kern = tc::sparse_fwd_tc_kernel<T, D, BM>;
   const int tiles_bytes = 128 * D * 2 + 4 * 64 * D * 2;
-  const int smem = 1024 + tiles_bytes + 2 * fp.topk * 4 + 16;
+  const int smem = 1024 + tiles_bytes + 4 * fp.topk * 4 + 16;
   if (smem > 113 * 1024) return SLA_ERR_BAD_TOPK;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   kern<<<dim3(p.n_tiles, bh), 192, smem, st>>>(tq, tk, tv, to, p);
