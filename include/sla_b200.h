@@ -13,7 +13,8 @@
  *   sparse_map                      : (B, H, M_BLOCKS, N_BLOCKS) int8 0/1
  *   col_offsets                     : (B, H, N_BLOCKS + 1) int32   } per-KV-block list of the
  *   col_index                       : (B, H, M_BLOCKS * topk) int32 } query blocks that selected it
- *   lin_state                       : (B, H, D*D + D)  16-bit: H = phi(k)^T v then z = sum phi(k)
+ *   lin_state                       : (B, H, 2*D*D + D) 16-bit: H = phi(k)^T v, z = sum phi(k), then H W^T
+ *                                     (sla_linear_state fills H and z; sla_fwd also the last part)
  *   w, bias                         : (D, D), (D)      fp32 (nn.Linear parameters of proj_l)
  * with M_BLOCKS = ceil(L / BLKQ), N_BLOCKS = ceil(L / BLKK).
  *

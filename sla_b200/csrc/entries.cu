@@ -90,6 +90,8 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   if (rc != SLA_OK) return rc;
   rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wl.partial), wl.nch, wl.rows, st);
   if (rc != SLA_OK) return rc;
+  rc = run_state_proj(s, lin_state, wbits, st);
+  if (rc != SLA_OK) return rc;
   FwdParams p = make_fwd(s, q, k, v, lut, o, o_s, lse, lin_state, wbits);
   if (legacy) return run_sparse_fwd_mma(s, p, true, st);
   // tcgen05 sparse branch into o_s (or into o when the caller keeps no copy), then the streaming
@@ -156,6 +158,7 @@ int sla_bwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   LinBwdParams lp;
   lp.q = q; lp.k = k; lp.v = v; lp.d_o = d_o; lp.lin_state = lin_state; lp.wbits = base + wb.wbits; lp.w = w;
   lp.dq = dq; lp.dk = dk; lp.dv = dv;
+  lp.g_sum = reinterpret_cast<float*>(base + wb.g_sum);
   lp.g_partial = reinterpret_cast<float*>(base + wb.g_partial);
   lp.dh = base + wb.dh;
   lp.dz = reinterpret_cast<float*>(base + wb.dz);

@@ -13,7 +13,7 @@ struct FwdParams {
   void* o;                // final output (or o_s when the linear branch is skipped)
   void* o_s;              // optional copy of the sparse branch output (needed by the backward)
   float* lse;
-  const void* lin_state;  // [BH][D*D + D] 16-bit: H then z
+  const void* lin_state;  // [BH][2*D*D + D] 16-bit: H, z, then H W^T
   const void* wbits;      // [D*D + D] 16-bit: W then bias
   int L, mb, topk;
   float scale_log2;       // softmax scale * log2(e)
@@ -39,6 +39,7 @@ struct LinBwdParams {
   const float* w;         // W fp32
   void *dq, *dk, *dv;     // written (not accumulated) with the linear branch's gradients
   float* g_partial;       // [BH][NCH][D*D + 2D]
+  float* g_sum;           // [BH][D*D + 2D]
   void* dh;               // [BH][D*D] 16-bit
   float* dz;              // [BH][D]
   float* dw_part;         // [BH][D*D + D]
@@ -51,6 +52,7 @@ int convert_proj(const sla_shape* s, const float* w, const float* bias, void* ou
 int run_sparse_fwd_mma(const sla_shape* s, const FwdParams& p, bool lin, cudaStream_t st);
 int run_sparse_fwd_tc(const sla_shape* s, const FwdParams& p, cudaStream_t st);
 int run_linear_readout(const sla_shape* s, const FwdParams& p, cudaStream_t st);
+int run_state_proj(const sla_shape* s, void* lin_state, const void* wbits, cudaStream_t st);
 int read_tc_error(int* out, bool clear);
 void set_trace_buffer(long long* p);
 int run_sparse_bwd_tc(const sla_shape* s, const BwdParams& p, void* stats, cudaStream_t st);

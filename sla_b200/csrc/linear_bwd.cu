@@ -1,28 +1,30 @@
 // Backward of the linear branch and of proj_l (the reference leaves this to PyTorch autograd of
-// sparse_linear_attention/core.py:90-100). With dY the gradient of the module output:
-//   do_l = dY W                      dnum = do_l / den          dden = -sum_d(do_l * o_l) / den
-//   dphi_q = dnum H^T + dden z       dq_lin = phi'(q) dphi_q
-//   G = sum_l dY_l^T (phi_q,l / den_l)                       (one D x D reduction per head)
+// sparse_linear_attention/core.py:90-100). With dY the gradient of the module output, o_l = phi_q H / den,
+// den = 1e-5 + phi_q . z and proj = o_l W^T + b:
+//   do_l = dY W,  t = do_l H^T = dY (W H^T) =: dY M            (M^T = H W^T is kept by the forward)
+//   dphi_q = t / den + dden z,   dden = -(do_l . o_l) / den = -(phi_q . t) / den^2
+//   dq_lin = phi'(q) dphi_q
+//   G = sum_l dY_l^T (phi_q,l / den_l)                          (one D x D reduction per head)
 //   dH = G^T W,  dW = sum_heads G H,  dz = sum_l dden_l phi_q,l,  db = sum_l dY_l
-//   dphi_k = v dH^T + dz             dk_lin = phi'(k) dphi_k    dv_lin = phi_k dH
-// Pass A (per query rows) writes dq_lin and per-chunk partials of G, dz, db; a per-head reduction
-// turns them into dH, dz and the head's share of dW, db; pass B (per key rows) writes dk_lin, dv_lin.
+//   dphi_k = v dH^T + dz,  dk_lin = phi'(k) dphi_k,  dv_lin = phi_k dH
+// Folding W into M and using phi_q . t for dden leaves two GEMMs per row tile in pass A (t and G)
+// and two in pass B. Pass A writes dq_lin and per-chunk partials of G, dz, db; small per-head kernels
+// turn them into dH, dz and the head's share of dW, db; pass B writes dk_lin, dv_lin.
 #include "common.cuh"
 #include "kernels.h"
 
 namespace sla {
 
 // ---------------------------------------------------------------------------------------------
-// Pass A
+// Pass A: D query rows per tile, one warp per 16 rows.
 // ---------------------------------------------------------------------------------------------
 template <typename T, int D, int FEAT>
 __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams p) {
   constexpr int NW = D / 16, NT = NW * 32, KS = D / 16;
   constexpr int TILE = D * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* sH = smem;
-  unsigned char* sW = sH + TILE;
-  unsigned char* sQ = sW + TILE;    // Q rows, then dq staging, then phi(q)/den
+  unsigned char* sM = smem;         // H W^T = M^T, stored [i][n]
+  unsigned char* sQ = sM + TILE;    // Q rows, then dq staging, then phi(q)/den
   unsigned char* sdY = sQ + TILE;
   float* s_z = reinterpret_cast<float*>(sdY + TILE);  // [D]
   float* s_rowc = s_z + D;                            // [D] dden*den per row of the tile
@@ -35,13 +37,12 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams 
   const T* qg = static_cast<const T*>(p.q) + head_off;
   const T* dyg = static_cast<const T*>(p.d_o) + head_off;
   T* dqg = static_cast<T*>(p.dq) + head_off;
-  const T* hs = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (D * D + D);
-  const T* wb = static_cast<const T*>(p.wbits);
-  const uint32_t sH_a = smem_u32(sH), sW_a = smem_u32(sW), sQ_a = smem_u32(sQ), sdY_a = smem_u32(sdY);
+  const T* hs = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (2 * D * D + D);
+  const T* mg = hs + D * D + D;
+  const uint32_t sM_a = smem_u32(sM), sQ_a = smem_u32(sQ), sdY_a = smem_u32(sdY);
   const int m0 = warp * 16;
 
-  load_tile_async<D, D>(sH_a, hs, 0, D, tid, NT);
-  load_tile_async<D, D>(sW_a, wb, 0, D, tid, NT);
+  load_tile_async<D, D>(sM_a, mg, 0, D, tid, NT);
   cp_async_commit();
   for (int i = tid; i < D; i += NT) s_z[i] = Elem<T>::to_f(hs[D * D + i]);
 
@@ -64,10 +65,7 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams 
       load_a_frags<D, KS>(qf, sQ_a, m0, 0, lane);
       feature_map_frags<T, KS, FEAT>(pq, qf);
     }
-    float acc[D / 8][4];
-#pragma unroll
-    for (int j = 0; j < D / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    gemm_b_kn<T, D, D / 8, KS>(acc, pq, sH_a, 0, 0, lane);  // num = phi(q) H
+    // den = 1e-5 + sum_d round(phi(q)*ksum) (core.py:95), each step rounded to T as in the forward
     float d0 = 0.f, d1 = 0.f;
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
@@ -82,40 +80,29 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams 
     d0 = round_to<T>(1e-5f + round_to<T>(quad_sum(d0)));
     d1 = round_to<T>(1e-5f + round_to<T>(quad_sum(d1)));
     const float rd0 = 1.f / d0, rd1 = 1.f / d1;
-    uint32_t ol[KS][4];  // o_l = num / den in T
-#pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-      acc[j][0] = round_to<T>(acc[j][0]) * rd0;
-      acc[j][1] = round_to<T>(acc[j][1]) * rd0;
-      acc[j][2] = round_to<T>(acc[j][2]) * rd1;
-      acc[j][3] = round_to<T>(acc[j][3]) * rd1;
-    }
-    acc_to_a_frags<T, KS>(ol, acc);
+
+    float acc[D / 8][4];
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    gemm_at_b_kn<T, D, D / 8, KS>(acc, sdY_a, m0, sW_a, lane);  // do_l = dY W
-    float dd0 = 0.f, dd1 = 0.f;
+    gemm_at_b_nk<T, D, D / 8, KS>(acc, sdY_a, m0, sM_a, lane);  // t[m][i] = sum_n dY[m][n] HW[i][n]
+    // s = phi_q . t per row
+    float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int kk = 0; kk < KS; ++kk) {
-      float2 o0 = Elem<T>::unpack2(ol[kk][0]), o1 = Elem<T>::unpack2(ol[kk][1]);
-      float2 o2 = Elem<T>::unpack2(ol[kk][2]), o3 = Elem<T>::unpack2(ol[kk][3]);
-      dd0 += acc[2 * kk][0] * o0.x + acc[2 * kk][1] * o0.y + acc[2 * kk + 1][0] * o2.x + acc[2 * kk + 1][1] * o2.y;
-      dd1 += acc[2 * kk][2] * o1.x + acc[2 * kk][3] * o1.y + acc[2 * kk + 1][2] * o3.x + acc[2 * kk + 1][3] * o3.y;
+      float2 p0 = Elem<T>::unpack2(pq[kk][0]), p1 = Elem<T>::unpack2(pq[kk][1]);
+      float2 p2 = Elem<T>::unpack2(pq[kk][2]), p3 = Elem<T>::unpack2(pq[kk][3]);
+      s0 += acc[2 * kk][0] * p0.x + acc[2 * kk][1] * p0.y + acc[2 * kk + 1][0] * p2.x + acc[2 * kk + 1][1] * p2.y;
+      s1 += acc[2 * kk][2] * p1.x + acc[2 * kk][3] * p1.y + acc[2 * kk + 1][2] * p3.x + acc[2 * kk + 1][3] * p3.y;
     }
-    const float dden0 = -quad_sum(dd0) * rd0, dden1 = -quad_sum(dd1) * rd1;
-#pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
-      acc[j][0] *= rd0; acc[j][1] *= rd0; acc[j][2] *= rd1; acc[j][3] *= rd1;  // dnum
-    }
-    uint32_t dn[KS][4];
-    acc_to_a_frags<T, KS>(dn, acc);
+    const float dden0 = -quad_sum(s0) * rd0 * rd0, dden1 = -quad_sum(s1) * rd1 * rd1;
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) {
       int col = 8 * j + 2 * t;
-      acc[j][0] = dden0 * s_z[col]; acc[j][1] = dden0 * s_z[col + 1];
-      acc[j][2] = dden1 * s_z[col]; acc[j][3] = dden1 * s_z[col + 1];
+      acc[j][0] = acc[j][0] * rd0 + dden0 * s_z[col];
+      acc[j][1] = acc[j][1] * rd0 + dden0 * s_z[col + 1];
+      acc[j][2] = acc[j][2] * rd1 + dden1 * s_z[col];
+      acc[j][3] = acc[j][3] * rd1 + dden1 * s_z[col + 1];
     }
-    gemm_b_nk<T, D, D / 8, KS>(acc, dn, sH_a, 0, 0, lane);  // dphi_q = dnum H^T + dden z
     feature_map_bwd_frags<T, KS, FEAT>(acc, pq);
     // dq_lin: stage in this warp's rows of the Q tile (its fragments are no longer needed) and flush
     store_acc_to_tile<T, D, D / 8>(sQ, acc, m0, lane);
@@ -170,40 +157,75 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Per-head reduction: G -> dH (T), dz, and the head's dW, db.
+// Per-head reductions. (1) sum the chunk partials; (2) G -> dH (T), and the head's dW; dz, db copied.
 // ---------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(1024) linear_bwd_reduce_kernel(LinBwdParams p, int D) {
-  extern __shared__ __align__(16) float sG[];  // [D][D]
-  const int bh = blockIdx.x, tid = threadIdx.x;
-  const int dd = D * D, n = dd + 2 * D;
-  const float* part = p.g_partial + static_cast<size_t>(bh) * p.nch * n;
-  for (int i = tid; i < dd; i += 1024) {
-    float s = 0.f;
-    for (int c = 0; c < p.nch; ++c) s += part[static_cast<size_t>(c) * n + i];
-    sG[i] = s;
-  }
-  float* dwp = p.dw_part + static_cast<size_t>(bh) * (dd + D);
-  for (int i = tid; i < 2 * D; i += 1024) {
-    float s = 0.f;
-    for (int c = 0; c < p.nch; ++c) s += part[static_cast<size_t>(c) * n + dd + i];
-    if (i < D) p.dz[static_cast<size_t>(bh) * D + i] = s;
-    else dwp[dd + i - D] = s;
-  }
-  __syncthreads();
-  const T* hs = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (dd + D);
+__global__ void __launch_bounds__(256) linear_bwd_gsum_kernel(const float* __restrict__ part,
+                                                              float* __restrict__ gsum, int nch, int n) {
+  const int bh = blockIdx.y;
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const float* p = part + static_cast<size_t>(bh) * nch * n + i;
+  float s = 0.f;
+  for (int c = 0; c < nch; ++c) s += p[static_cast<size_t>(c) * n];
+  gsum[static_cast<size_t>(bh) * n + i] = s;
+}
+
+// One CTA per head, one warp per 16 output rows, both products on the tensor cores with G rounded to T:
+//   dH[i][j] = sum_n G[n][i] W[n][j]      dW_head[n][k] = sum_i G[n][i] H[i][k]
+template <typename T, int D>
+__global__ void __launch_bounds__(D / 16 * 32) linear_bwd_reduce_kernel(LinBwdParams p) {
+  constexpr int NT = D / 16 * 32, KS = D / 16, dd = D * D, n = dd + 2 * D;
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* sG = smem;              // [n][i] T
+  unsigned char* sW = sG + dd * 2;       // [n][j] T
+  unsigned char* sH = sW + dd * 2;       // [i][k] T
+  const int bh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const float* G = p.g_sum + static_cast<size_t>(bh) * n;
+  const T* hs = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (2 * dd + D);
   T* dh = static_cast<T*>(p.dh) + static_cast<size_t>(bh) * dd;
-  for (int o = tid; o < dd; o += 1024) {
-    int a = o / D, b = o % D;
-    // dH[i=a][j=b] = sum_n G[n][a] W[n][b]
-    float s = 0.f;
-    for (int nn = 0; nn < D; ++nn) s = fmaf(sG[nn * D + a], p.w[nn * D + b], s);
-    dh[o] = Elem<T>::from_f(s);
-    // dW_head[n=a][k=b] = sum_i G[a][i] H[i][b]
-    float u = 0.f;
-    for (int i = 0; i < D; ++i) u = fmaf(sG[a * D + i], Elem<T>::to_f(hs[i * D + b]), u);
-    dwp[o] = u;
+  float* dwp = p.dw_part + static_cast<size_t>(bh) * (dd + D);
+  const uint32_t sG_a = smem_u32(sG), sW_a = smem_u32(sW), sH_a = smem_u32(sH);
+  load_tile_async<D, D>(sW_a, p.wbits, 0, D, tid, NT);
+  load_tile_async<D, D>(sH_a, hs, 0, D, tid, NT);
+  cp_async_commit();
+  for (int c = tid; c < dd / 8; c += NT) {   // 8 consecutive fp32 -> one 16-byte chunk of T
+    const int r = c / (D / 8), ch = c % (D / 8);
+    const float4 a = *reinterpret_cast<const float4*>(G + r * D + ch * 8);
+    const float4 b = *reinterpret_cast<const float4*>(G + r * D + ch * 8 + 4);
+    uint4 v;
+    v.x = Elem<T>::pack2(a.x, a.y); v.y = Elem<T>::pack2(a.z, a.w);
+    v.z = Elem<T>::pack2(b.x, b.y); v.w = Elem<T>::pack2(b.z, b.w);
+    *reinterpret_cast<uint4*>(sG + tile_off<D>(r, ch)) = v;
   }
+  for (int i = tid; i < 2 * D; i += NT) {
+    if (i < D) p.dz[static_cast<size_t>(bh) * D + i] = G[dd + i];
+    else dwp[dd + i - D] = G[dd + i];
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  const int m0 = warp * 16;
+  float acc[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  gemm_atrans_b_kn<T, D, D / 8, KS>(acc, sG_a, m0, sW_a, lane);   // rows i of dH
+  float acc2[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) acc2[j][0] = acc2[j][1] = acc2[j][2] = acc2[j][3] = 0.f;
+  {
+    uint32_t a[KS][4];
+    load_a_frags<D, KS>(a, sG_a, m0, 0, lane);
+    gemm_b_kn<T, D, D / 8, KS>(acc2, a, sH_a, 0, 0, lane);         // rows n of dW_head
+  }
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) {
+    const int r0 = m0 + g, c = 8 * j + 2 * t;
+    *reinterpret_cast<float2*>(dwp + r0 * D + c) = make_float2(acc2[j][0], acc2[j][1]);
+    *reinterpret_cast<float2*>(dwp + (r0 + 8) * D + c) = make_float2(acc2[j][2], acc2[j][3]);
+  }
+  __syncthreads();   // all warps are done reading W: reuse it as the staging tile for dH
+  store_acc_to_tile<T, D, D / 8>(sW, acc, m0, lane);
+  flush16<T, D>(sW, m0, dh, m0, D, lane, false);
 }
 
 __global__ void dw_final_kernel(const float* __restrict__ dw_part, float* __restrict__ dw,
@@ -273,16 +295,18 @@ static int launch_lin_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_
   const int bh = s->B * s->H, dd = D * D;
   {
     auto kern = linear_bwd_q_kernel<T, D, FEAT>;
-    int smem = 4 * dd * 2 + 2 * D * 4;
+    int smem = 3 * dd * 2 + 2 * D * 4;
     SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     kern<<<dim3(p.nch, bh), D / 16 * 32, smem, st>>>(p);
     SLA_LAUNCH_OK();
   }
   {
-    auto kern = linear_bwd_reduce_kernel<T>;
-    int smem = dd * 4;
-    SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<bh, 1024, smem, st>>>(p, D);
+    const int n = dd + 2 * D;
+    linear_bwd_gsum_kernel<<<dim3(ceil_div(n, 256), bh), 256, 0, st>>>(p.g_partial, p.g_sum, p.nch, n);
+    SLA_LAUNCH_OK();
+    auto rk = linear_bwd_reduce_kernel<T, D>;
+    SLA_CUDA_OK(cudaFuncSetAttribute(rk, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * dd * 2));
+    rk<<<bh, D / 16 * 32, 3 * dd * 2, st>>>(p);
     SLA_LAUNCH_OK();
     dw_final_kernel<<<ceil_div(dd + D, 256), 256, 0, st>>>(p.dw_part, p.dw, p.dbias, bh, dd, D);
     SLA_LAUNCH_OK();

@@ -134,16 +134,17 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_state_kernel(const T* __re
   linear_state_chunk<T, D, FEAT>(k, v, partial, L, nch, rows, smem);
 }
 
+// n = D*D + D values per head; the head's record is rec_stride elements long (H, z, then room for H W^T)
 template <typename T>
 __global__ void linear_state_reduce_kernel(const float* __restrict__ partial, T* __restrict__ state, int nch,
-                                           int n) {
+                                           int n, int rec_stride) {
   int bh = blockIdx.y;
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float* p = partial + static_cast<size_t>(bh) * nch * n + i;
   float s = 0.f;
   for (int c = 0; c < nch; ++c) s += p[static_cast<size_t>(c) * n];
-  state[static_cast<size_t>(bh) * n + i] = Elem<T>::from_f(s);
+  state[static_cast<size_t>(bh) * rec_stride + i] = Elem<T>::from_f(s);
 }
 
 template <typename T, int D>
@@ -164,7 +165,7 @@ static int launch_state(const sla_shape* s, const T* k, const T* v, T* state, fl
   }
   SLA_LAUNCH_OK();
   int n = D * D + D;
-  linear_state_reduce_kernel<T><<<dim3(ceil_div(n, 256), bh), 256, 0, st>>>(partial, state, nch, n);
+  linear_state_reduce_kernel<T><<<dim3(ceil_div(n, 256), bh), 256, 0, st>>>(partial, state, nch, n, 2 * D * D + D);
   SLA_LAUNCH_OK();
   return SLA_OK;
 }

@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(BM / 16 * 32) sparse_fwd_mma_kernel(FwdParams 
       os_pk[j][1] = Elem<T>::pack2(o_acc[j][2], o_acc[j][3]);
     }
     // stage H (D x D, [i][j]) over the K ring and W ([n][k], 16-bit) over the V ring
-    const T* hs = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (D * D + D);
+    const T* hs = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (2 * D * D + D);
     const T* wb = static_cast<const T*>(p.wbits);
     static_assert(2 * TILE_KV >= D * D * 2, "state tile must fit in the K/V ring");
     load_tile_async<D, D>(sK_a, hs, 0, D, tid, NT);

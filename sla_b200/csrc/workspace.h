@@ -56,7 +56,7 @@ inline WsLinearState ws_linear_state(const sla_shape* s) {
   return w;
 }
 
-// extra bytes the fused forward needs after the linear-state workspace: proj weight in 16 bit
+// extra bytes the fused forward needs after the linear-state workspace: proj weight + bias in 16 bit
 inline size_t ws_fwd_extra(const sla_shape* s) { return ws_round(size_t(s->D) * s->D * 2 + s->D * 2); }
 
 // ---- backward ----
@@ -66,6 +66,7 @@ struct WsBwd {
   size_t dh;        // 16-bit [BH][D*D] dH, then fp32 [BH][D] dz
   size_t dz;
   size_t dw_part;   // fp32 [BH][D*D + D] per-head dW and db
+  size_t g_sum;     // fp32 [BH][D*D + 2*D]
   size_t total;
   int nch, rows;
 };
@@ -84,6 +85,7 @@ inline WsBwd ws_bwd(const sla_shape* s) {
   w.dh = o;        o += ws_round(bh * dd * 2);
   w.dz = o;        o += ws_round(bh * s->D * 4);
   w.dw_part = o;   o += ws_round(bh * (dd + s->D) * 4);
+  w.g_sum = o;     o += ws_round(bh * (dd + 2 * s->D) * 4);
   w.total = o;
   return w;
 }

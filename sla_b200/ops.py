@@ -157,7 +157,7 @@ class _SLAFused(torch.autograd.Function):
         o = torch.empty_like(q)
         o_s = torch.empty_like(q) if need_grad else None
         lse = torch.empty((B, H, L), dtype=torch.float32, device=dev)
-        lin_state = torch.empty((B, H, D * D + D), dtype=q.dtype, device=dev)
+        lin_state = torch.empty((B, H, 2 * D * D + D), dtype=q.dtype, device=dev)
         ws = _workspace(shape, _lib.OP_FWD, dev)
         check(lib.sla_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o), _p(o_s),
                           _p(lse), _p(lin_state), _p(ws), ws.numel(), _stream(q)))
@@ -200,7 +200,7 @@ def sage_sla_attention(q, k, v, weight, bias, bm: BlockMap, feature="softmax"):
     B, H, L, D = q.shape
     shape = make_shape(B, H, L, D, 128, 64, bm.topk, q.dtype, feature)
     o = torch.empty_like(q)
-    lin_state = torch.empty((B, H, D * D + D), dtype=q.dtype, device=q.device)
+    lin_state = torch.empty((B, H, 2 * D * D + D), dtype=q.dtype, device=q.device)
     ws = _workspace(shape, _lib.OP_SAGE_FWD, q.device)
     check(lib.sage_sla_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o),
                            _p(lin_state), _p(ws), ws.numel(), _stream(q)))
