@@ -44,17 +44,24 @@ def _peaks():
 
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.proc, self.lines = index, None, []
+        self.t0 = self.t1 = None
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.index), "-lms", "10"], stdout=subprocess.PIPE, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()
         except Exception:
@@ -62,7 +69,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
     def stop(self):
         if self.proc is None:
@@ -74,7 +81,11 @@ class ClockSampler:
         except Exception:
             pass
         sm, smax, reasons = [], None, set()
-        for ln in self.lines:
+        inside = [ln for (ts, ln) in self.lines
+                  if self.t0 is None or (self.t0 - 0.02 <= ts <= (self.t1 or ts) + 0.02)]
+        if len(inside) < 3:          # very short region: fall back to everything sampled around it
+            inside = [ln for (_, ln) in self.lines]
+        for ln in inside:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -225,7 +236,7 @@ def gpu_baselines(w, q, k, v, do, W, b, steps, warmup):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3")
@@ -286,17 +297,19 @@ def main():
 
     # ---- main timed region: exactly K forward+backward steps ----
     sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         step_fwdbwd()
     sync()
     l0 = _lib.lib.sla_launch_count()
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.mark_begin()
     e0.record()
     for _ in range(args.steps):
         step_fwdbwd()
     e1.record()
     sync()
+    sampler.mark_end()
     clocks = sampler.stop()
     launches = _lib.lib.sla_launch_count() - l0
     ms = e0.elapsed_time(e1) / args.steps
