@@ -126,6 +126,23 @@ SLA_API int sla_sparse_bwd(const sla_shape* shape, const void* q, const void* k,
 SLA_API int sla_linear_state(const sla_shape* shape, const void* k, const void* v, void* lin_state,
                      void* ws, size_t ws_bytes, sla_stream_t stream);
 
+/* Same result as sla_linear_state, for callers that cannot supply a workspace. No counterpart in the
+ * reference. Some hosts fix their device-memory budget at start-up -- an inference server that gives
+ * the whole GPU to its own pool, a plugin host that treats a cudaMalloc in steady state as an error --
+ * and so have nothing to pass as `ws`. This entry point allocates nothing (no cudaMalloc, cudaFree or
+ * allocating library call): its scratch is a 16 MiB array reserved inside the library image, which
+ * every GPU that loads the library holds until the process exits.
+ *   - Limit: B*H*(D*D + D)*4 bytes must fit in those 16 MiB (B*H <= 254 at D = 128, <= 1008 at
+ *     D = 64); larger shapes return SLA_ERR_WS_TOO_SMALL. Long sequences use fewer, longer row chunks.
+ *   - The first call on each device looks up the array's device address (a one-time, synchronous
+ *     query); make that first call before starting any stream capture.
+ *   - All calls on a device share the array and it keeps the previous call's contents; every slot a
+ *     call reads is first overwritten by that call, so nothing needs clearing, but two calls whose
+ *     kernels overlap on the GPU (different streams) race on it. Serialise them.
+ */
+SLA_API int sla_linear_state_static(const sla_shape* shape, const void* k, const void* v,
+                                    void* lin_state, sla_stream_t stream);
+
 /* Replaces sparse_linear_attention/core.py:88-100 (everything in SparseLinearAttention.forward
  * after get_block_map and the dtype casts): sparse branch, feature maps, linear branch, proj_l and
  * the final sum. o_s may be NULL when no backward will follow. lin_state and lse are outputs. */

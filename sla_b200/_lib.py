@@ -19,7 +19,7 @@ FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA = 1, 2
 # every symbol include/sla_b200.h declares
 EXPORTS = (
     "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_debug_set_trace", "sla_topk_count", "sla_workspace_bytes",
-    "sla_block_map", "sla_column_lists", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_fwd", "sla_bwd",
+    "sla_block_map", "sla_column_lists", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_linear_state_static", "sla_fwd", "sla_bwd",
     "sage_sla_fwd",
 )
 
@@ -69,6 +69,8 @@ def _load() -> C.CDLL:
     lib.sla_sparse_bwd.argtypes = [sp, vp, vp, vp, vp, f32p, vp, i32p, i32p, i32p, vp, vp, vp, vp, C.c_size_t, vp]
     lib.sla_linear_state.restype = C.c_int
     lib.sla_linear_state.argtypes = [sp, vp, vp, vp, vp, C.c_size_t, vp]
+    lib.sla_linear_state_static.restype = C.c_int
+    lib.sla_linear_state_static.argtypes = [sp, vp, vp, vp, vp]
     lib.sla_fwd.restype = C.c_int
     lib.sla_fwd.argtypes = [sp, vp, vp, vp, i32p, f32p, f32p, vp, vp, f32p, vp, vp, C.c_size_t, vp]
     lib.sla_bwd.restype = C.c_int

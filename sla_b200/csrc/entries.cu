@@ -68,6 +68,15 @@ int sla_linear_state(const sla_shape* s, const void* k, const void* v, void* lin
                           w.nch, w.rows, static_cast<cudaStream_t>(stream));
 }
 
+int sla_linear_state_static(const sla_shape* s, const void* k, const void* v, void* lin_state,
+                            sla_stream_t stream) {
+  if (!k || !v || !lin_state) return SLA_ERR_NULL;
+  int rc = check_common(s);
+  if (rc != SLA_OK) return rc;
+  if (!all_aligned({k, v, lin_state})) return SLA_ERR_BAD_ALIGN;
+  return run_linear_state_static(s, k, v, lin_state, static_cast<cudaStream_t>(stream));
+}
+
 int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
             const float* w, const float* bias, void* o, void* o_s, float* lse, void* lin_state, void* ws,
             size_t ws_bytes, sla_stream_t stream) {

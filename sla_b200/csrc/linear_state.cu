@@ -182,4 +182,46 @@ int run_linear_state(const sla_shape* s, const void* k, const void* v, void* lin
   return launch_state<T, 128>(s, (const T*)k, (const T*)v, (T*)lin_state, partial, nch, rows, st);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Variant for callers that cannot hand over a workspace
+// ---------------------------------------------------------------------------------------------
+// Scratch for the per-chunk fp32 partials, reserved inside the library image: every GPU that loads the
+// library holds these 16 MiB until the process exits. All calls on a device share it.
+constexpr size_t kStaticScratchFloats = size_t(4) << 20;   // 4 Mi floats = 16 MiB
+static __device__ __align__(256) float g_state_scratch[kStaticScratchFloats];
+
+// In host code `g_state_scratch` is only a handle, not an address a kernel could use: the device
+// address is looked up once per device (with that device current) and cached.
+static float* static_scratch_for_current_device(int* status) {
+  static float* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { set_last_cuda_error(e); *status = SLA_ERR_CUDA; return nullptr; }
+  if (dev < 0 || dev >= 64) { *status = SLA_ERR_UNSUPPORTED; return nullptr; }
+  if (ptrs[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_state_scratch);
+    if (e != cudaSuccess) { set_last_cuda_error(e); *status = SLA_ERR_CUDA; return nullptr; }
+    ptrs[dev] = ptr;
+  }
+  *status = SLA_OK;
+  return ptrs[dev];
+}
+
+int run_linear_state_static(const sla_shape* s, const void* k, const void* v, void* lin_state, cudaStream_t st) {
+  const size_t rec = size_t(s->D) * s->D + s->D;
+  const size_t bh = size_t(s->B) * s->H;
+  // as many row chunks per head as fit in the reserved scratch (at least one, at most one per 512 rows)
+  size_t max_chunks = kStaticScratchFloats / (bh * rec);
+  if (max_chunks < 1) return SLA_ERR_WS_TOO_SMALL;
+  int nch = (s->L + 511) / 512;
+  if (static_cast<size_t>(nch) > max_chunks) nch = static_cast<int>(max_chunks);
+  int rows = ((s->L + nch - 1) / nch + 63) / 64 * 64;
+  nch = (s->L + rows - 1) / rows;
+  int status = SLA_OK;
+  float* scratch = static_scratch_for_current_device(&status);
+  if (scratch == nullptr) return status;
+  return run_linear_state(s, k, v, lin_state, scratch, nch, rows, st);
+}
+
 }  // namespace sla

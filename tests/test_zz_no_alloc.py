@@ -1,0 +1,59 @@
+"""sla_linear_state_static: the variant of the linear-state reduction for hosts that cannot hand the
+library a workspace (memory budget frozen at start-up, cudaMalloc forbidden in steady state). Its
+scratch lives in a fixed 16 MiB array inside the library. Called through the C ABI twice in a row and
+compared with sla_linear_state (caller-provided workspace). The two entry points may split the rows
+into different chunks, so sums differ in fp32 rounding order: same tolerance as the other 16-bit
+checks (cosine >= 0.999, relative L1 <= 1e-2), in practice identical to the last bit or two.
+This file is named so that pytest collects it last."""
+import ctypes as C
+
+import pytest
+import torch
+
+from helpers import assert_close_parity
+
+pytestmark = pytest.mark.gpu
+
+
+def _both(B, H, L, D, feature, seed):
+    from sla_b200 import _lib, ops
+    from sla_b200._lib import check, lib
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn(B, H, L, D, generator=g).bfloat16().cuda()
+    v = torch.randn(B, H, L, D, generator=g).bfloat16().cuda()
+    shape = ops.make_shape(B, H, L, D, 64, 64, 1, torch.bfloat16, feature)
+    st = torch.cuda.current_stream().cuda_stream
+    rec = 2 * D * D + D
+    ref = torch.zeros(B, H, rec, dtype=torch.bfloat16, device="cuda")
+    ws = ops._workspace(shape, _lib.OP_LINEAR_STATE, "cuda")
+    check(lib.sla_linear_state(C.byref(shape), k.data_ptr(), v.data_ptr(), ref.data_ptr(), ws.data_ptr(),
+                               ws.numel(), st))
+    got = torch.zeros_like(ref)
+    before = torch.cuda.memory_allocated()
+    check(lib.sla_linear_state_static(C.byref(shape), k.data_ptr(), v.data_ptr(), got.data_ptr(), st))
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == before
+    n = D * D + D   # H and z; the H W^T part of the record is filled by sla_fwd only
+    return got[..., :n].float().cpu(), ref[..., :n].float().cpu()
+
+
+def test_static_scratch_variant_matches_twice_in_a_row():
+    # first call: many chunks per head; second call: other shape, feature map and fewer chunks, so any
+    # stale partial left in the shared array by the first call would show up
+    for args in ((1, 3, 5000, 128, "softmax", 1), (2, 2, 700, 64, "elu", 2)):
+        got, ref = _both(*args)
+        assert torch.isfinite(got).all()
+        assert_close_parity(got, ref, cos_min=0.999, l1_max=1e-2, what=f"lin_state {args}")
+        assert float((got - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
+def test_static_scratch_variant_rejects_oversized_shapes():
+    from sla_b200 import ops
+    from sla_b200._lib import lib
+    B, H, L, D = 8, 40, 64, 128            # B*H = 320 > 254 heads at D = 128
+    k = torch.zeros(1, dtype=torch.bfloat16, device="cuda")
+    shape = ops.make_shape(B, H, L, D, 64, 64, 1, torch.bfloat16, "softmax")
+    buf = torch.zeros(16, dtype=torch.bfloat16, device="cuda")
+    rc = lib.sla_linear_state_static(C.byref(shape), buf.data_ptr(), buf.data_ptr(), buf.data_ptr(),
+                                     torch.cuda.current_stream().cuda_stream)
+    assert rc == -5, lib.sla_status_string(rc)
