@@ -347,6 +347,25 @@ static int launch_block_map(const sla_shape* s, const TIn* q, const TIn* k, int3
   return SLA_OK;
 }
 
+// Column mean of K per head, rounded to the element type (what k.mean(dim=-2) returns): used by the
+// SageSLA path (SageSLA/core.py:102). partial: fp32 [BH][ceil(L/512)][D]; kmean: fp32 [BH][D].
+template <typename TIn, int D>
+static int k_mean_typed(const sla_shape* s, const TIn* k, float* partial, float* kmean, cudaStream_t st) {
+  const int bh = s->B * s->H, nch = ceil_div(s->L, kColsumRows);
+  colsum_kernel<TIn, D><<<dim3(nch, bh), 256, 0, st>>>(k, partial, s->L, nch);
+  SLA_LAUNCH_OK();
+  kmean_finalize_kernel<TIn><<<bh, D, 0, st>>>(partial, kmean, s->L, nch, D);
+  SLA_LAUNCH_OK();
+  return SLA_OK;
+}
+int run_k_mean(const sla_shape* s, const void* k, float* partial, float* kmean, cudaStream_t st) {
+  if (s->dtype == SLA_BF16)
+    return s->D == 64 ? k_mean_typed<__nv_bfloat16, 64>(s, (const __nv_bfloat16*)k, partial, kmean, st)
+                      : k_mean_typed<__nv_bfloat16, 128>(s, (const __nv_bfloat16*)k, partial, kmean, st);
+  return s->D == 64 ? k_mean_typed<__half, 64>(s, (const __half*)k, partial, kmean, st)
+                    : k_mean_typed<__half, 128>(s, (const __half*)k, partial, kmean, st);
+}
+
 }  // namespace sla
 
 extern "C" int sla_column_lists(const sla_shape* s, const int8_t* sparse_map, int32_t* col_offsets,

@@ -59,6 +59,7 @@ int run_sparse_bwd_tc(const sla_shape* s, const BwdParams& p, void* stats, cudaS
 int run_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, float* partial,
                      int nch, int rows, cudaStream_t st);
 int run_linear_state_static(const sla_shape* s, const void* k, const void* v, void* lin_state, cudaStream_t st);
+int run_k_mean(const sla_shape* s, const void* k, float* partial, float* kmean, cudaStream_t st);
 int run_sparse_bwd_mma(const sla_shape* s, const BwdParams& p, cudaStream_t st);
 int run_linear_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_t st);
 

@@ -1,9 +1,514 @@
-// SageSLA quantized forward (placeholder translation unit until the kernels land).
+// SageSLA quantized forward (SageSLA/core.py:75-163): the sparse branch with INT8 Q.K^T and FP8 (e4m3)
+// P.V on tcgen05, then the same linear branch and proj_l as the 16-bit path.
+//
+// The reference delegates the quantized arithmetic to the third-party package spas_sage_attn (not part of
+// the reference tree); what its call sites fix is reproduced here: K is smoothed by its per-head mean
+// before quantization (SageSLA/core.py:102,108), Q is quantized per 128-row block and K per 64-row block
+// with one fp32 scale each (core.py:105-108), V is stored as e4m3 with one fp32 scale per (batch, head,
+// channel) (core.py:127-129), scores use scale = D^-0.5 (core.py:110), no causal mask, no PV skipping
+// (pvthreshold = 1e6, core.py:136). The recipe itself (symmetric abs-max scales, P scaled by 256 before
+// the e4m3 rounding) is this library's own.
+//
+// Kernel structure = sparse_fwd_tc.cu with BLKQ = 128: S = Q8 K8^T by kind::i8 (s32 accumulators in
+// TMEM), softmax in fp32 on S * sq * sk * scale * log2e, P written back to TMEM as e4m3 and multiplied
+// with the e4m3 V tile (MN-major B operand) by kind::f8f6f4.
 #include "common.cuh"
 #include "kernels.h"
+#include "tc_common.cuh"
 #include "workspace.h"
 
-extern "C" int sage_sla_fwd(const sla_shape*, const void*, const void*, const void*, const int32_t*,
-                            const float*, const float*, void*, void*, void*, size_t, sla_stream_t) {
-  return SLA_ERR_UNSUPPORTED;
+namespace sla {
+namespace tc {
+
+struct SageParams {
+  const int32_t* lut;
+  const float *qscale, *kscale, *vscale;   // [BH][MB], [BH][NB], [BH][D]
+  float* lse;
+  int* err;
+  int L, mb, nb, topk;
+  float scale_log2;
+};
+
+__device__ __forceinline__ float ex2s(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+// four fp32 -> four e4m3 bytes, element 0 in the lowest byte
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(lo) : "f"(b), "f"(a));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(hi) : "f"(d), "f"(c));
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+enum : int { kSErrQ = 301, kSErrK = 302, kSErrV = 303, kSErrEmpty = 304, kSErrS = 305, kSErrP = 306,
+             kSErrPv = 307, kSErrDrain = 308 };
+
+constexpr float kPScale = 256.0f;   // P in [0,1] is multiplied by this before rounding to e4m3 (max 448)
+
+// D = 128 only: rows of the 8-bit tensors are exactly one 128-byte swizzle atom.
+template <typename T>
+__global__ void __launch_bounds__(192, 2)
+sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, SageParams p) {
+  constexpr int D = 128;
+  constexpr int Q_BYTES = 128 * 128, KV_BYTES = 64 * 128;      // 8-bit tiles
+  constexpr int O_SLAB = 128 * 128;                            // 16-bit output staging, 2 slabs
+  constexpr int NS = 4;                                        // ring stages (K and V each)
+  constexpr uint32_t IDESC_S = idesc_i8(128, 64);
+  constexpr uint32_t IDESC_PV = idesc_e4m3(128, D, 1);
+  constexpr uint32_t TMEM_COLS = 256;
+  constexpr int COL_O = 0, COL_S = D;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[4 * NS + 6];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  __shared__ float s_vscale[D];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x, bh = blockIdx.y;
+  const int L = p.L;
+  const uint32_t raw_a = smem_u32(smem_raw);
+  const uint32_t base_a = (raw_a + 1023u) & ~1023u;
+  uint8_t* base_p = smem_raw + (base_a - raw_a);
+  const uint32_t sO = base_a;                        // 32 KB output staging (also holds Q8 in its first 16 KB)
+  const uint32_t sQ = base_a;
+  const uint32_t sK0 = sO + 2 * O_SLAB;
+  const uint32_t sV0 = sK0 + NS * KV_BYTES;
+  int32_t* ulist = reinterpret_cast<int32_t*>(base_p + 2 * O_SLAB + 2 * NS * KV_BYTES);
+  float* sk_list = reinterpret_cast<float*>(ulist + p.topk);
+
+  const uint32_t bar0 = smem_u32(&bars[0]);
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  // q_full | k_full[NS] | v_full[NS] | k_empty[NS] | v_empty[NS] | s_full[2] | p_full[2] | pv_done
+  constexpr int B_Q = 0, B_K = 1, B_V = 1 + NS, B_KE = 1 + 2 * NS, B_VE = 1 + 3 * NS, B_S = 1 + 4 * NS,
+                B_P = 3 + 4 * NS, B_PV = 5 + 4 * NS;
+
+  if (tid == 0) {
+    s_abort = *reinterpret_cast<volatile int*>(p.err) != 0;
+    mbar_init(BAR(B_Q), 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(BAR(B_K + s), 1); mbar_init(BAR(B_V + s), 1);
+      mbar_init(BAR(B_KE + s), 1); mbar_init(BAR(B_VE + s), 1);
+    }
+    for (int b = 0; b < 2; ++b) { mbar_init(BAR(B_S + b), 1); mbar_init(BAR(B_P + b), 128); }
+    mbar_init(BAR(B_PV), 1);
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 4) {
+    if (lane == 0) { prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmO); }
+    const int32_t* row = p.lut + (static_cast<size_t>(bh) * p.mb + tile) * p.topk;
+    for (int i = lane; i < p.topk; i += 32) {
+      int idx = row[i];
+      ulist[i] = idx;
+      sk_list[i] = p.kscale[static_cast<size_t>(bh) * p.nb + idx];
+    }
+  }
+  for (int i = tid; i < D; i += 192) s_vscale[i] = p.vscale[static_cast<size_t>(bh) * D + i];
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+  const int n_ent = p.topk;
+  volatile int* abortp = &s_abort;
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0 && !*abortp) {
+      mbar_expect_tx(BAR(B_Q), Q_BYTES);
+      tma_load_3d(sQ, &tmQ, BAR(B_Q), 0, tile * 128, bh);
+      int issued_k = 0, issued_v = 0;
+      for (int t = 0; t <= n_ent; ++t) {
+        if (t < n_ent) {
+          const int s = t % NS, use = t / NS;
+          if (use > 0 && !mbar_wait(BAR(B_KE + s), (use - 1) & 1, kSErrEmpty, p.err)) { *abortp = 1; break; }
+          if (*abortp) break;
+          mbar_expect_tx(BAR(B_K + s), KV_BYTES);
+          tma_load_3d(sK0 + s * KV_BYTES, &tmK, BAR(B_K + s), 0, ulist[t] * 64, bh);
+          issued_k = t + 1;
+        }
+        if (t >= 1) {
+          const int j = t - 1, s = j % NS, use = j / NS;
+          if (use > 0 && !mbar_wait(BAR(B_VE + s), (use - 1) & 1, kSErrEmpty, p.err)) { *abortp = 1; break; }
+          if (*abortp) break;
+          mbar_expect_tx(BAR(B_V + s), KV_BYTES);
+          tma_load_3d(sV0 + s * KV_BYTES, &tmV, BAR(B_V + s), 0, ulist[j] * 64, bh);
+          issued_v = j + 1;
+        }
+      }
+      if (*abortp) {
+        mbar_wait(BAR(B_Q), 0, kSErrDrain, p.err);
+        for (int j = max(0, issued_k - NS); j < issued_k; ++j) mbar_wait(BAR(B_K + j % NS), (j / NS) & 1, kSErrDrain, p.err);
+        for (int j = max(0, issued_v - NS); j < issued_v; ++j) mbar_wait(BAR(B_V + j % NS), (j / NS) & 1, kSErrDrain, p.err);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0 && !*abortp) {
+      const uint32_t q_lo = desc_lo(sQ, 16);
+      auto issue_s = [&](int j) {
+        const uint32_t k_lo = desc_lo(sK0 + (j % NS) * KV_BYTES, 16);
+        const uint32_t d = tmem + COL_S + (j & 1) * 64;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)   // K = 32 int8 = 32 bytes per step inside the 128-byte row
+          mma_ss_i8(d, q_lo + ((kk * 32) >> 4), k_lo + ((kk * 32) >> 4), IDESC_S, kk > 0 ? 1u : 0u);
+      };
+      bool ok = mbar_wait(BAR(B_Q), 0, kSErrQ, p.err) && mbar_wait(BAR(B_K), 0, kSErrK, p.err);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        tc_commit(BAR(B_S));
+        tc_commit(BAR(B_KE));
+      }
+      for (int j = 0; ok && j < n_ent; ++j) {
+        if (j + 1 < n_ent) {
+          ok = mbar_wait(BAR(B_K + (j + 1) % NS), ((j + 1) / NS) & 1, kSErrK, p.err);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(j + 1);
+          tc_commit(BAR(B_S + ((j + 1) & 1)));
+          tc_commit(BAR(B_KE + (j + 1) % NS));
+        }
+        ok = mbar_wait(BAR(B_P + (j & 1)), (j >> 1) & 1, kSErrP, p.err) &&
+             mbar_wait(BAR(B_V + j % NS), (j / NS) & 1, kSErrV, p.err);
+        if (!ok || *abortp) { ok = false; break; }
+        tc_fence_after();
+        // B = V8_j rows [32 kk, +32): MN-major, one 128-byte atom per row, 8-row groups 1024 B apart
+        const uint32_t v_lo = desc_lo(sV0 + (j % NS) * KV_BYTES, KV_BYTES);
+        const uint32_t pa = tmem + COL_S + (j & 1) * 64;   // P_j: four e4m3 per column, 16 columns
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk)
+          mma_ts_f8(tmem + COL_O, pa + kk * 8, v_lo + ((kk * 4096) >> 4), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(BAR(B_VE + j % NS));
+        tc_commit(BAR(B_PV));
+      }
+      if (!ok) *abortp = 1;
+    }
+  } else {
+    // ------------------------------ softmax warps ------------------------------
+    const int row = tid;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float sq = p.qscale[static_cast<size_t>(bh) * p.mb + tile] * p.scale_log2;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = !*abortp;
+    for (int j = 0; ok && j < n_ent; ++j) {
+      const int b = j & 1;
+      if (!mbar_wait(BAR(B_S + b), (j >> 1) & 1, kSErrS, p.err)) { ok = false; break; }
+      if (*abortp) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_addr = tmem + lane_addr + COL_S + b * 64;
+      uint32_t sv[64];
+      tmem_ld_x64(s_addr, sv);
+      tmem_wait_ld();
+      const float sc = sq * sk_list[j];
+      const int valid = L - ulist[j] * 64;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float x = static_cast<float>(static_cast<int32_t>(sv[c])) * sc;
+        if (valid < 64 && c >= valid) x = -INFINITY;
+        sv[c] = __float_as_uint(x);
+        mx = fmaxf(mx, x);
+      }
+      const bool need = mx > m_used;            // exact running maximum: P stays in [0, 1]
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
+        if (!mbar_wait(BAR(B_PV), (j - 1) & 1, kSErrPv, p.err)) { ok = false; break; }
+        tc_fence_after();
+        const float alpha = need ? ex2s(m_used - mx) : 1.0f;
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t ov[32];
+          tmem_ld_x32(tmem + lane_addr + COL_O + c0, ov);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
+          tmem_st_x32(tmem + lane_addr + COL_O + c0, ov);
+        }
+      }
+      if (need) {
+        l *= ex2s(m_used - mx);
+        m_used = mx;
+      }
+      uint32_t pk[16];
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 64; c += 4) {
+        float p0 = ex2s(__uint_as_float(sv[c]) - m_used), p1 = ex2s(__uint_as_float(sv[c + 1]) - m_used);
+        float p2 = ex2s(__uint_as_float(sv[c + 2]) - m_used), p3 = ex2s(__uint_as_float(sv[c + 3]) - m_used);
+        rs += (p0 + p1) + (p2 + p3);
+        pk[c >> 2] = pack_e4m3x4(p0 * kPScale, p1 * kPScale, p2 * kPScale, p3 * kPScale);
+      }
+      l += rs;
+      tmem_st_x16(s_addr, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(BAR(B_P + b));
+    }
+    if (ok && n_ent > 0) ok = mbar_wait(BAR(B_PV), (n_ent - 1) & 1, kSErrPv, p.err);
+    if (!ok) *abortp = 1;
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    if (!*abortp) {
+      tc_fence_after();
+      const float inv = 1.0f / (l * kPScale);
+      const int grow = tile * 128 + row;
+      if (grow < L) p.lse[static_cast<size_t>(bh) * L + grow] = m_used + log2f(l);
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t ov[32];
+        tmem_ld_x32(tmem + lane_addr + COL_O + c0, ov);
+        tmem_wait_ld();
+        const uint32_t slab = sO + (c0 >> 6) * O_SLAB + row * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = c0 + q4 * 8 + 2 * e;
+            w[e] = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 2 * e]) * inv * s_vscale[c],
+                                  __uint_as_float(ov[q4 * 8 + 2 * e + 1]) * inv * s_vscale[c + 1]);
+          }
+          const int chunk = ((c0 & 63) >> 3) + q4;
+          const uint32_t addr = slab + ((chunk ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");
+      if (tid == 0) {
+        for (int c = 0; c < 2; ++c) tma_store_3d(&tmO, sO + c * O_SLAB, c * 64, tile * 128, bh);
+        tma_store_commit();
+        tma_store_wait_all();
+      }
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+}  // namespace tc
+
+// ---------------------------------------------------------------------------------------------
+// Quantization pre-passes (HBM-bound)
+// ---------------------------------------------------------------------------------------------
+// One CTA per block of `blk` rows: symmetric abs-max INT8, scale = amax / 127 (zero blocks get scale 1e-8/127).
+// z = 0: Q in blocks of 128 rows; z = 1: K - mean in blocks of 64 rows.
+template <typename T>
+__global__ void __launch_bounds__(256) sage_quant_qk_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                            const float* __restrict__ kmean, int8_t* __restrict__ q8,
+                                                            int8_t* __restrict__ k8, float* __restrict__ qscale,
+                                                            float* __restrict__ kscale, int L, int mb, int nb) {
+  constexpr int D = 128;
+  __shared__ float red[8];
+  const bool is_k = blockIdx.z == 1;
+  const int blk = is_k ? 64 : 128, nblk = is_k ? nb : mb;
+  if (static_cast<int>(blockIdx.x) >= nblk) return;
+  const int bh = blockIdx.y, ib = blockIdx.x, tid = threadIdx.x;
+  const T* src = (is_k ? k : q) + static_cast<size_t>(bh) * L * D;
+  int8_t* dst = (is_k ? k8 : q8) + static_cast<size_t>(bh) * L * D;
+  const int c = (tid & 15) * 8;                 // 16 threads per row, 8 elements each
+  float mean[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) mean[e] = is_k ? kmean[static_cast<size_t>(bh) * D + c + e] : 0.f;
+  float vals[8][8];                             // up to 8 rows per thread (128 rows / 16 row groups)
+  const int rows_per_thread = blk / 16;
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = ib * blk + (tid >> 4) + 16 * i;
+    if (i < rows_per_thread && r < L) {
+      uint4 raw = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * D + c);
+      const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 f = Elem<T>::unpack2(u[e]);
+        vals[i][2 * e] = f.x - mean[2 * e];
+        vals[i][2 * e + 1] = f.y - mean[2 * e + 1];
+        amax = fmaxf(amax, fmaxf(fabsf(vals[i][2 * e]), fabsf(vals[i][2 * e + 1])));
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) vals[i][e] = 0.f;
+    }
+  }
+  amax = warp_max(amax);
+  if ((tid & 31) == 0) red[tid >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+  const float scale = fmaxf(amax, 1e-8f) / 127.f, inv = 1.f / scale;
+  if (tid == 0) (is_k ? kscale : qscale)[static_cast<size_t>(bh) * nblk + ib] = scale;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = ib * blk + (tid >> 4) + 16 * i;
+    if (i < rows_per_thread && r < L) {
+      uint32_t w[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        int b0 = __float2int_rn(vals[i][4 * h] * inv), b1 = __float2int_rn(vals[i][4 * h + 1] * inv);
+        int b2 = __float2int_rn(vals[i][4 * h + 2] * inv), b3 = __float2int_rn(vals[i][4 * h + 3] * inv);
+        w[h] = (b0 & 0xff) | ((b1 & 0xff) << 8) | ((b2 & 0xff) << 16) | (static_cast<uint32_t>(b3 & 0xff) << 24);
+      }
+      *reinterpret_cast<uint2*>(dst + static_cast<size_t>(r) * D + c) = make_uint2(w[0], w[1]);
+    }
+  }
+}
+
+// per-channel abs-max of V over chunks of 512 rows: partial[bh][chunk][D]
+template <typename T>
+__global__ void __launch_bounds__(256) sage_v_amax_kernel(const T* __restrict__ v, float* __restrict__ partial,
+                                                          int L, int nch) {
+  constexpr int D = 128;
+  __shared__ float red[16][D];
+  const int bh = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
+  const int rg = tid >> 4, c = (tid & 15) * 8;
+  const T* base = v + static_cast<size_t>(bh) * L * D;
+  float am[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) am[e] = 0.f;
+  const int row1 = min(L, (ch + 1) * 512);
+  for (int r = ch * 512 + rg; r < row1; r += 16) {
+    uint4 raw = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(r) * D + c);
+    const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 f = Elem<T>::unpack2(u[e]);
+      am[2 * e] = fmaxf(am[2 * e], fabsf(f.x));
+      am[2 * e + 1] = fmaxf(am[2 * e + 1], fabsf(f.y));
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) red[rg][c + e] = am[e];
+  __syncthreads();
+  if (tid < D) {
+    float m = 0.f;
+#pragma unroll
+    for (int g = 0; g < 16; ++g) m = fmaxf(m, red[g][tid]);
+    partial[(static_cast<size_t>(bh) * nch + ch) * D + tid] = m;
+  }
+}
+__global__ void sage_v_scale_kernel(const float* __restrict__ partial, float* __restrict__ vscale, int nch) {
+  const int bh = blockIdx.x, d = threadIdx.x;
+  float m = 0.f;
+  for (int c = 0; c < nch; ++c) m = fmaxf(m, partial[(static_cast<size_t>(bh) * nch + c) * 128 + d]);
+  vscale[static_cast<size_t>(bh) * 128 + d] = fmaxf(m, 1e-8f) / 448.f;
+}
+template <typename T>
+__global__ void __launch_bounds__(256) sage_quant_v_kernel(const T* __restrict__ v, const float* __restrict__ vscale,
+                                                           uint8_t* __restrict__ v8, int L) {
+  constexpr int D = 128;
+  const int bh = blockIdx.y, tid = threadIdx.x;
+  const int c = (tid & 15) * 8;
+  float inv[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) inv[e] = 1.f / vscale[static_cast<size_t>(bh) * D + c + e];
+  const T* base = v + static_cast<size_t>(bh) * L * D;
+  uint8_t* out = v8 + static_cast<size_t>(bh) * L * D;
+  for (int r = blockIdx.x * 64 + (tid >> 4); r < min(L, (static_cast<int>(blockIdx.x) + 1) * 64); r += 16) {
+    uint4 raw = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(r) * D + c);
+    const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 t = Elem<T>::unpack2(u[e]);
+      f[2 * e] = t.x * inv[2 * e];
+      f[2 * e + 1] = t.y * inv[2 * e + 1];
+    }
+    uint2 w = make_uint2(tc::pack_e4m3x4(f[0], f[1], f[2], f[3]), tc::pack_e4m3x4(f[4], f[5], f[6], f[7]));
+    *reinterpret_cast<uint2*>(out + static_cast<size_t>(r) * D + c) = w;
+  }
+}
+
+template <typename T>
+static int run_sage_typed(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+                          void* o_s, float* lse, unsigned char* ws, cudaStream_t st) {
+  const int bh = s->B * s->H, L = s->L, D = 128;
+  const int mb = ceil_div(L, 128), nb = ceil_div(L, 64);
+  WsSage w = ws_sage(s);
+  float* kmean = reinterpret_cast<float*>(ws + w.kmean);
+  float* part = reinterpret_cast<float*>(ws + w.colsum);
+  int8_t* q8 = reinterpret_cast<int8_t*>(ws + w.q8);
+  int8_t* k8 = reinterpret_cast<int8_t*>(ws + w.k8);
+  uint8_t* v8 = ws + w.v8;
+  float* qs = reinterpret_cast<float*>(ws + w.qscale);
+  float* ks = reinterpret_cast<float*>(ws + w.kscale);
+  float* vs = reinterpret_cast<float*>(ws + w.vscale);
+  int rc = run_k_mean(s, k, part, kmean, st);
+  if (rc != SLA_OK) return rc;
+  sage_quant_qk_kernel<T><<<dim3(nb, bh, 2), 256, 0, st>>>(static_cast<const T*>(q), static_cast<const T*>(k), kmean,
+                                                          q8, k8, qs, ks, L, mb, nb);
+  SLA_LAUNCH_OK();
+  sage_v_amax_kernel<T><<<dim3(w.nch, bh), 256, 0, st>>>(static_cast<const T*>(v), part, L, w.nch);
+  SLA_LAUNCH_OK();
+  sage_v_scale_kernel<<<bh, D, 0, st>>>(part, vs, w.nch);
+  SLA_LAUNCH_OK();
+  sage_quant_v_kernel<T><<<dim3(nb, bh), 256, 0, st>>>(static_cast<const T*>(v), vs, v8, L);
+  SLA_LAUNCH_OK();
+
+  CUtensorMap tq, tk, tv, to;
+  if ((rc = make_tmap_3d_u8(&tq, q8, 128, L, bh, 128)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d_u8(&tk, k8, 128, L, bh, 64)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d_u8(&tv, v8, 128, L, bh, 64)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&to, o_s, s->dtype, D, L, bh, 128)) != SLA_OK) return rc;
+  tc::SageParams p;
+  p.lut = lut; p.qscale = qs; p.kscale = ks; p.vscale = vs; p.lse = lse;
+  p.err = tc_error_word();
+  if (p.err == nullptr) return SLA_ERR_CUDA;
+  p.L = L; p.mb = mb; p.nb = nb; p.topk = s->topk;
+  p.scale_log2 = softmax_scale(s) * kLog2e;
+  auto kern = tc::sage_fwd_tc_kernel<T>;
+  const int smem = 1024 + 2 * 128 * 128 + 2 * 4 * 64 * 128 + s->topk * 8 + 16;
+  if (smem > 113 * 1024) return SLA_ERR_BAD_TOPK;
+  SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  kern<<<dim3(mb, bh), 192, smem, st>>>(tq, tk, tv, to, p);
+  SLA_LAUNCH_OK();
+  return SLA_OK;
+}
+
+}  // namespace sla
+
+extern "C" int sage_sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+                            const float* w, const float* bias, void* o, void* lin_state, void* ws, size_t ws_bytes,
+                            sla_stream_t stream) {
+  using namespace sla;
+  if (!q || !k || !v || !lut || !o || !ws) return SLA_ERR_NULL;
+  int rc = validate_shape(s);
+  if (rc != SLA_OK) return rc;
+  if (s->BLKQ != 128 || s->BLKK != 64) return SLA_ERR_BAD_SHAPE;   // SageSLA/README.md:16-17
+  if (s->D != 128) return SLA_ERR_UNSUPPORTED;                     // 8-bit rows must fill a 128-byte swizzle atom
+  if ((rc = check_device_arch()) != SLA_OK) return rc;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(ws)) return SLA_ERR_BAD_ALIGN;
+  WsSage wsz = ws_sage(s);
+  if (ws_bytes < wsz.total) return SLA_ERR_WS_TOO_SMALL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned char* base = static_cast<unsigned char*>(ws);
+  float* lse = reinterpret_cast<float*>(base + wsz.lse);
+  // sparse branch into o
+  rc = s->dtype == SLA_BF16 ? run_sage_typed<__nv_bfloat16>(s, q, k, v, lut, o, lse, base, st)
+                            : run_sage_typed<__half>(s, q, k, v, lut, o, lse, base, st);
+  if (rc != SLA_OK || (s->flags & SLA_FLAG_SPARSE_ONLY)) return rc;
+  // linear branch + proj_l exactly as in the 16-bit path (SageSLA/core.py:148-158)
+  if (!w || !lin_state) return SLA_ERR_NULL;
+  WsLinearState wl = ws_linear_state(s);
+  void* wbits = base + wsz.wbits;
+  if ((rc = convert_proj(s, w, bias, wbits, st)) != SLA_OK) return rc;
+  if ((rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wsz.lin + wl.partial), wl.nch, wl.rows, st)) != SLA_OK) return rc;
+  if ((rc = run_state_proj(s, lin_state, wbits, st)) != SLA_OK) return rc;
+  FwdParams p;
+  p.q = q; p.k = k; p.v = v; p.lut = lut; p.o = o; p.o_s = o; p.lse = lse; p.lin_state = lin_state; p.wbits = wbits;
+  p.L = s->L; p.mb = ceil_div(s->L, s->BLKQ); p.topk = s->topk; p.scale_log2 = softmax_scale(s) * kLog2e;
+  return run_linear_readout(s, p, st);
 }

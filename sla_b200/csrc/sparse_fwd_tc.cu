@@ -408,6 +408,23 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int dtype, int D, int L, in
   return SLA_OK;
 }
 
+int make_tmap_3d_u8(CUtensorMap* out, const void* base, int row_bytes, int L, int BH, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return SLA_ERR_CUDA;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(BH)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(L) * row_bytes};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(row_bytes), static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_cuda_error(cudaErrorInvalidValue);
+    return SLA_ERR_CUDA;
+  }
+  return SLA_OK;
+}
+
 template <typename T, int D, int BM>
 static int launch_tc(const sla_shape* s, const FwdParams& fp, cudaStream_t st) {
   const int bh = s->B * s->H;

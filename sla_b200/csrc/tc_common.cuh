@@ -143,11 +143,45 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_
       : "memory");
 }
 
+// 8-bit kinds (K = 32 per instruction): kind::i8 (s8 x s8 -> s32) and kind::f8f6f4 (e4m3 x e4m3 -> f32)
+__device__ __forceinline__ void mma_ss_i8(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_f8(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], db, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi)
+      : "memory");
+}
+// instruction descriptors: s8 x s8 -> s32, both K-major; e4m3 x e4m3 -> f32 with an MN-major B
+__host__ __device__ constexpr uint32_t idesc_i8(int M, int N) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t idesc_e4m3(int M, int N, int b_mn_major) {
+  return (1u << 4) | (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+
 }  // namespace tc
 
 // host: encode a 3-D tensor map (D, L, BH) of 16-bit elements with a (64, box_rows, 1) box and
 // 128-byte swizzle. Returns SLA_OK or SLA_ERR_CUDA.
 int make_tmap_3d(CUtensorMap* out, const void* base, int dtype, int D, int L, int BH, int box_rows);
+// host: same for 8-bit elements, rows of `row_bytes` (<= 128) bytes, box = (row_bytes, box_rows, 1).
+int make_tmap_3d_u8(CUtensorMap* out, const void* base, int row_bytes, int L, int BH, int box_rows);
 // host: address of the current device's error word (looked up once per device), or nullptr.
 int* tc_error_word();
 

@@ -115,10 +115,11 @@ struct WsSage {
   size_t colsum;   // fp32 [BH][NCH][D] partial column sums of K, then [BH][NCH][D] column abs-max of V
   size_t q8;       // int8 [BH][L][D]
   size_t k8;       // int8 [BH][L][D]
-  size_t v8;       // e4m3 [BH][D][Lpad] (transposed, Lpad = ceil(L/64)*64)
+  size_t v8;       // e4m3 [BH][L][D]
   size_t qscale;   // fp32 [BH][M_BLOCKS]
   size_t kscale;   // fp32 [BH][N_BLOCKS]
   size_t vscale;   // fp32 [BH][D]
+  size_t lse;      // fp32 [BH][L]
   size_t total;
   int nch;
 };
@@ -126,7 +127,6 @@ inline WsSage ws_sage(const sla_shape* s) {
   WsSage w;
   size_t bh = size_t(s->B) * s->H;
   int mb = ws_ceil_div(s->L, s->BLKQ), nb = ws_ceil_div(s->L, s->BLKK);
-  size_t lpad = size_t(nb) * 64;
   w.nch = ws_ceil_div(s->L, kColsumRows);
   size_t o = 0;
   w.lin = o;    o += ws_linear_state(s).total;
@@ -135,10 +135,11 @@ inline WsSage ws_sage(const sla_shape* s) {
   w.colsum = o; o += ws_round(bh * w.nch * s->D * 4 * 2);
   w.q8 = o;     o += ws_round(bh * size_t(s->L) * s->D);
   w.k8 = o;     o += ws_round(bh * size_t(s->L) * s->D);
-  w.v8 = o;     o += ws_round(bh * s->D * lpad);
+  w.v8 = o;     o += ws_round(bh * size_t(s->L) * s->D);
   w.qscale = o; o += ws_round(bh * mb * 4);
   w.kscale = o; o += ws_round(bh * nb * 4);
   w.vscale = o; o += ws_round(bh * s->D * 4);
+  w.lse = o;    o += ws_round(bh * size_t(s->L) * 4);
   w.total = o;
   return w;
 }

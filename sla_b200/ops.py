@@ -194,11 +194,13 @@ def sla_attention(q, k, v, weight, bias, bm: BlockMap, BLKQ=64, BLKK=64, feature
     return _SLAFused.apply(q, k, v, weight, bias, bm, BLKQ, BLKK, feature, need_grad, impl_flags)
 
 
-def sage_sla_attention(q, k, v, weight, bias, bm: BlockMap, feature="softmax"):
-    """SageSLA/core.py:100-158: quantized sparse branch + linear branch + proj_l. Forward only."""
+def sage_sla_attention(q, k, v, weight, bias, bm: BlockMap, feature="softmax", sparse_only: bool = False):
+    """SageSLA/core.py:100-158: quantized sparse branch + linear branch + proj_l. Forward only.
+    ``sparse_only`` returns the quantized sparse branch alone (the o_s of SageSLA/core.py:114)."""
     _require_cuda(q, k, v, weight)
     B, H, L, D = q.shape
-    shape = make_shape(B, H, L, D, 128, 64, bm.topk, q.dtype, feature)
+    shape = make_shape(B, H, L, D, 128, 64, bm.topk, q.dtype, feature,
+                       flags=_lib.FLAG_SPARSE_ONLY if sparse_only else 0)
     o = torch.empty_like(q)
     lin_state = torch.empty((B, H, 2 * D * D + D), dtype=q.dtype, device=q.device)
     ws = _workspace(shape, _lib.OP_SAGE_FWD, q.device)

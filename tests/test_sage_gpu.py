@@ -1,0 +1,68 @@
+"""GPU checks of the SageSLA quantized forward (sage_sla_fwd through the C ABI / module).
+The reference's quantized kernels live in the un-vendored spas_sage_attn package, so parity at that
+boundary is unpinned; the checks are (i) against this repository's CPU restatement of the same
+quantization recipe, (ii) against the un-quantized 16-bit path (cosine >= 0.995, the bar for the
+quantized path), (iii) the whole module against the oracle module forward."""
+import pytest
+import torch
+
+from helpers import assert_close_parity, cos_sim
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(B, H, L, D, seed, k_offset=0.0):
+    g = torch.Generator().manual_seed(seed)
+    q, k, v = (torch.randn(B, H, L, D, generator=g) for _ in range(3))
+    k = k + k_offset * torch.randn(1, H, 1, D, generator=g)
+    return q.bfloat16(), k.bfloat16(), v.bfloat16()
+
+
+@pytest.mark.parametrize("B,H,L,ratio,koff", [(1, 2, 1000, 0.3, 0.0), (2, 1, 2500, 0.1, 2.0), (1, 1, 128, 1.0, 0.5),
+                                              (1, 1, 1104, 0.25, 1.0)])
+def test_sage_sparse_branch(B, H, L, ratio, koff):
+    from oracle import sla_oracle as O
+    from sla_b200 import ops
+    D = 128
+    q, k, v = _inputs(B, H, L, D, L, koff)
+    w = torch.zeros(D, D, device="cuda")
+    bm = ops.block_map(q.cuda(), k.cuda(), ratio, 128, 64)
+    got = ops.sage_sla_attention(q.cuda(), k.cuda(), v.cuda(), w, None, bm, sparse_only=True).float().cpu()
+    lut = bm.lut.cpu().long()
+    ref_q = O.sage_sparse_fwd(q, k, v, lut, 128, 64, p_scale=256.0)
+    ref_f, _ = O.sparse_fwd_gather(q, k, v, lut, 128, 64)
+    assert torch.isfinite(got).all()
+    assert_close_parity(got, ref_q, cos_min=0.999, l1_max=3e-2, what="vs quantized oracle")
+    assert cos_sim(got, ref_f) >= 0.995, "vs un-quantized sparse attention"
+
+
+def test_sage_module_matches_oracle_and_16bit_module():
+    import sla_b200
+    from oracle import sla_oracle as O
+    B, H, L, D = 1, 2, 1500, 128
+    q, k, v = _inputs(B, H, L, D, 7, 1.0)
+    g = torch.Generator().manual_seed(3)
+    w, b = torch.randn(D, D, generator=g) * 0.05, torch.randn(D, generator=g) * 0.05
+    sage = sla_b200.SageSparseLinearAttention(D, 0.2, "softmax").cuda()
+    full = sla_b200.SparseLinearAttention(D, 0.2, "softmax", BLKQ=128, BLKK=64).cuda()
+    for m in (sage, full):
+        with torch.no_grad():
+            m.proj_l.weight.copy_(w)
+            m.proj_l.bias.copy_(b)
+    with torch.no_grad():
+        o_sage, sp = sage(q.cuda(), k.cuda(), v.cuda(), return_sparsity=True)
+        o_full = full(q.cuda(), k.cuda(), v.cuda())
+    assert o_sage.dtype == torch.bfloat16 and sp == 4 / 24
+    ref = O.sla_forward(q, k, v, w, b, 0.2, "softmax", 128, 64, torch.bfloat16)
+    assert cos_sim(o_sage.float().cpu(), ref.float()) >= 0.995
+    assert cos_sim(o_sage.float().cpu(), o_full.float().cpu()) >= 0.995
+
+
+def test_sage_rejects_other_block_sizes_and_head_dims():
+    import sla_b200
+    with pytest.raises(ValueError):
+        sla_b200.SageSparseLinearAttention(128, 0.2, BLKQ=64, BLKK=64)
+    m = sla_b200.SageSparseLinearAttention(64, 0.5).cuda()
+    x = torch.randn(1, 1, 256, 64, device="cuda").bfloat16()
+    with pytest.raises(NotImplementedError):
+        m(x, x, x)
