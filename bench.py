@@ -139,10 +139,20 @@ def cpu_sample(w):
     return q, k, v, do, W, b
 
 
+def _use_all_host_threads():
+    """torchrun pins OMP_NUM_THREADS=1; the CPU arm is meant to use every core it may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def run_reference_arm(args, w, rank):
     if rank != 0:
         return
-    cores = torch.get_num_threads()
+    cores = _use_all_host_threads()
     sample = cpu_sample(w)
     for _ in range(min(args.warmup, 1)):
         cpu_reference_step(w, sample)
@@ -277,11 +287,15 @@ def main():
     q, k, v, do = synthetic.make_inputs(w, dev, units=unit_ids)
     q, k, v, do = (t.view(w.B, w.H, w.L, w.D) for t in (q, k, v, do))
     W, b = synthetic.make_proj(w, dev)
-    m = sla_b200.SparseLinearAttention(w.D, w.topk, w.feature, w.BLKQ, w.BLKK).to(dev)
+    bwd = w.backward and not w.quantized
+    if w.quantized:
+        m = sla_b200.SageSparseLinearAttention(w.D, w.topk, w.feature).to(dev)
+    else:
+        m = sla_b200.SparseLinearAttention(w.D, w.topk, w.feature, w.BLKQ, w.BLKK).to(dev)
     with torch.no_grad():
         m.proj_l.weight.copy_(W)
         m.proj_l.bias.copy_(b)
-    if args.legacy_mma:
+    if args.legacy_mma and not w.quantized:
         m.impl_flags |= _lib.FLAG_LEGACY_MMA
     qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
 
@@ -290,6 +304,8 @@ def main():
             return m(q, k, v)
 
     def step_fwdbwd():
+        if not bwd:
+            return step_fwd()
         o = m(qg, kg, vg)
         o.backward(do)
         qg.grad = kg.grad = vg.grad = None
@@ -328,6 +344,11 @@ def main():
     ho, hdq, hdk, hdv = (torch.empty_like(hq).pin_memory() for _ in range(4))
 
     def step_e2e():
+        if not bwd:
+            dq_, dk_, dv_ = (h.to(dev, non_blocking=True) for h in (hq, hk, hv))
+            with torch.no_grad():
+                ho.copy_(m(dq_, dk_, dv_), non_blocking=True)
+            return
         dq_, dk_, dv_, ddo = (h.to(dev, non_blocking=True) for h in (hq, hk, hv, hdo))
         dq_.requires_grad_(True); dk_.requires_grad_(True); dv_.requires_grad_(True)
         o = m(dq_, dk_, dv_)
@@ -349,14 +370,20 @@ def main():
     # ---- the dominant kernels timed alone (CUDA events on the launching stream) ----
     peaks = _peaks()
     import ctypes as C
-    bm = ops.block_map(q, k, w.topk, w.BLKQ, w.BLKK, want_cols=True)
+    BLKQ, BLKK = (128, 64) if w.quantized else (w.BLKQ, w.BLKK)
+    bm = ops.block_map(q, k, w.topk, BLKQ, BLKK, want_cols=True)
     flags = _lib.FLAG_SPARSE_ONLY | (_lib.FLAG_LEGACY_MMA if args.legacy_mma else 0)
-    shape = ops.make_shape(w.B, w.H, w.L, w.D, w.BLKQ, w.BLKK, bm.topk, torch.bfloat16, w.feature, flags=flags)
+    shape = ops.make_shape(w.B, w.H, w.L, w.D, BLKQ, BLKK, bm.topk, torch.bfloat16, w.feature, flags=flags)
     o_s = torch.empty_like(q)
     lse = torch.empty((w.B, w.H, w.L), dtype=torch.float32, device=dev)
     st = torch.cuda.current_stream().cuda_stream
 
+    Wz = torch.zeros(w.D, w.D, device=dev)
+
     def k_fwd():
+        if w.quantized:   # quantization pre-passes + the 8-bit kernel (sparse branch only)
+            ops.sage_sla_attention(q, k, v, Wz, None, bm, w.feature, sparse_only=True)
+            return
         _lib.check(_lib.lib.sla_sparse_fwd(C.byref(shape), q.data_ptr(), k.data_ptr(), v.data_ptr(),
                                            bm.lut.data_ptr(), o_s.data_ptr(), lse.data_ptr(), st))
 
@@ -370,32 +397,41 @@ def main():
                                            dk_.data_ptr(), dv_.data_ptr(), bws.data_ptr(), bws.numel(), st))
 
     def k_map():
-        ops.block_map(q, k, w.topk, w.BLKQ, w.BLKK, want_cols=True)
+        ops.block_map(q, k, w.topk, BLKQ, BLKK, want_cols=True)
 
     kf_ms = timed(k_fwd, args.steps, 3, torch.cuda.synchronize)
-    kb_ms = timed(k_bwd, args.steps, 3, torch.cuda.synchronize)
+    if bwd:
+        k_fwd()
+    kb_ms = timed(k_bwd, args.steps, 3, torch.cuda.synchronize) if bwd else 0.0
     km_ms = timed(k_map, args.steps, 3, torch.cuda.synchronize)
     fwd_flops = w.sparse_flops(False)
     bwd_flops = w.sparse_flops(True) - fwd_flops
     kernels = {
         "sparse_fwd": {"ms": kf_ms, "tflops": fwd_flops / kf_ms / 1e9},
-        "sparse_bwd_dq_dkdv": {"ms": kb_ms, "tflops": bwd_flops / kb_ms / 1e9},
         "block_map": {"ms": km_ms, "gbs": 2 * tensor_bytes / km_ms / 1e6},
     }
+    if bwd:
+        kernels["sparse_bwd_dq_dkdv"] = {"ms": kb_ms, "tflops": bwd_flops / kb_ms / 1e9}
+    # DRAM bytes per launch from the committed ncu captures (profiles/tcgen05_sparse_kernels_c3.md,
+    # profiles/sage_fwd_tc_c4.md): dram__bytes_read.sum + dram__bytes_write.sum; null where not captured
+    traffic_table = {("c3", "sparse_fwd"): 386.1e6, ("c3", "sparse_bwd_dq_dkdv"): 494.8e6 + 588.1e6,
+                     ("c4", "sparse_fwd"): 1.925e9}
     dom = "sparse_bwd_dq_dkdv" if kb_ms >= kf_ms else "sparse_fwd"
     achieved = kernels[dom]["tflops"]
     roofline = {"kernel": dom, "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
-                "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                "traffic": traffic_table.get((w.name, dom)),
                 "peak_source": peaks["source"] + " burst (kernel timed alone)",
                 "algorithmic_flops_per_launch": bwd_flops if dom != "sparse_fwd" else fwd_flops}
 
-    dense_fb = w.dense_equiv_flops(True)
+    dense_fb = w.dense_equiv_flops(bwd)
     n_units_total = world * w.units
     value = world * dense_fb / ms / 1e9
     line = {
-        "metric": "sla_fwd_bwd_dense_equiv_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "metric": "sla_fwd_bwd_dense_equiv_tflops" if bwd else "sla_fwd_dense_equiv_tflops", "value": value,
+        "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "vs_baseline": None, "dtype": "int8/e4m3" if w.quantized else "bf16", "data": "synthetic",
         "config": {"workload": w.name, "B_per_gpu": w.B, "H": w.H, "L": w.L, "D": w.D, "BLKQ": w.BLKQ,
                    "BLKK": w.BLKK, "topk": w.topk, "topk_blocks": w.topk_blocks, "feature_map": w.feature,
                    "global_units": n_units_total, "parallelism": f"bh-shard x{world}",
@@ -403,24 +439,26 @@ def main():
                    "impl": "mma.sync" if args.legacy_mma else "default"},
         "fwd_ms": fwd_ms, "fwd_bwd_ms": ms,
         "fwd_dense_equiv_tflops": world * w.dense_equiv_flops(False) / fwd_ms / 1e9,
-        "sparse_actual_tflops": world * (w.sparse_flops(True) + w.linear_flops(True)) / ms / 1e9,
+        "sparse_actual_tflops": world * (w.sparse_flops(bwd) + w.linear_flops(bwd)) / ms / 1e9,
         "e2e": {"value": world * dense_fb / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": 4 * tensor_bytes, "d2h_bytes_per_step": 4 * tensor_bytes},
+                "h2d_bytes_per_step": (4 if bwd else 3) * tensor_bytes,
+                "d2h_bytes_per_step": (4 if bwd else 1) * tensor_bytes},
         "gpu_launches": int(launches), "clocks": clocks, "kernels": kernels, "roofline": roofline,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        _use_all_host_threads()
         sample = cpu_sample(w)
-        cpu_reference_step(w, sample)
+        cpu_reference_step(w, sample, bwd)
         ts, t_end = [], time.perf_counter() + 15.0
         while len(ts) < 2 or (time.perf_counter() < t_end and len(ts) < 8):
-            ts.append(cpu_reference_step(w, sample))
+            ts.append(cpu_reference_step(w, sample, bwd))
         sec = sum(ts) / len(ts)
         line["cpu_baseline"] = {"value": dense_fb / w.units / sec / 1e12, "unit": "TFLOP/s",
                                 "cores": torch.get_num_threads(), "kind": "port",
                                 "sample": f"1 of {w.units} (batch,head) units x {len(ts)} repeats, "
                                           f"forward+backward incl. block map ({sec:.2f} s each)"}
-    if rank == 0 and world == 1 and not args.no_baselines:
-        line["gpu_baselines"] = gpu_baselines(w, q, k, v, do, W, b, max(3, args.steps // 2), 3)
+    if rank == 0 and world == 1 and not args.no_baselines and not w.quantized and bwd:
+        line["gpu_baselines"] = gpu_baselines(w, q, k, v, do, W, b, max(3, min(10, args.steps // 2)), 3)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
