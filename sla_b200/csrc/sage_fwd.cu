@@ -151,43 +151,49 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else if (warp == 5) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0 && !*abortp) {
+    // All 32 lanes run the control flow; one elected lane issues the tcgen05 instructions.
+    if (!*abortp) {
       const uint32_t q_lo = desc_lo(sQ, 16);
       auto issue_s = [&](int j) {
         const uint32_t k_lo = desc_lo(sK0 + (j % NS) * KV_BYTES, 16);
         const uint32_t d = tmem + COL_S + (j & 1) * 64;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)   // K = 32 int8 = 32 bytes per step inside the 128-byte row
-          mma_ss_i8(d, q_lo + ((kk * 32) >> 4), k_lo + ((kk * 32) >> 4), IDESC_S, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk)   // K = 32 int8 = 32 bytes per step inside the 128-byte row
+            mma_ss_i8(d, q_lo + ((kk * 32) >> 4), k_lo + ((kk * 32) >> 4), IDESC_S, kk > 0 ? 1u : 0u);
+          tc_commit(BAR(B_S + (j & 1)));
+          tc_commit(BAR(B_KE + j % NS));
+        }
+        __syncwarp();
       };
-      bool ok = mbar_wait(BAR(B_Q), 0, kSErrQ, p.err) && mbar_wait(BAR(B_K), 0, kSErrK, p.err);
+      bool ok = warp_all(mbar_wait(BAR(B_Q), 0, kSErrQ, p.err) && mbar_wait(BAR(B_K), 0, kSErrK, p.err));
       if (ok) {
         tc_fence_after();
         issue_s(0);
-        tc_commit(BAR(B_S));
-        tc_commit(BAR(B_KE));
       }
       for (int j = 0; ok && j < n_ent; ++j) {
         if (j + 1 < n_ent) {
-          ok = mbar_wait(BAR(B_K + (j + 1) % NS), ((j + 1) / NS) & 1, kSErrK, p.err);
+          ok = warp_all(mbar_wait(BAR(B_K + (j + 1) % NS), ((j + 1) / NS) & 1, kSErrK, p.err));
           if (!ok) break;
           tc_fence_after();
           issue_s(j + 1);
-          tc_commit(BAR(B_S + ((j + 1) & 1)));
-          tc_commit(BAR(B_KE + (j + 1) % NS));
         }
-        ok = mbar_wait(BAR(B_P + (j & 1)), (j >> 1) & 1, kSErrP, p.err) &&
-             mbar_wait(BAR(B_V + j % NS), (j / NS) & 1, kSErrV, p.err);
-        if (!ok || *abortp) { ok = false; break; }
+        ok = warp_all(mbar_wait(BAR(B_P + (j & 1)), (j >> 1) & 1, kSErrP, p.err) &&
+                      mbar_wait(BAR(B_V + j % NS), (j / NS) & 1, kSErrV, p.err) && !*abortp);
+        if (!ok) break;
         tc_fence_after();
         // B = V8_j rows [32 kk, +32): MN-major, one 128-byte atom per row, 8-row groups 1024 B apart
         const uint32_t v_lo = desc_lo(sV0 + (j % NS) * KV_BYTES, KV_BYTES);
         const uint32_t pa = tmem + COL_S + (j & 1) * 64;   // P_j: four e4m3 per column, 16 columns
+        const uint32_t acc_on = j > 0 ? 1u : 0u;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk)
-          mma_ts_f8(tmem + COL_O, pa + kk * 8, v_lo + ((kk * 4096) >> 4), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(BAR(B_VE + j % NS));
-        tc_commit(BAR(B_PV));
+          for (int kk = 0; kk < 2; ++kk)
+            mma_ts_f8(tmem + COL_O, pa + kk * 8, v_lo + ((kk * 4096) >> 4), IDESC_PV, kk > 0 ? 1u : acc_on);
+          tc_commit(BAR(B_VE + j % NS));
+          tc_commit(BAR(B_PV));
+        }
+        __syncwarp();
       }
       if (!ok) *abortp = 1;
     }

@@ -77,10 +77,13 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   constexpr uint32_t IDESC_T = idesc_f16(FMT, 128, 64, 0, 0);
   constexpr uint32_t IDESC_ACC = idesc_f16(FMT, 128, D, 0, 1);
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr int COL_ACC1 = 0, COL_ACC2 = D, COL_T = KVS ? 2 * D : D;
+  // dQ variant: the stationary Q and dO tiles are also copied into TMEM (16-bit, D/2 columns each) so
+  // that the score GEMMs read their A operand from tensor memory instead of re-reading 4 KB of shared
+  // memory per k-step.
+  constexpr int COL_ACC1 = 0, COL_ACC2 = D, COL_X1 = D, COL_X2 = D + D / 2, COL_T = 2 * D;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * NS + 6];
+  __shared__ __align__(8) uint64_t bars[2 * NS + 7];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_n_entries;
   __shared__ int s_abort;
@@ -101,7 +104,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
   // 0 x_full | 1..NS y_full | NS+1..2NS y_empty | then t_full[2], c_full[2], acc_done
-  constexpr int B_X = 0, B_YF = 1, B_YE = 1 + NS, B_T = 1 + 2 * NS, B_C = 3 + 2 * NS, B_ACC = 5 + 2 * NS;
+  constexpr int B_X = 0, B_YF = 1, B_YE = 1 + NS, B_T = 1 + 2 * NS, B_C = 3 + 2 * NS, B_ACC = 5 + 2 * NS, B_XT = 6 + 2 * NS;
 
   if (tid == 0) {
     s_abort = *reinterpret_cast<volatile int*>(p.err) != 0;
@@ -115,6 +118,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       mbar_init(BAR(B_C + b), 256);
     }
     mbar_init(BAR(B_ACC), 1);
+    mbar_init(BAR(B_XT), 512);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -211,64 +215,82 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     }
   } else if (warp == 17) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0 && !*abortp) {
+    // All 32 lanes run the control flow; one elected lane issues the tcgen05 instructions.
+    if (!*abortp) {
+      long long* trm = lane == 0 ? tr : nullptr;
       const uint32_t x1_lo = desc_lo(sX1, 16), x2_lo = desc_lo(sX2, 16);
       auto issue_t = [&](int j) {
         const int s = j % NS, b = j & 1;
         const uint32_t y1_lo = desc_lo(sY0 + s * 2 * Y_BYTES, 16), y2_lo = desc_lo(sY0 + s * 2 * Y_BYTES + Y_BYTES, 16);
         const uint32_t t1 = tmem + COL_T + b * 128, t2 = t1 + 64;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss(t1, x1_lo + (((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4), y1_lo + (((kk >> 2) * Y_SLAB + (kk & 3) * 32) >> 4),
-                 IDESC_T, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t yo = ((kk >> 2) * Y_SLAB + (kk & 3) * 32) >> 4;
+            if (KVS) mma_ss(t1, x1_lo + (((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4), y1_lo + yo, IDESC_T, kk > 0 ? 1u : 0u);
+            else mma_ts(t1, tmem + COL_X1 + kk * 8, y1_lo + yo, IDESC_T, kk > 0 ? 1u : 0u);
+          }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss(t2, x2_lo + (((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4), y2_lo + (((kk >> 2) * Y_SLAB + (kk & 3) * 32) >> 4),
-                 IDESC_T, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t yo = ((kk >> 2) * Y_SLAB + (kk & 3) * 32) >> 4;
+            if (KVS) mma_ss(t2, x2_lo + (((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4), y2_lo + yo, IDESC_T, kk > 0 ? 1u : 0u);
+            else mma_ts(t2, tmem + COL_X2 + kk * 8, y2_lo + yo, IDESC_T, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(BAR(B_T + b));
+        }
+        __syncwarp();
       };
-      bool ok = mbar_wait(BAR(B_X), 0, kBErrX, p.err);
+      bool ok = warp_all(mbar_wait(BAR(B_X), 0, kBErrX, p.err));
+      if (ok && !KVS) {
+        ok = warp_all(mbar_wait(BAR(B_XT), 0, kBErrX, p.err));   // Q, dO copied to tensor memory by the compute groups
+        tc_fence_after();
+      }
       for (int j = 0; ok && j < 2 && j < n_ent; ++j) {
-        ok = mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrYFull, p.err);
+        ok = warp_all(mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrYFull, p.err));
         if (!ok) break;
         tc_fence_after();
         issue_t(j);
-        tc_commit(BAR(B_T + (j & 1)));
       }
       for (int j = 0; ok && j < n_ent; ++j) {
         const int s = j % NS, b = j & 1;
-        trace_ev(tr, 1, j, 0);
-        ok = mbar_wait(BAR(B_C + b), (j >> 1) & 1, kBErrCFull, p.err);
-        if (!ok || *abortp) { ok = false; break; }
-        trace_ev(tr, 1, j, 1);
+        trace_ev(trm, 1, j, 0);
+        ok = warp_all(mbar_wait(BAR(B_C + b), (j >> 1) & 1, kBErrCFull, p.err) && !*abortp);
+        if (!ok) break;
+        trace_ev(trm, 1, j, 1);
         tc_fence_after();
         // streamed tiles as MN-major B operands: 8-row groups 1024 B apart, 64-column slabs Y_SLAB apart
         const uint32_t y1_lo = desc_lo(sY0 + s * 2 * Y_BYTES, Y_SLAB), y2_lo = desc_lo(sY0 + s * 2 * Y_BYTES + Y_BYTES, Y_SLAB);
         const uint32_t a1 = tmem + COL_T + b * 128, a2 = a1 + 64;   // 16-bit operands written by the compute groups
         const uint32_t acc_on = j > 0 ? 1u : 0u;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          // 16-bit operand columns: elements [0,32) packed at +0..15, elements [32,64) at +32..47
-          const uint32_t ao = (kk >> 1) * 32 + (kk & 1) * 8;
-          const uint32_t ko = (kk * 2048) >> 4;
-          if (KVS) {
-            mma_ts(tmem + COL_ACC2, a1 + ao, y2_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dV += P^T dO_i  (kernel.py:220)
-            mma_ts(tmem + COL_ACC1, a2 + ao, y1_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dK += dS^T Q_i (kernel.py:225)
-          } else {
-            mma_ts(tmem + COL_ACC1, a2 + ao, y1_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dQ += dS K_j   (kernel.py:163)
+          for (int kk = 0; kk < 4; ++kk) {
+            // 16-bit operand columns: elements [0,32) packed at +0..15, elements [32,64) at +32..47
+            const uint32_t ao = (kk >> 1) * 32 + (kk & 1) * 8;
+            const uint32_t ko = (kk * 2048) >> 4;
+            if (KVS) {
+              mma_ts(tmem + COL_ACC2, a1 + ao, y2_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dV += P^T dO_i  (kernel.py:220)
+              mma_ts(tmem + COL_ACC1, a2 + ao, y1_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dK += dS^T Q_i (kernel.py:225)
+            } else {
+              mma_ts(tmem + COL_ACC1, a2 + ao, y1_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dQ += dS K_j   (kernel.py:163)
+            }
           }
+          tc_commit(BAR(B_YE + s));
         }
-        tc_commit(BAR(B_YE + s));
-        trace_ev(tr, 1, j, 2);
+        __syncwarp();
+        trace_ev(trm, 1, j, 2);
         if (j + 2 < n_ent) {
-          ok = mbar_wait(BAR(B_YF + (j + 2) % NS), ((j + 2) / NS) & 1, kBErrYFull, p.err);
+          ok = warp_all(mbar_wait(BAR(B_YF + (j + 2) % NS), ((j + 2) / NS) & 1, kBErrYFull, p.err));
           if (!ok) break;
           tc_fence_after();
           issue_t(j + 2);
-          tc_commit(BAR(B_T + b));
         }
-        trace_ev(tr, 1, j, 3);
+        trace_ev(trm, 1, j, 3);
       }
-      if (ok) tc_commit(BAR(B_ACC));
+      if (ok) {
+        if (elect_one()) tc_commit(BAR(B_ACC));
+        __syncwarp();
+      }
       if (!ok) *abortp = 1;
     }
   } else {
@@ -287,6 +309,27 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     }
     const bool key_ok = grow < L;                           // KVS: keys past the end give P = 0 (kernel.py:216)
     bool ok = !*abortp;
+    if (!KVS && ok) {
+      // stationary tiles -> TMEM: groups 0,1 copy the two column halves of Q, groups 2,3 those of dO
+      ok = mbar_wait(BAR(B_X), 0, kBErrX, p.err);
+      if (ok) {
+        constexpr int NCH = D / 16;                           // 16-byte chunks per thread (D/2 elements)
+        const uint32_t src = ((wg >> 1) ? sX2 : sX1) + (((wg & 1) * (D / 2)) >> 6) * X_SLAB + row * 128;
+        const int chunk0 = (((wg & 1) * (D / 2)) & 63) >> 3;
+        uint32_t xr[NCH * 4];
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          const uint32_t addr = src + (((chunk0 + c) ^ (row & 7)) << 4);
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n"
+                       : "=r"(xr[4 * c]), "=r"(xr[4 * c + 1]), "=r"(xr[4 * c + 2]), "=r"(xr[4 * c + 3]) : "r"(addr));
+        }
+        const uint32_t dst = tmem + lane_addr + ((wg >> 1) ? COL_X2 : COL_X1) + (wg & 1) * (D / 4);
+        if constexpr (NCH * 4 == 32) tmem_st_x32(dst, xr); else tmem_st_x16(dst, xr);
+        tmem_wait_st();
+        tc_fence_before();
+      }
+      mbar_arrive(BAR(B_XT));
+    }
     for (int j = buf; ok && j < n_ent; j += 2) {
       long long* trc = ((warp & 3) == 0 && lane == 0) ? tr : nullptr;
       trace_ev(trc, 2 + ch, j, 0);

@@ -187,47 +187,50 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   } else if (warp == 5) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0 && !*abortp) {
+    // All 32 lanes run the control flow; one elected lane issues the tcgen05 instructions.
+    if (!*abortp) {
       const uint32_t q_lo = desc_lo(sQ, 16);
       auto issue_s = [&](int j) {
         const uint32_t k_lo = desc_lo(sK0 + (j & 1) * KV_BYTES, 16);
         const uint32_t d = tmem + COL_S + (j & 1) * 64;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          // k-step kk: 32 bytes further inside the 128-byte swizzle atom, next slab every 4 steps
-          constexpr int dummy = 0; (void)dummy;
-          mma_ss(d, q_lo + (((kk >> 2) * Q_SLAB + (kk & 3) * 32) >> 4), k_lo + (((kk >> 2) * KV_SLAB + (kk & 3) * 32) >> 4),
-                 IDESC_S, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < D / 16; ++kk)   // k-step: 32 bytes further inside the swizzle atom, next slab every 4 steps
+            mma_ss(d, q_lo + (((kk >> 2) * Q_SLAB + (kk & 3) * 32) >> 4), k_lo + (((kk >> 2) * KV_SLAB + (kk & 3) * 32) >> 4),
+                   IDESC_S, kk > 0 ? 1u : 0u);
+          tc_commit(BAR(B_S + (j & 1)));
+          tc_commit(BAR(B_KE + (j & 1)));
         }
+        __syncwarp();
       };
-      bool ok = mbar_wait(BAR(B_Q), 0, kErrQ, p.err) && mbar_wait(BAR(B_K), 0, kErrKFull, p.err);
+      bool ok = warp_all(mbar_wait(BAR(B_Q), 0, kErrQ, p.err) && mbar_wait(BAR(B_K), 0, kErrKFull, p.err));
       if (ok) {
         tc_fence_after();
         issue_s(0);
-        tc_commit(BAR(B_S));
-        tc_commit(BAR(B_KE));
       }
       for (int j = 0; ok && j < n_ent; ++j) {
         if (j + 1 < n_ent) {
-          ok = mbar_wait(BAR(B_K + ((j + 1) & 1)), ((j + 1) >> 1) & 1, kErrKFull, p.err);
+          ok = warp_all(mbar_wait(BAR(B_K + ((j + 1) & 1)), ((j + 1) >> 1) & 1, kErrKFull, p.err));
           if (!ok) break;
           tc_fence_after();
           issue_s(j + 1);
-          tc_commit(BAR(B_S + ((j + 1) & 1)));
-          tc_commit(BAR(B_KE + ((j + 1) & 1)));
         }
-        ok = mbar_wait(BAR(B_P + (j & 1)), (j >> 1) & 1, kErrPFull, p.err) &&
-             mbar_wait(BAR(B_V + (j & 1)), (j >> 1) & 1, kErrVFull, p.err);
-        if (!ok || *abortp) { ok = false; break; }
+        ok = warp_all(mbar_wait(BAR(B_P + (j & 1)), (j >> 1) & 1, kErrPFull, p.err) &&
+                      mbar_wait(BAR(B_V + (j & 1)), (j >> 1) & 1, kErrVFull, p.err) && !*abortp);
+        if (!ok) break;
         tc_fence_after();
         // B = V_j rows [16 kk, +16): MN-major, 8-row groups 1024 B apart, 64-column slabs KV_SLAB apart
         const uint32_t v_lo = desc_lo(sV0 + (j & 1) * KV_BYTES, KV_SLAB);
         const uint32_t pa = tmem + COL_S + (j & 1) * 64;   // P_j: 16-bit pairs packed over S_j
+        const uint32_t acc_on = j > 0 ? 1u : 0u;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_ts(tmem + COL_O, pa + kk * 8, v_lo + ((kk * 2048) >> 4), IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(BAR(B_E + (j & 1)));
-        tc_commit(BAR(B_PV));
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ts(tmem + COL_O, pa + kk * 8, v_lo + ((kk * 2048) >> 4), IDESC_PV, kk > 0 ? 1u : acc_on);
+          tc_commit(BAR(B_E + (j & 1)));
+          tc_commit(BAR(B_PV));
+        }
+        __syncwarp();
       }
       if (!ok) *abortp = 1;
     }
