@@ -12,6 +12,7 @@ namespace {
 int check_common(const sla_shape* s) {
   int rc = validate_shape(s);
   if (rc != SLA_OK) return rc;
+  if (!(softmax_scale(s) > 0.f)) return SLA_ERR_UNSUPPORTED;   // the kernels take row maxima before scaling
   return check_device_arch();
 }
 

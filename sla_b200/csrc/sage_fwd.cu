@@ -179,7 +179,7 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           issue_s(j + 1);
         }
         ok = warp_all(mbar_wait(BAR(B_P + (j & 1)), (j >> 1) & 1, kSErrP, p.err) &&
-                      mbar_wait(BAR(B_V + j % NS), (j / NS) & 1, kSErrV, p.err) && !*abortp);
+                      mbar_wait(BAR(B_V + j % NS), (j / NS) & 1, kSErrV, p.err));
         if (!ok) break;
         tc_fence_after();
         // B = V8_j rows [32 kk, +32): MN-major, one 128-byte atom per row, 8-row groups 1024 B apart

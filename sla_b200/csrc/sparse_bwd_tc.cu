@@ -254,7 +254,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       for (int j = 0; ok && j < n_ent; ++j) {
         const int s = j % NS, b = j & 1;
         trace_ev(trm, 1, j, 0);
-        ok = warp_all(mbar_wait(BAR(B_C + b), (j >> 1) & 1, kBErrCFull, p.err) && !*abortp);
+        ok = warp_all(mbar_wait(BAR(B_C + b), (j >> 1) & 1, kBErrCFull, p.err));
         if (!ok) break;
         trace_ev(trm, 1, j, 1);
         tc_fence_after();

@@ -216,7 +216,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           issue_s(j + 1);
         }
         ok = warp_all(mbar_wait(BAR(B_P + (j & 1)), (j >> 1) & 1, kErrPFull, p.err) &&
-                      mbar_wait(BAR(B_V + (j & 1)), (j >> 1) & 1, kErrVFull, p.err) && !*abortp);
+                      mbar_wait(BAR(B_V + (j & 1)), (j >> 1) & 1, kErrVFull, p.err));
         if (!ok) break;
         tc_fence_after();
         // B = V_j rows [16 kk, +16): MN-major, 8-row groups 1024 B apart, 64-column slabs KV_SLAB apart
@@ -256,14 +256,23 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld_x64(s_addr, sv);
         tmem_wait_ld();
         const int valid = L - (entry & 0x0fffffff) * 64;     // keys of this block that exist (kernel.py:57)
-        float mx = -INFINITY;
+        // row maximum of the raw scores (the scale is positive, so it commutes with max); four
+        // independent chains keep the dependent-issue latency off the critical path
+        if (valid < 64) {                                       // kernel.py:61-62: keys past the end
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float x = __uint_as_float(sv[c]) * sc;
-          if (valid < 64 && c >= valid) x = -INFINITY;       // kernel.py:61-62
-          sv[c] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
+          for (int c = 0; c < 64; ++c)
+            if (c >= valid) sv[c] = 0xff800000u;                // -inf
         }
+        float mx0 = __uint_as_float(sv[0]), mx1 = __uint_as_float(sv[1]);
+        float mx2 = __uint_as_float(sv[2]), mx3 = __uint_as_float(sv[3]);
+#pragma unroll
+        for (int c = 4; c < 64; c += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sv[c]));
+          mx1 = fmaxf(mx1, __uint_as_float(sv[c + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sv[c + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sv[c + 3]));
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc;
         m_true = fmaxf(m_true, mx);
         const bool need = m_true > m_used + kRescaleThreshold;   // also true on the first active block
         if (j > 0 && __any_sync(0xffffffffu, need)) {
@@ -285,14 +294,19 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           l *= ex2(m_used - m_true);
           m_used = m_true;
         }
-        float rs = 0.f;
+        float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+        const float neg_m = -m_used;
 #pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          float p0 = ex2(__uint_as_float(sv[c]) - m_used);
-          float p1 = ex2(__uint_as_float(sv[c + 1]) - m_used);
-          rs += p0 + p1;
+        for (int c = 0; c < 64; c += 4) {
+          float p0 = ex2(fmaf(__uint_as_float(sv[c]), sc, neg_m));          // exp2(s * scale * log2e - m)
+          float p1 = ex2(fmaf(__uint_as_float(sv[c + 1]), sc, neg_m));
+          float p2 = ex2(fmaf(__uint_as_float(sv[c + 2]), sc, neg_m));
+          float p3 = ex2(fmaf(__uint_as_float(sv[c + 3]), sc, neg_m));
+          rs0 += p0; rs1 += p1; rs2 += p2; rs3 += p3;
           pk[c >> 1] = Elem<T>::pack2(p0, p1);              // P rounded to T before P.V (kernel.py:71)
+          pk[(c >> 1) + 1] = Elem<T>::pack2(p2, p3);
         }
+        const float rs = (rs0 + rs1) + (rs2 + rs3);
         l += rs;
       } else {
 #pragma unroll
