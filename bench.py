@@ -314,9 +314,15 @@ def main():
     # ---- main timed region: exactly K forward+backward steps ----
     sampler = ClockSampler(local_rank)
     sampler.start()
+    def check_device(where):
+        code = _lib.poll_device_error()
+        if code:
+            raise RuntimeError(f"device-side error {code} of a tcgen05 kernel during {where}: no number reported")
+
     for _ in range(args.warmup):
         step_fwdbwd()
     sync()
+    check_device("warm-up")
     l0 = _lib.lib.sla_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler.mark_begin()
@@ -328,6 +334,7 @@ def main():
     sampler.mark_end()
     clocks = sampler.stop()
     launches = _lib.lib.sla_launch_count() - l0
+    check_device("the timed region")
     ms = e0.elapsed_time(e1) / args.steps
     if world > 1:
         t = torch.tensor([ms], dtype=torch.float64, device=dev)

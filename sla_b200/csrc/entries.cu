@@ -104,13 +104,8 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   if (rc != SLA_OK) return rc;
   FwdParams p = make_fwd(s, q, k, v, lut, o, o_s, lse, lin_state, wbits);
   if (legacy) return run_sparse_fwd_mma(s, p, true, st);
-  // tcgen05 sparse branch into o_s (or into o when the caller keeps no copy), then the streaming
-  // read-out adds the projected linear branch in place
-  FwdParams ps = make_fwd(s, q, k, v, lut, o_s ? o_s : o, nullptr, lse, nullptr, nullptr);
-  rc = run_sparse_fwd_tc(s, ps, st);
-  if (rc != SLA_OK) return rc;
-  p.o_s = o_s ? o_s : o;
-  return run_linear_readout(s, p, st);
+  // tcgen05 sparse branch with the linear read-out, proj_l and the final sum fused into its epilogue
+  return run_sparse_fwd_tc(s, p, st);
 }
 
 static int sparse_bwd_impl(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s,

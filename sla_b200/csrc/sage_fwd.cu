@@ -45,7 +45,7 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 enum : int { kSErrQ = 301, kSErrK = 302, kSErrV = 303, kSErrEmpty = 304, kSErrS = 305, kSErrP = 306,
              kSErrPv = 307, kSErrDrain = 308 };
 
-constexpr float kPScale = 256.0f;   // P in [0,1] is multiplied by this before rounding to e4m3 (max 448)
+constexpr float kPShift = 8.0f;     // P in [0,1] is multiplied by 2^8 before rounding to e4m3 (max 448)
 
 // D = 128 only: rows of the 8-bit tensors are exactly one 128-byte swizzle atom.
 template <typename T>
@@ -62,7 +62,7 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   constexpr int COL_O = 0, COL_S = D;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[4 * NS + 6];
+  __shared__ __align__(8) uint64_t bars[4 * NS + 7];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ float s_vscale[D];
@@ -82,7 +82,8 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  // q_full | k_full[NS] | v_full[NS] | k_empty[NS] | v_empty[NS] | s_full[2] | p_full[2] | pv_done
+  // q_full | k_full[NS] | v_full[NS] | k_empty[NS] | v_empty[NS] | s_full[2] | p_full[2] | pv_done[2]
+  // (entry j signals pv_done[j & 1]: a parity wait only tells neighbouring phases apart)
   constexpr int B_Q = 0, B_K = 1, B_V = 1 + NS, B_KE = 1 + 2 * NS, B_VE = 1 + 3 * NS, B_S = 1 + 4 * NS,
                 B_P = 3 + 4 * NS, B_PV = 5 + 4 * NS;
 
@@ -95,6 +96,7 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) { mbar_init(BAR(B_S + b), 1); mbar_init(BAR(B_P + b), 128); }
     mbar_init(BAR(B_PV), 1);
+    mbar_init(BAR(B_PV + 1), 1);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -191,7 +193,7 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           for (int kk = 0; kk < 2; ++kk)
             mma_ts_f8(tmem + COL_O, pa + kk * 8, v_lo + ((kk * 4096) >> 4), IDESC_PV, kk > 0 ? 1u : acc_on);
           tc_commit(BAR(B_VE + j % NS));
-          tc_commit(BAR(B_PV));
+          tc_commit(BAR(B_PV + (j & 1)));
         }
         __syncwarp();
       }
@@ -215,17 +217,25 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tmem_wait_ld();
       const float sc = sq * sk_list[j];
       const int valid = L - ulist[j] * 64;
-      float mx = -INFINITY;
+      if (valid < 64) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float x = static_cast<float>(static_cast<int32_t>(sv[c])) * sc;
-        if (valid < 64 && c >= valid) x = -INFINITY;
-        sv[c] = __float_as_uint(x);
-        mx = fmaxf(mx, x);
+        for (int c = 0; c < 64; ++c)
+          if (c >= valid) sv[c] = 0x80000000u;          // most negative integer: exp2 gives 0
       }
+      // row maximum on the integer scores (the dequantisation scale is positive); four chains
+      int32_t im0 = static_cast<int32_t>(sv[0]), im1 = static_cast<int32_t>(sv[1]);
+      int32_t im2 = static_cast<int32_t>(sv[2]), im3 = static_cast<int32_t>(sv[3]);
+#pragma unroll
+      for (int c = 4; c < 64; c += 4) {
+        im0 = max(im0, static_cast<int32_t>(sv[c]));
+        im1 = max(im1, static_cast<int32_t>(sv[c + 1]));
+        im2 = max(im2, static_cast<int32_t>(sv[c + 2]));
+        im3 = max(im3, static_cast<int32_t>(sv[c + 3]));
+      }
+      const float mx = static_cast<float>(max(max(im0, im1), max(im2, im3))) * sc;
       const bool need = mx > m_used;            // exact running maximum: P stays in [0, 1]
       if (j > 0 && __any_sync(0xffffffffu, need)) {
-        if (!mbar_wait(BAR(B_PV), (j - 1) & 1, kSErrPv, p.err)) { ok = false; break; }
+        if (!mbar_wait(BAR(B_PV + ((j - 1) & 1)), ((j - 1) >> 1) & 1, kSErrPv, p.err)) { ok = false; break; }
         tc_fence_after();
         const float alpha = need ? ex2s(m_used - mx) : 1.0f;
 #pragma unroll
@@ -243,28 +253,32 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         m_used = mx;
       }
       uint32_t pk[16];
-      float rs = 0.f;
+      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+      const float off = kPShift - m_used;               // P * 2^kPShift straight out of the exponent
 #pragma unroll
       for (int c = 0; c < 64; c += 4) {
-        float p0 = ex2s(__uint_as_float(sv[c]) - m_used), p1 = ex2s(__uint_as_float(sv[c + 1]) - m_used);
-        float p2 = ex2s(__uint_as_float(sv[c + 2]) - m_used), p3 = ex2s(__uint_as_float(sv[c + 3]) - m_used);
-        rs += (p0 + p1) + (p2 + p3);
-        pk[c >> 2] = pack_e4m3x4(p0 * kPScale, p1 * kPScale, p2 * kPScale, p3 * kPScale);
+        float p0 = ex2s(fmaf(static_cast<float>(static_cast<int32_t>(sv[c])), sc, off));
+        float p1 = ex2s(fmaf(static_cast<float>(static_cast<int32_t>(sv[c + 1])), sc, off));
+        float p2 = ex2s(fmaf(static_cast<float>(static_cast<int32_t>(sv[c + 2])), sc, off));
+        float p3 = ex2s(fmaf(static_cast<float>(static_cast<int32_t>(sv[c + 3])), sc, off));
+        rs0 += p0; rs1 += p1; rs2 += p2; rs3 += p3;
+        pk[c >> 2] = pack_e4m3x4(p0, p1, p2, p3);
       }
+      const float rs = (rs0 + rs1) + (rs2 + rs3);
       l += rs;
       tmem_st_x16(s_addr, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(BAR(B_P + b));
     }
-    if (ok && n_ent > 0) ok = mbar_wait(BAR(B_PV), (n_ent - 1) & 1, kSErrPv, p.err);
+    if (ok && n_ent > 0) ok = mbar_wait(BAR(B_PV + ((n_ent - 1) & 1)), ((n_ent - 1) >> 1) & 1, kSErrPv, p.err);
     if (!ok) *abortp = 1;
     asm volatile("bar.sync 1, 128;\n" ::: "memory");
     if (!*abortp) {
       tc_fence_after();
-      const float inv = 1.0f / (l * kPScale);
+      const float inv = 1.0f / l;                       // l carries the 2^kPShift of P
       const int grow = tile * 128 + row;
-      if (grow < L) p.lse[static_cast<size_t>(bh) * L + grow] = m_used + log2f(l);
+      if (grow < L) p.lse[static_cast<size_t>(bh) * L + grow] = m_used + log2f(l) - kPShift;
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t ov[32];

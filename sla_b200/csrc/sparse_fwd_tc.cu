@@ -35,6 +35,11 @@ struct TcFwdParams {
   int* err;
   int L, mb, topk, n_tiles;
   float scale_log2;
+  // fused linear branch (core.py:90,95-100); feature < 0: sparse branch only
+  int feature;             // sla_feature, or -1
+  int store_os;            // also store the sparse branch output through tmOs
+  const void* lin_state;   // [BH][2*D*D + D] T: H, z, H W^T
+  const void* wbits;       // [D*D + D] T: W, bias
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -45,13 +50,14 @@ __device__ __forceinline__ float ex2(float x) {
 
 enum : int {
   kErrQ = 101, kErrKFull = 102, kErrVFull = 103, kErrEmpty = 104, kErrSFull = 105, kErrPFull = 106,
-  kErrPvDone = 107, kErrDrain = 108
+  kErrPvDone = 107, kErrDrain = 108, kErrHw = 109, kErrPhi = 110, kErrLin = 111
 };
 
 template <typename T, int D, int BM>
 __global__ void __launch_bounds__(192, 2)
 sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                     const __grid_constant__ CUtensorMap tmOs, const __grid_constant__ CUtensorMap tmHW,
                      TcFwdParams p) {
   constexpr int SLABS = D / 64;                 // 64-column (128-byte) slabs per row
   constexpr int Q_SLAB = 128 * 128;             // bytes of one Q slab (128 rows x 128 B)
@@ -66,7 +72,8 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   constexpr float kRescaleThreshold = 8.0f;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[14];
+  __shared__ __align__(8) uint64_t bars[18];
+  __shared__ float s_z[D], s_bias[D];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_n_entries;
   __shared__ int s_abort;
@@ -86,8 +93,14 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  // 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 v_empty | 7,8 s_full | 9,10 p_full | 11 pv_done | 12,13 k_empty
-  constexpr int B_Q = 0, B_K = 1, B_V = 3, B_E = 5, B_S = 7, B_P = 9, B_PV = 11, B_KE = 12;
+  // 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 v_empty | 7,8 s_full | 9,10 p_full | 11,12 pv_done | 13,14 k_empty
+  // 15 hw_full (H W^T landed in the K stages) | 16 phi_full (phi(q) written over Q) | 17 lin_done
+  // pv_done alternates between two barriers (entry j -> barrier j & 1). A parity wait only tells
+  // neighbouring phases apart, and a softmax thread that skipped the rescale for a while knows no more
+  // than "P.V of entry j-2 is complete" when S_j arrives; with two barriers that is enough.
+  constexpr int B_Q = 0, B_K = 1, B_V = 3, B_E = 5, B_S = 7, B_P = 9, B_PV = 11, B_KE = 13;
+  constexpr int B_HW = 15, B_PHI = 16, B_LIN = 17;
+  const bool fused = p.feature >= 0;
 
   if (tid == 0) {
     s_abort = *reinterpret_cast<volatile int*>(p.err) != 0;  // an earlier CTA failed: do no work
@@ -101,6 +114,10 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(BAR(B_P + s), 128);
     }
     mbar_init(BAR(B_PV), 1);
+    mbar_init(BAR(B_PV + 1), 1);
+    mbar_init(BAR(B_HW), 1);
+    mbar_init(BAR(B_PHI), 128);
+    mbar_init(BAR(B_LIN), 1);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -110,6 +127,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       prefetch_tmap(&tmK);
       prefetch_tmap(&tmV);
       prefetch_tmap(&tmO);
+      if (fused) prefetch_tmap(&tmHW);
     }
     // Entry list: block index | bit 28 (upper half of the tile selects it) | bit 29 (lower half).
     // The LUT rows are first copied to shared memory with coalesced loads; a serial merge straight
@@ -142,6 +160,11 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (warp == 5) {
     tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
     tmem_relinquish();
+  }
+  if (fused && tid < D) {
+    const T* rec = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (2 * D * D + D);
+    s_z[tid] = Elem<T>::to_f(rec[D * D + tid]);
+    s_bias[tid] = Elem<T>::to_f(static_cast<const T*>(p.wbits)[D * D + tid]);
   }
   tc_fence_before();
   __syncthreads();
@@ -176,6 +199,20 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           mbar_expect_tx(BAR(B_V + s), KV_BYTES);
           for (int c = 0; c < SLABS; ++c) tma_load_3d(sV0 + s * KV_BYTES + c * KV_SLAB, &tmV, BAR(B_V + s), c * 64, row0, bh);
           issued_v = j + 1;
+        }
+      }
+      if (fused && !*abortp) {
+        // H W^T of this head (D x D) goes into the two K stages once the last S GEMMs have read them
+        bool free_k = true;
+        for (int j = max(0, n_ent - 2); free_k && j < n_ent; ++j)
+          free_k = mbar_wait(BAR(B_KE + (j & 1)), (j >> 1) & 1, kErrEmpty, p.err);
+        if (!free_k) *abortp = 1;
+        else {
+          mbar_expect_tx(BAR(B_HW), D * D * 2);
+          for (int r = 0; r < D / 64; ++r)
+            for (int c = 0; c < SLABS; ++c)
+              tma_load_3d(sK0 + r * KV_BYTES + c * KV_SLAB, &tmHW, BAR(B_HW), c * 64, r * 64, bh);
+          if (*abortp) mbar_wait(BAR(B_HW), 0, kErrDrain, p.err);
         }
       }
       if (*abortp) {
@@ -228,9 +265,25 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int kk = 0; kk < 4; ++kk)
             mma_ts(tmem + COL_O, pa + kk * 8, v_lo + ((kk * 2048) >> 4), IDESC_PV, kk > 0 ? 1u : acc_on);
           tc_commit(BAR(B_E + (j & 1)));
-          tc_commit(BAR(B_PV));
+          tc_commit(BAR(B_PV + (j & 1)));
         }
         __syncwarp();
+      }
+      if (ok && fused) {
+        // read-out of the linear branch: LIN[128 x D] = phi(Q) (H W^T) into the (now idle) S columns
+        ok = warp_all(mbar_wait(BAR(B_HW), 0, kErrHw, p.err) && mbar_wait(BAR(B_PHI), 0, kErrPhi, p.err));
+        if (ok) {
+          tc_fence_after();
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t hw_lo = desc_lo(sK0 + (kk >> 2) * KV_BYTES, KV_SLAB) + (((kk & 3) * 2048) >> 4);
+              mma_ss(tmem + COL_S, q_lo + (((kk >> 2) * Q_SLAB + (kk & 3) * 32) >> 4), hw_lo, IDESC_PV, kk > 0 ? 1u : 0u);
+            }
+            tc_commit(BAR(B_LIN));
+          }
+          __syncwarp();
+        }
       }
       if (!ok) *abortp = 1;
     }
@@ -277,7 +330,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const bool need = m_true > m_used + kRescaleThreshold;   // also true on the first active block
         if (j > 0 && __any_sync(0xffffffffu, need)) {
           // O holds sum_{j' < j} P V with the old reference maximum: wait for PV_{j-1}, then scale it
-          if (!mbar_wait(BAR(B_PV), (j - 1) & 1, kErrPvDone, p.err)) { ok = false; break; }
+          if (!mbar_wait(BAR(B_PV + ((j - 1) & 1)), ((j - 1) >> 1) & 1, kErrPvDone, p.err)) { ok = false; break; }
           tc_fence_after();
           const float alpha = need ? ex2(m_used - m_true) : 1.0f;
 #pragma unroll
@@ -317,7 +370,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_before();
       mbar_arrive(BAR(B_P + b));
     }
-    if (ok && n_ent > 0) ok = mbar_wait(BAR(B_PV), (n_ent - 1) & 1, kErrPvDone, p.err);
+    if (ok && n_ent > 0) ok = mbar_wait(BAR(B_PV + ((n_ent - 1) & 1)), ((n_ent - 1) >> 1) & 1, kErrPvDone, p.err);
     if (!ok) *abortp = 1;
     // all four softmax warps agree on whether the tile is good before touching the Q buffer
     asm volatile("bar.sync 1, 128;\n" ::: "memory");
@@ -326,32 +379,156 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const float inv = 1.0f / l;
       const int grow = tile * 128 + row;
       if (grow < L) p.lse[static_cast<size_t>(bh) * L + grow] = m_used + log2f(l);   // kernel.py:81
-      // O / l -> T, staged in the (idle) Q buffer in the same 128B-swizzled slab layout, then one TMA
-      // store per slab; rows past the end of the sequence are clipped by the copy engine.
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      // 16-byte chunk ch of this thread's row inside a 128-row tile at `tile_base` (128B-swizzled slabs)
+      auto chunk_addr = [&](uint32_t tile_base, int ch) {
+        return tile_base + (ch >> 3) * Q_SLAB + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
+      };
+      // O / l -> T for columns [c0, c0 + 32), written to the staging tile
+      auto stage_os = [&](uint32_t tile_base, int c0) {
         uint32_t ov[32];
         tmem_ld_x32(tmem + lane_addr + COL_O + c0, ov);
         tmem_wait_ld();
-        const uint32_t slab = sQ + (c0 >> 6) * Q_SLAB + row * 128;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           uint32_t w0 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
           uint32_t w1 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
           uint32_t w2 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
           uint32_t w3 = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
-          const int chunk = ((c0 & 63) >> 3) + q4;
-          const uint32_t addr = slab + ((chunk ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
-                       : "memory");
+          st_shared_v4(chunk_addr(tile_base, (c0 >> 3) + q4), w0, w1, w2, w3);
         }
-      }
-      fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 128;\n" ::: "memory");
-      if (tid == 0) {
-        for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO, sQ + c * Q_SLAB, c * 64, tile * 128, bh);
-        tma_store_commit();
-        tma_store_wait_all();
+      };
+      if (!fused) {
+        // staged in the (idle) Q buffer, then one TMA store per slab; rows past the end of the
+        // sequence are clipped by the copy engine
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) stage_os(sQ, c0);
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        if (tid == 0) {
+          for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO, sQ + c * Q_SLAB, c * 64, tile * 128, bh);
+          tma_store_commit();
+          tma_store_wait_all();
+        }
+      } else {
+        // ---- phi(q) of this thread's row, written over the row in the Q tile (core.py:90) ----
+        float dsum = 0.f;        // sum_d round(phi_d * z_d), core.py:95
+        auto emit_phi = [&](int ch, const float (&f)[8]) {
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            w[i] = Elem<T>::pack2(f[2 * i], f[2 * i + 1]);
+            const float2 ph = Elem<T>::unpack2(w[i]);
+            dsum += round_to<T>(ph.x * s_z[ch * 8 + 2 * i]) + round_to<T>(ph.y * s_z[ch * 8 + 2 * i + 1]);
+          }
+          st_shared_v4(chunk_addr(sQ, ch), w[0], w[1], w[2], w[3]);
+        };
+        auto load_x = [&](int ch, float (&f)[8]) {
+          uint32_t w0, w1, w2, w3;
+          ld_shared_v4(chunk_addr(sQ, ch), w0, w1, w2, w3);
+          float2 a = Elem<T>::unpack2(w0), b2 = Elem<T>::unpack2(w1), c = Elem<T>::unpack2(w2), d = Elem<T>::unpack2(w3);
+          f[0] = a.x; f[1] = a.y; f[2] = b2.x; f[3] = b2.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+        };
+        if (p.feature == SLA_PHI_SOFTMAX) {
+          float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+          for (int ch = 0; ch < D / 8; ++ch) {
+            float f[8];
+            load_x(ch, f);
+            mx0 = fmaxf(mx0, fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])));
+            mx1 = fmaxf(mx1, fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])));
+          }
+          const float mx = fmaxf(mx0, mx1);
+          // exp(x - max) in fp32 is parked in the idle S columns of this thread's TMEM lane
+          float e0 = 0.f, e1 = 0.f;
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t ev[32];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              float f[8];
+              load_x((c0 >> 3) + q4, f);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float e = __expf(f[i] - mx);
+                if (i & 1) e1 += e; else e0 += e;
+                ev[q4 * 8 + i] = __float_as_uint(e);
+              }
+            }
+            tmem_st_x32(tmem + lane_addr + COL_S + c0, ev);
+          }
+          tmem_wait_st();
+          const float inv_s = 1.f / (e0 + e1);
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t ev[32];
+            tmem_ld_x32(tmem + lane_addr + COL_S + c0, ev);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(ev[q4 * 8 + i]) * inv_s;
+              emit_phi((c0 >> 3) + q4, f);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < D / 8; ++ch) {
+            float f[8];
+            load_x(ch, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (p.feature == SLA_PHI_RELU) f[i] = fmaxf(f[i], 0.f);
+              else f[i] = f[i] > 0.f ? f[i] + 1.f : __expf(f[i]);      // elu(x) + 1
+            }
+            emit_phi(ch, f);
+          }
+        }
+        const float rden = 1.f / round_to<T>(1e-5f + round_to<T>(dsum));
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(BAR(B_PHI));
+        // ---- while the read-out GEMM runs: the sparse branch's own output, staged in the idle V stages ----
+        if (p.store_os) {
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) stage_os(sV0, c0);
+        }
+        const bool lin_ok = mbar_wait(BAR(B_LIN), 0, kErrLin, p.err);
+        if (lin_ok) {
+          tc_fence_after();
+          // o = o_s + round(lin / den + bias) (core.py:96-100), staged over phi(q)
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t ov[32], lv[32];
+            tmem_ld_x32(tmem + lane_addr + COL_O + c0, ov);
+            tmem_ld_x32(tmem + lane_addr + COL_S + c0, lv);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint32_t w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int c = q4 * 8 + 2 * i;
+                const float os0 = round_to<T>(__uint_as_float(ov[c]) * inv), os1 = round_to<T>(__uint_as_float(ov[c + 1]) * inv);
+                const float l0 = round_to<T>(__uint_as_float(lv[c]) * rden + s_bias[c0 + c]);
+                const float l1 = round_to<T>(__uint_as_float(lv[c + 1]) * rden + s_bias[c0 + c + 1]);
+                w[i] = Elem<T>::pack2(os0 + l0, os1 + l1);
+              }
+              st_shared_v4(chunk_addr(sQ, (c0 >> 3) + q4), w[0], w[1], w[2], w[3]);
+            }
+          }
+        } else {
+          *abortp = 1;
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        if (tid == 0 && !*abortp) {
+          if (p.store_os)
+            for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmOs, sV0 + c * Q_SLAB, c * 64, tile * 128, bh);
+          for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO, sQ + c * Q_SLAB, c * 64, tile * 128, bh);
+          tma_store_commit();
+          tma_store_wait_all();
+        }
       }
     }
   }
@@ -409,10 +586,16 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 int make_tmap_3d(CUtensorMap* out, const void* base, int dtype, int D, int L, int BH, int box_rows) {
+  return make_tmap_rows(out, base, dtype, D, L, BH, size_t(L) * D * 2, box_rows);
+}
+
+// (BH, L, D) 16-bit rows of D contiguous elements, consecutive heads `head_stride_bytes` apart
+int make_tmap_rows(CUtensorMap* out, const void* base, int dtype, int D, int L, int BH, size_t head_stride_bytes,
+                   int box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return SLA_ERR_CUDA;
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(BH)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(L) * D * 2};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(head_stride_bytes)};
   cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(out, dtype == SLA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
@@ -445,13 +628,24 @@ int make_tmap_3d_u8(CUtensorMap* out, const void* base, int row_bytes, int L, in
 template <typename T, int D, int BM>
 static int launch_tc(const sla_shape* s, const FwdParams& fp, cudaStream_t st) {
   const int bh = s->B * s->H;
-  CUtensorMap tq, tk, tv, to;
+  CUtensorMap tq, tk, tv, to, tos, thw;
   int rc;
   if ((rc = make_tmap_3d(&tq, fp.q, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
   if ((rc = make_tmap_3d(&tk, fp.k, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
   if ((rc = make_tmap_3d(&tv, fp.v, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
   if ((rc = make_tmap_3d(&to, fp.o, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
   tc::TcFwdParams p;
+  const bool fused = fp.lin_state != nullptr;
+  tos = to; thw = to;
+  p.feature = fused ? s->feature_map : -1;
+  p.store_os = fused && fp.o_s != nullptr && fp.o_s != fp.o;
+  p.lin_state = fp.lin_state; p.wbits = fp.wbits;
+  if (p.store_os && (rc = make_tmap_3d(&tos, fp.o_s, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  if (fused) {
+    // H W^T sits behind H and z in each head's record: D rows of D elements, records 2*D*D + D apart
+    const char* hw = static_cast<const char*>(fp.lin_state) + (size_t(D) * D + D) * 2;
+    if ((rc = make_tmap_rows(&thw, hw, s->dtype, D, D, bh, size_t(2 * D * D + D) * 2, 64)) != SLA_OK) return rc;
+  }
   p.err = tc_error_word();
   if (p.err == nullptr) return SLA_ERR_CUDA;
   p.lut = fp.lut; p.lse = fp.lse; p.L = s->L; p.mb = fp.mb; p.topk = fp.topk;
@@ -462,7 +656,7 @@ static int launch_tc(const sla_shape* s, const FwdParams& fp, cudaStream_t st) {
   const int smem = 1024 + tiles_bytes + 4 * fp.topk * 4 + 16;
   if (smem > 113 * 1024) return SLA_ERR_BAD_TOPK;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  kern<<<dim3(p.n_tiles, bh), 192, smem, st>>>(tq, tk, tv, to, p);
+  kern<<<dim3(p.n_tiles, bh), 192, smem, st>>>(tq, tk, tv, to, tos, thw, p);
   SLA_LAUNCH_OK();
   return SLA_OK;
 }

@@ -118,6 +118,13 @@ __device__ __forceinline__ bool elect_one() {
 }
 __device__ __forceinline__ bool warp_all(bool ok) { return __all_sync(0xffffffffu, ok) != 0; }
 
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
+}
+
 // ---- descriptors ----
 // Shared-memory matrix descriptor, 128-byte swizzle. Bits [0,14) address>>4, [16,30) leading byte
 // offset>>4, [32,46) stride byte offset>>4, [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
@@ -204,6 +211,8 @@ __host__ __device__ constexpr uint32_t idesc_e4m3(int M, int N, int b_mn_major) 
 // host: encode a 3-D tensor map (D, L, BH) of 16-bit elements with a (64, box_rows, 1) box and
 // 128-byte swizzle. Returns SLA_OK or SLA_ERR_CUDA.
 int make_tmap_3d(CUtensorMap* out, const void* base, int dtype, int D, int L, int BH, int box_rows);
+int make_tmap_rows(CUtensorMap* out, const void* base, int dtype, int D, int L, int BH, size_t head_stride_bytes,
+                   int box_rows);
 // host: same for 8-bit elements, rows of `row_bytes` (<= 128) bytes, box = (row_bytes, box_rows, 1).
 int make_tmap_3d_u8(CUtensorMap* out, const void* base, int row_bytes, int L, int BH, int box_rows);
 // host: address of the current device's error word (looked up once per device), or nullptr.
