@@ -169,18 +169,13 @@ int sla_bwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   lp.dz = reinterpret_cast<float*>(base + wb.dz);
   lp.dw_part = reinterpret_cast<float*>(base + wb.dw_part);
   lp.dw = dw; lp.dbias = dbias; lp.L = s->L; lp.nch = wb.nch; lp.rows = wb.rows;
-  if (legacy) {
-    // linear branch first (overwrites), then the mma.sync sparse kernels add their part
-    lp.accumulate = 0;
-    rc = run_linear_bwd(s, lp, st);
-    if (rc != SLA_OK) return rc;
-    return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 1, st);
-  }
-  // tcgen05 sparse kernels overwrite dq, dk, dv; the linear branch then adds its part
-  rc = sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 0, st);
+  // Linear branch first (plain stores), then the sparse kernels add their part: the tcgen05 kernels
+  // through TMA reduce-add stores, the mma.sync kernels by reading the tile back.
+  (void)legacy;
+  lp.accumulate = 0;
+  rc = run_linear_bwd(s, lp, st);
   if (rc != SLA_OK) return rc;
-  lp.accumulate = 1;
-  return run_linear_bwd(s, lp, st);
+  return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 1, st);
 }
 
 }  // extern "C"

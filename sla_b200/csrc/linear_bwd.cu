@@ -24,10 +24,9 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams 
   constexpr int TILE = D * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* sM = smem;         // H W^T = M^T, stored [i][n]
-  unsigned char* sQ = sM + TILE;    // Q rows, then dq staging, then phi(q)/den
-  unsigned char* sdY = sQ + TILE;
-  float* s_z = reinterpret_cast<float*>(sdY + TILE);  // [D]
-  float* s_rowc = s_z + D;                            // [D] dden*den per row of the tile
+  // two {Q, dY} buffers: the next row tile is copied in while this one is worked on
+  float* s_z = reinterpret_cast<float*>(smem + 5 * TILE);  // [D]
+  float* s_rowc = s_z + D;                                 // [D] dden*den per row of the tile
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -39,7 +38,7 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams 
   T* dqg = static_cast<T*>(p.dq) + head_off;
   const T* hs = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (2 * D * D + D);
   const T* mg = hs + D * D + D;
-  const uint32_t sM_a = smem_u32(sM), sQ_a = smem_u32(sQ), sdY_a = smem_u32(sdY);
+  const uint32_t sM_a = smem_u32(sM);
   const int m0 = warp * 16;
 
   load_tile_async<D, D>(sM_a, mg, 0, D, tid, NT);
@@ -52,11 +51,24 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams 
   float vec_acc = 0.f;   // thread tid < D: dz[tid]; tid >= D: db[tid - D]
 
   const int row_begin = ch * p.rows, row_end = min(L, row_begin + p.rows);
-  for (int row0 = row_begin; row0 < row_end; row0 += D) {
-    load_tile_async<D, D>(sQ_a, qg, row0, L, tid, NT);
-    load_tile_async<D, D>(sdY_a, dyg, row0, L, tid, NT);
+  auto prefetch = [&](int row0, int buf) {
+    const uint32_t a = smem_u32(smem + (1 + 2 * buf) * TILE);
+    load_tile_async<D, D>(a, qg, row0, L, tid, NT);
+    load_tile_async<D, D>(a + TILE, dyg, row0, L, tid, NT);
     cp_async_commit();
-    cp_async_wait<0>();
+  };
+  if (row_begin < row_end) prefetch(row_begin, 0);
+  int buf = 0;
+  for (int row0 = row_begin; row0 < row_end; row0 += D, buf ^= 1) {
+    unsigned char* sQ = smem + (1 + 2 * buf) * TILE;   // Q rows, then dq staging, then phi(q)/den
+    unsigned char* sdY = sQ + TILE;
+    const uint32_t sQ_a = smem_u32(sQ), sdY_a = smem_u32(sdY);
+    if (row0 + D < row_end) {          // the other buffer was released by the barrier that ended the last tile
+      prefetch(row0 + D, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
     __syncthreads();
 
     uint32_t pq[KS][4];
@@ -238,56 +250,72 @@ __global__ void dw_final_kernel(const float* __restrict__ dw_part, float* __rest
 }
 
 // ---------------------------------------------------------------------------------------------
-// Pass B: dk_lin, dv_lin for 64 key rows per CTA.
+// Pass B: dk_lin, dv_lin. A CTA keeps the head's dH in shared memory and streams its chunk of key rows
+// through two {K, V} buffers of 64 rows (the next tile is copied in while this one is worked on).
 // ---------------------------------------------------------------------------------------------
 template <typename T, int D, int FEAT>
 __global__ void __launch_bounds__(128) linear_bwd_kv_kernel(LinBwdParams p) {
   constexpr int NT = 128, KS = D / 16;
+  constexpr int T64 = 64 * D * 2;
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* sdH = smem;                  // [D][D]
-  unsigned char* sK = sdH + D * D * 2;        // [64][D]
-  unsigned char* sV = sK + 64 * D * 2;        // [64][D]
-  float* s_dz = reinterpret_cast<float*>(sV + 64 * D * 2);
+  float* s_dz = reinterpret_cast<float*>(smem + D * D * 2 + 4 * T64);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t = lane & 3;
-  const int bh = blockIdx.y, row0 = blockIdx.x * 64;
+  const int ch = blockIdx.x, bh = blockIdx.y;
   const int L = p.L;
   const size_t head_off = static_cast<size_t>(bh) * L * D;
   const T* kg = static_cast<const T*>(p.k) + head_off;
   const T* vg = static_cast<const T*>(p.v) + head_off;
   const T* dh = static_cast<const T*>(p.dh) + static_cast<size_t>(bh) * D * D;
-  const uint32_t sdH_a = smem_u32(sdH), sK_a = smem_u32(sK), sV_a = smem_u32(sV);
+  const uint32_t sdH_a = smem_u32(sdH);
   const int m0 = warp * 16;
+  const int row_begin = ch * p.rows, row_end = min(L, row_begin + p.rows);
+  auto prefetch = [&](int row0, int buf) {
+    const uint32_t a = smem_u32(smem + D * D * 2 + 2 * buf * T64);
+    load_tile_async<D, 64>(a, kg, row0, L, tid, NT);
+    load_tile_async<D, 64>(a + T64, vg, row0, L, tid, NT);
+    cp_async_commit();
+  };
   load_tile_async<D, D>(sdH_a, dh, 0, D, tid, NT);
-  load_tile_async<D, 64>(sK_a, kg, row0, L, tid, NT);
-  load_tile_async<D, 64>(sV_a, vg, row0, L, tid, NT);
-  cp_async_commit();
+  if (row_begin < row_end) prefetch(row_begin, 0);
+  else cp_async_commit();
   for (int i = tid; i < D; i += NT) s_dz[i] = p.dz[static_cast<size_t>(bh) * D + i];
-  cp_async_wait<0>();
-  __syncthreads();
 
-  uint32_t pk[KS][4];
-  {
-    uint32_t kf[KS][4];
-    load_a_frags<D, KS>(kf, sK_a, m0, 0, lane);
-    feature_map_frags<T, KS, FEAT>(pk, kf);
-  }
-  float acc[D / 8][4];
+  int buf = 0;
+  for (int row0 = row_begin; row0 < row_end; row0 += 64, buf ^= 1) {
+    unsigned char* sK = smem + D * D * 2 + 2 * buf * T64;
+    unsigned char* sV = sK + T64;
+    const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV);
+    cp_async_wait<0>();
+    __syncthreads();   // this tile has landed, and every warp is done with the other buffer
+    if (row0 + 64 < row_end) prefetch(row0 + 64, buf ^ 1);
+
+    uint32_t pk[KS][4];
+    {
+      uint32_t kf[KS][4];
+      load_a_frags<D, KS>(kf, sK_a, m0, 0, lane);
+      feature_map_frags<T, KS, FEAT>(pk, kf);
+    }
+    float acc[D / 8][4];
 #pragma unroll
-  for (int j = 0; j < D / 8; ++j) {
-    int col = 8 * j + 2 * t;
-    acc[j][0] = s_dz[col]; acc[j][1] = s_dz[col + 1];
-    acc[j][2] = s_dz[col]; acc[j][3] = s_dz[col + 1];
-  }
-  gemm_at_b_nk<T, D, D / 8, KS>(acc, sV_a, m0, sdH_a, lane);  // dphi_k = v dH^T + dz
-  feature_map_bwd_frags<T, KS, FEAT>(acc, pk);
-  store_acc_to_tile<T, D, D / 8>(sK, acc, m0, lane);
-  flush16<T, D>(sK, m0, static_cast<T*>(p.dk) + head_off, row0 + m0, L, lane, p.accumulate != 0);
+    for (int j = 0; j < D / 8; ++j) {
+      int col = 8 * j + 2 * t;
+      acc[j][0] = s_dz[col]; acc[j][1] = s_dz[col + 1];
+      acc[j][2] = s_dz[col]; acc[j][3] = s_dz[col + 1];
+    }
+    gemm_at_b_nk<T, D, D / 8, KS>(acc, sV_a, m0, sdH_a, lane);  // dphi_k = v dH^T + dz
+    feature_map_bwd_frags<T, KS, FEAT>(acc, pk);
+    // each warp stages and flushes its own 16 rows
+    store_acc_to_tile<T, D, D / 8>(sK, acc, m0, lane);
+    flush16<T, D>(sK, m0, static_cast<T*>(p.dk) + head_off, row0 + m0, L, lane, p.accumulate != 0);
 #pragma unroll
-  for (int j = 0; j < D / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-  gemm_b_kn<T, D, D / 8, KS>(acc, pk, sdH_a, 0, 0, lane);  // dv_lin = phi(k) dH
-  store_acc_to_tile<T, D, D / 8>(sV, acc, m0, lane);
-  flush16<T, D>(sV, m0, static_cast<T*>(p.dv) + head_off, row0 + m0, L, lane, p.accumulate != 0);
+    for (int j = 0; j < D / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    gemm_b_kn<T, D, D / 8, KS>(acc, pk, sdH_a, 0, 0, lane);  // dv_lin = phi(k) dH
+    store_acc_to_tile<T, D, D / 8>(sV, acc, m0, lane);
+    flush16<T, D>(sV, m0, static_cast<T*>(p.dv) + head_off, row0 + m0, L, lane, p.accumulate != 0);
+  }
+  cp_async_wait<0>();
 }
 
 template <typename T, int D, int FEAT>
@@ -295,7 +323,7 @@ static int launch_lin_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_
   const int bh = s->B * s->H, dd = D * D;
   {
     auto kern = linear_bwd_q_kernel<T, D, FEAT>;
-    int smem = 3 * dd * 2 + 2 * D * 4;
+    int smem = 5 * dd * 2 + 2 * D * 4;
     SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     kern<<<dim3(p.nch, bh), D / 16 * 32, smem, st>>>(p);
     SLA_LAUNCH_OK();
@@ -313,9 +341,9 @@ static int launch_lin_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_
   }
   {
     auto kern = linear_bwd_kv_kernel<T, D, FEAT>;
-    int smem = dd * 2 + 2 * 64 * D * 2 + D * 4;
+    int smem = dd * 2 + 4 * 64 * D * 2 + D * 4;
     SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<dim3(ceil_div(s->L, 64), bh), 128, smem, st>>>(p);
+    kern<<<dim3(p.nch, bh), 128, smem, st>>>(p);
     SLA_LAUNCH_OK();
   }
   return SLA_OK;

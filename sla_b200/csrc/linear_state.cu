@@ -10,101 +10,118 @@
 
 namespace sla {
 
-template <typename T, int FEAT, int EPL>
-__device__ inline void phi_row(float (&x)[EPL]) {
+// phi of 8 consecutive elements of a row; the row is spread over 8 consecutive lanes (CPT such pieces
+// per lane), reductions run over those 8 lanes.
+template <typename T, int FEAT, int N>
+__device__ inline void phi_piece(float (&x)[N]) {
   if (FEAT == SLA_PHI_SOFTMAX) {
     float mx = x[0];
 #pragma unroll
-    for (int i = 1; i < EPL; ++i) mx = fmaxf(mx, x[i]);
-    mx = warp_max(mx);
+    for (int i = 1; i < N; ++i) mx = fmaxf(mx, x[i]);
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) {
+    for (int i = 0; i < N; ++i) {
       x[i] = __expf(x[i] - mx);
       s += x[i];
     }
-    s = 1.f / warp_sum(s);
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) x[i] *= s;
+    for (int o = 1; o < 8; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    s = 1.f / s;
+#pragma unroll
+    for (int i = 0; i < N; ++i) x[i] *= s;
   } else if (FEAT == SLA_PHI_RELU) {
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) x[i] = fmaxf(x[i], 0.f);
+    for (int i = 0; i < N; ++i) x[i] = fmaxf(x[i], 0.f);
   } else {
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) x[i] = x[i] > 0.f ? x[i] + 1.f : __expf(x[i]);
+    for (int i = 0; i < N; ++i) x[i] = x[i] > 0.f ? x[i] + 1.f : __expf(x[i]);
   }
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) x[i] = round_to<T>(x[i]);
 }
 
 // Reduces rows [chunk*rows, (chunk+1)*rows) of one head into partial[(bh*nch + chunk)*(D*D+D)].
+// 64-row {K, V} tiles stream through two buffers (the next tile is copied in while this one is worked
+// on); phi(k) is computed in place on the K tile, 8 lanes per row, then H += phi(k)^T V on mma.sync with
+// warp w owning rows [16w, 16w+16) of H.
 template <typename T, int D, int FEAT>
 __device__ inline void linear_state_chunk(const T* __restrict__ k, const T* __restrict__ v,
                                           float* __restrict__ partial, int L, int nch, int rows,
                                           unsigned char* smem) {
   constexpr int NW = D / 16, NT = NW * 32;
-  constexpr int EPL = D / 32;  // elements of a row per lane
-  unsigned char* sPhi = smem;            // [64][D] T
-  unsigned char* sV = smem + 64 * D * 2; // [64][D] T
-  float* red = reinterpret_cast<float*>(smem);  // reused at the end: [NW][D]
+  constexpr int T64 = 64 * D * 2;
+  constexpr int CPT = D / 64;          // 16-byte pieces of a row per lane
+  constexpr int RPP = NT / 8;          // rows per pass of the phi step
+  float* red = reinterpret_cast<float*>(smem);  // reused at the end: [RPP][D]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int ch = blockIdx.x, bh = blockIdx.y;
   const T* kg = k + static_cast<size_t>(bh) * L * D;
   const T* vg = v + static_cast<size_t>(bh) * L * D;
-  const uint32_t sPhi_a = smem_u32(sPhi), sV_a = smem_u32(sV);
 
   float acc[D / 8][4];
 #pragma unroll
   for (int j = 0; j < D / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-  float zacc[EPL];
+  float zacc[CPT][8];
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) zacc[i] = 0.f;
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) zacc[c][i] = 0.f;
 
   const int row_begin = ch * rows, row_end = min(L, row_begin + rows);
-  for (int row0 = row_begin; row0 < row_end; row0 += 64) {
-    load_tile_async<D, 64>(sV_a, vg, row0, L, tid, NT);
+  auto prefetch = [&](int row0, int buf) {
+    const uint32_t a = smem_u32(smem + 2 * buf * T64);
+    load_tile_async<D, 64>(a, kg, row0, L, tid, NT);
+    load_tile_async<D, 64>(a + T64, vg, row0, L, tid, NT);
     cp_async_commit();
-    // phi(k) for 64 rows, one warp per row
-    for (int r = warp; r < 64; r += NW) {
-      int gr = row0 + r;
-      float x[EPL];
-      if (gr < L) {
-        const T* src = kg + static_cast<size_t>(gr) * D + lane * EPL;
-        if (EPL == 4) {
-          uint2 raw = *reinterpret_cast<const uint2*>(src);
-          float2 a = Elem<T>::unpack2(raw.x), b = Elem<T>::unpack2(raw.y);
-          x[0] = a.x; x[1] = a.y; x[EPL - 2] = b.x; x[EPL - 1] = b.y;
-        } else {
-          uint32_t raw = *reinterpret_cast<const uint32_t*>(src);
-          float2 a = Elem<T>::unpack2(raw);
-          x[0] = a.x; x[1] = a.y;
+  };
+  if (row_begin < row_end) prefetch(row_begin, 0);
+  const int e8 = tid & 7, prow = tid >> 3;
+  int buf = 0;
+  for (int row0 = row_begin; row0 < row_end; row0 += 64, buf ^= 1) {
+    unsigned char* sK = smem + 2 * buf * T64;
+    const uint32_t sK_a = smem_u32(sK), sV_a = sK_a + T64;
+    cp_async_wait<0>();
+    __syncthreads();   // this tile has landed, and every warp is done with the other buffer
+    if (row0 + 64 < row_end) prefetch(row0 + 64, buf ^ 1);
+    // phi(k) in place; rows past the end of the sequence were zero-filled and must stay zero
+#pragma unroll
+    for (int r0 = 0; r0 < 64; r0 += RPP) {
+      const int r = r0 + prow;
+      float x[CPT * 8];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(sK + tile_off<D>(r, e8 + 8 * c));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = Elem<T>::unpack2(w[i]);
+          x[c * 8 + 2 * i] = f.x;
+          x[c * 8 + 2 * i + 1] = f.y;
         }
-        phi_row<T, FEAT, EPL>(x);
-      } else {
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) x[i] = 0.f;  // rows past the end contribute nothing
       }
+      phi_piece<T, FEAT, CPT * 8>(x);
+      const bool live = row0 + r < L;
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) zacc[i] += x[i];
-      int col = lane * EPL;
-      unsigned char* dst = sPhi + tile_off<D>(r, col >> 3) + (col & 7) * 2;
-      if (EPL == 4) {
-        uint2 pk;
-        pk.x = Elem<T>::pack2(x[0], x[1]);
-        pk.y = Elem<T>::pack2(x[EPL - 2], x[EPL - 1]);
-        *reinterpret_cast<uint2*>(dst) = pk;
-      } else {
-        *reinterpret_cast<uint32_t*>(dst) = Elem<T>::pack2(x[0], x[1]);
+      for (int c = 0; c < CPT; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          w[i] = live ? Elem<T>::pack2(x[c * 8 + 2 * i], x[c * 8 + 2 * i + 1]) : 0u;
+          const float2 f = Elem<T>::unpack2(w[i]);     // phi(k) is rounded to T before it is used (core.py:91)
+          zacc[c][2 * i] += f.x;
+          zacc[c][2 * i + 1] += f.y;
+        }
+        *reinterpret_cast<uint4*>(sK + tile_off<D>(r, e8 + 8 * c)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
-    cp_async_wait<0>();
     __syncthreads();
     uint32_t a[4][4];
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) load_a_frag_trans<D>(a[kk], sPhi_a, kk * 16, warp * 16, lane);
+    for (int kk = 0; kk < 4; ++kk) load_a_frag_trans<D>(a[kk], sK_a, kk * 16, warp * 16, lane);
     gemm_b_kn<T, D, D / 8, 4>(acc, a, sV_a, 0, 0, lane);
-    __syncthreads();
   }
+  cp_async_wait<0>();
+  __syncthreads();
 
   float* out = partial + (static_cast<size_t>(bh) * nch + ch) * (D * D + D);
   const int g = lane >> 2, t = lane & 3;
@@ -114,13 +131,16 @@ __device__ inline void linear_state_chunk(const T* __restrict__ k, const T* __re
     *reinterpret_cast<float2*>(out + r0 * D + c) = make_float2(acc[j][0], acc[j][1]);
     *reinterpret_cast<float2*>(out + (r0 + 8) * D + c) = make_float2(acc[j][2], acc[j][3]);
   }
+  // z: lane e8 of row group prow holds columns [8 (e8 + 8c), +8)
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) red[warp * D + lane * EPL + i] = zacc[i];
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[prow * D + (e8 + 8 * c) * 8 + i] = zacc[c][i];
   __syncthreads();
   for (int d = tid; d < D; d += NT) {
     float s = 0.f;
-#pragma unroll
-    for (int w = 0; w < NW; ++w) s += red[w * D + d];
+#pragma unroll 8
+    for (int w = 0; w < RPP; ++w) s += red[w * D + d];
     out[D * D + d] = s;
   }
 }
@@ -130,7 +150,7 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_state_kernel(const T* __re
                                                                    const T* __restrict__ v,
                                                                    float* __restrict__ partial, int L,
                                                                    int nch, int rows) {
-  __shared__ __align__(128) unsigned char smem[2 * 64 * D * 2];
+  extern __shared__ __align__(128) unsigned char smem[];   // two {K, V} buffers of 64 rows
   linear_state_chunk<T, D, FEAT>(k, v, partial, L, nch, rows, smem);
 }
 
@@ -152,18 +172,20 @@ static int launch_state(const sla_shape* s, const T* k, const T* v, T* state, fl
                         int rows, cudaStream_t st) {
   int bh = s->B * s->H;
   dim3 grid(nch, bh);
+  const int smem = 4 * 64 * D * 2;
+  auto go = [&](auto kern) -> int {
+    SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<grid, D / 16 * 32, smem, st>>>(k, v, partial, s->L, nch, rows);
+    SLA_LAUNCH_OK();
+    return SLA_OK;
+  };
+  int rc;
   switch (s->feature_map) {
-    case SLA_PHI_SOFTMAX:
-      linear_state_kernel<T, D, SLA_PHI_SOFTMAX><<<grid, D / 16 * 32, 0, st>>>(k, v, partial, s->L, nch, rows);
-      break;
-    case SLA_PHI_RELU:
-      linear_state_kernel<T, D, SLA_PHI_RELU><<<grid, D / 16 * 32, 0, st>>>(k, v, partial, s->L, nch, rows);
-      break;
-    default:
-      linear_state_kernel<T, D, SLA_PHI_ELU><<<grid, D / 16 * 32, 0, st>>>(k, v, partial, s->L, nch, rows);
-      break;
+    case SLA_PHI_SOFTMAX: rc = go(linear_state_kernel<T, D, SLA_PHI_SOFTMAX>); break;
+    case SLA_PHI_RELU: rc = go(linear_state_kernel<T, D, SLA_PHI_RELU>); break;
+    default: rc = go(linear_state_kernel<T, D, SLA_PHI_ELU>); break;
   }
-  SLA_LAUNCH_OK();
+  if (rc != SLA_OK) return rc;
   int n = D * D + D;
   linear_state_reduce_kernel<T><<<dim3(ceil_div(n, 256), bh), 256, 0, st>>>(partial, state, nch, n, 2 * D * D + D);
   SLA_LAUNCH_OK();

@@ -40,6 +40,7 @@ struct TcBwdParams {
   int* err;
   long long* trace;          // optional timeline of CTA (0,0): [role 0..3][entry < 64][4 events], SM clock cycles
   int L, Lpad, mb, nb, topk, max_entries;
+  int accumulate;            // add the result to what dq / dk / dv already hold (the linear branch's part)
   float scale, scale_log2;
 };
 
@@ -417,9 +418,15 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       fence_proxy_async_smem();
       asm volatile("bar.sync 1, 512;\n" ::: "memory");
       if (tid == 0) {
-        for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO1, sX1 + c * X_SLAB, c * 64, tile * 128, bh);
-        if (KVS)
-          for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO2, sX2 + c * X_SLAB, c * 64, tile * 128, bh);
+        if (p.accumulate) {   // read-modify-write done by the copy engine in L2: no load stalls this CTA
+          for (int c = 0; c < SLABS; ++c) tma_reduce_add_3d(&tmO1, sX1 + c * X_SLAB, c * 64, tile * 128, bh);
+          if (KVS)
+            for (int c = 0; c < SLABS; ++c) tma_reduce_add_3d(&tmO2, sX2 + c * X_SLAB, c * 64, tile * 128, bh);
+        } else {
+          for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO1, sX1 + c * X_SLAB, c * 64, tile * 128, bh);
+          if (KVS)
+            for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO2, sX2 + c * X_SLAB, c * 64, tile * 128, bh);
+        }
         tma_store_commit();
         tma_store_wait_all();
       }
@@ -470,6 +477,11 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ o_s
   }
 }
 
+static int bwd_tc_smem_bytes(int D, int max_entries) {
+  const int NS = D == 128 ? 4 : 6;
+  return 1024 + 2 * 128 * D * 2 + NS * 2 * 64 * D * 2 + NS * 512 + 2 * max_entries * 4 + 16;
+}
+
 template <typename T, int D, int BM, bool KVS>
 static int launch_bwd_tc(const sla_shape* s, const BwdParams& bp, const float2* stats, int Lpad, cudaStream_t st) {
   const int bh = s->B * s->H;
@@ -491,11 +503,10 @@ static int launch_bwd_tc(const sla_shape* s, const BwdParams& bp, const float2* 
   if (p.err == nullptr) return SLA_ERR_CUDA;
   p.trace = g_trace_buffer ? g_trace_buffer + (KVS ? 1024 : 0) : nullptr;
   p.L = s->L; p.Lpad = Lpad; p.mb = bp.mb; p.nb = bp.nb; p.topk = bp.topk;
-  p.scale = bp.scale; p.scale_log2 = bp.scale_log2;
-  constexpr int NS = D == 128 ? 4 : 6;
+  p.scale = bp.scale; p.scale_log2 = bp.scale_log2; p.accumulate = bp.accumulate;
   const int max_entries = KVS ? 2 * bp.mb : 2 * bp.topk;
   p.max_entries = max_entries;
-  const int smem = 1024 + 2 * 128 * D * 2 + NS * 2 * 64 * D * 2 + NS * 512 + 2 * max_entries * 4 + 16;
+  const int smem = bwd_tc_smem_bytes(D, max_entries);
   if (smem > 227 * 1024) return SLA_ERR_BAD_SHAPE;
   auto kern = tc::sparse_bwd_tc_kernel<T, D, BM, KVS>;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -508,6 +519,9 @@ static int launch_bwd_tc(const sla_shape* s, const BwdParams& bp, const float2* 
 template <typename T, int D, int BM>
 static int run_bwd_tc_typed(const sla_shape* s, const BwdParams& bp, float2* stats, int Lpad, cudaStream_t st) {
   const int bh = s->B * s->H;
+  // nothing is launched unless both kernels fit: the caller falls back to another path on BAD_SHAPE
+  if (bwd_tc_smem_bytes(D, 2 * bp.mb) > 227 * 1024 || bwd_tc_smem_bytes(D, 2 * bp.topk) > 227 * 1024)
+    return SLA_ERR_BAD_SHAPE;
   bwd_prep_kernel<T, D><<<dim3(ceil_div(Lpad, 8), bh), 256, 0, st>>>(
       static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L, Lpad);
   SLA_LAUNCH_OK();
