@@ -60,6 +60,15 @@ struct Elem<__nv_bfloat16> {
     __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
     return __bfloat1622float2(v);
   }
+  // element-wise product / sum of two packed pairs, each result rounded once to T
+  __device__ static inline uint32_t mul2(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  __device__ static inline uint32_t add2(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
 };
 template <>
 struct Elem<__half> {
@@ -72,6 +81,14 @@ struct Elem<__half> {
   __device__ static inline float2 unpack2(uint32_t u) {
     __half2 v = *reinterpret_cast<__half2*>(&u);
     return __half22float2(v);
+  }
+  __device__ static inline uint32_t mul2(uint32_t a, uint32_t b) {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  __device__ static inline uint32_t add2(uint32_t a, uint32_t b) {
+    __half2 r = __hadd2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
   }
 };
 template <>

@@ -73,7 +73,8 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[18];
-  __shared__ float s_z[D], s_bias[D];
+  __shared__ uint32_t s_zp[D / 2];   // z of the linear state, pairs of T
+  __shared__ float s_bias[D];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_n_entries;
   __shared__ int s_abort;
@@ -163,7 +164,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   }
   if (fused && tid < D) {
     const T* rec = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (2 * D * D + D);
-    s_z[tid] = Elem<T>::to_f(rec[D * D + tid]);
+    if (tid < D / 2) s_zp[tid] = reinterpret_cast<const uint32_t*>(rec + D * D)[tid];
     s_bias[tid] = Elem<T>::to_f(static_cast<const T*>(p.wbits)[D * D + tid]);
   }
   tc_fence_before();
@@ -417,8 +418,8 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             w[i] = Elem<T>::pack2(f[2 * i], f[2 * i + 1]);
-            const float2 ph = Elem<T>::unpack2(w[i]);
-            dsum += round_to<T>(ph.x * s_z[ch * 8 + 2 * i]) + round_to<T>(ph.y * s_z[ch * 8 + 2 * i + 1]);
+            const float2 pz = Elem<T>::unpack2(Elem<T>::mul2(w[i], s_zp[ch * 4 + i]));   // each product rounded to T
+            dsum += pz.x + pz.y;
           }
           st_shared_v4(chunk_addr(sQ, ch), w[0], w[1], w[2], w[3]);
         };
@@ -438,6 +439,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             mx1 = fmaxf(mx1, fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])));
           }
           const float mx = fmaxf(mx0, mx1);
+          const float neg_mx = -mx * kLog2e;
           // exp(x - max) in fp32 is parked in the idle S columns of this thread's TMEM lane
           float e0 = 0.f, e1 = 0.f;
 #pragma unroll
@@ -449,7 +451,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               load_x((c0 >> 3) + q4, f);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                const float e = __expf(f[i] - mx);
+                const float e = ex2(fmaf(f[i], kLog2e, neg_mx));
                 if (i & 1) e1 += e; else e0 += e;
                 ev[q4 * 8 + i] = __float_as_uint(e);
               }
@@ -509,10 +511,10 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 const int c = q4 * 8 + 2 * i;
-                const float os0 = round_to<T>(__uint_as_float(ov[c]) * inv), os1 = round_to<T>(__uint_as_float(ov[c + 1]) * inv);
-                const float l0 = round_to<T>(__uint_as_float(lv[c]) * rden + s_bias[c0 + c]);
-                const float l1 = round_to<T>(__uint_as_float(lv[c + 1]) * rden + s_bias[c0 + c + 1]);
-                w[i] = Elem<T>::pack2(os0 + l0, os1 + l1);
+                const uint32_t os2 = Elem<T>::pack2(__uint_as_float(ov[c]) * inv, __uint_as_float(ov[c + 1]) * inv);
+                const uint32_t lin2 = Elem<T>::pack2(fmaf(__uint_as_float(lv[c]), rden, s_bias[c0 + c]),
+                                                     fmaf(__uint_as_float(lv[c + 1]), rden, s_bias[c0 + c + 1]));
+                w[i] = Elem<T>::add2(os2, lin2);
               }
               st_shared_v4(chunk_addr(sQ, (c0 >> 3) + q4), w[0], w[1], w[2], w[3]);
             }
