@@ -59,7 +59,11 @@ enum sla_op { SLA_OP_BLOCK_MAP = 0, SLA_OP_FWD = 1, SLA_OP_BWD = 2, SLA_OP_LINEA
               SLA_OP_SAGE_FWD = 4, SLA_OP_SPARSE_BWD = 5 };
 enum sla_flags {
   SLA_FLAG_SPARSE_ONLY = 1, /* skip the linear branch and proj_l (the `_attention` operator) */
-  SLA_FLAG_LEGACY_MMA = 2   /* use the mma.sync kernels instead of the tcgen05 ones */
+  SLA_FLAG_LEGACY_MMA = 2,  /* use the mma.sync kernels instead of the tcgen05 ones */
+  SLA_FLAG_LINEAR_UNSELECTED = 4 /* sla_fwd only: the linear branch of query block i sums over the KV blocks
+                                    that block did NOT select (the scope drawn in assets/overview_of_SLA.png)
+                                    instead of over all tokens (core.py:92-96). Forward only: sla_bwd returns
+                                    SLA_ERR_UNSUPPORTED with this flag. */
 };
 
 typedef struct sla_shape {

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libsla_b200.so")
 SLA_BF16, SLA_FP16, SLA_FP32 = 0, 1, 2
 PHI = {"softmax": 0, "relu": 1, "elu": 2}
 OP_BLOCK_MAP, OP_FWD, OP_BWD, OP_LINEAR_STATE, OP_SAGE_FWD, OP_SPARSE_BWD = 0, 1, 2, 3, 4, 5
-FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA = 1, 2
+FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA, FLAG_LINEAR_UNSELECTED = 1, 2, 4
 
 # every symbol include/sla_b200.h declares
 EXPORTS = (

@@ -18,7 +18,7 @@ _FEATURES = ("elu", "relu", "softmax")
 
 class SparseLinearAttention(nn.Module):
     def __init__(self, head_dim, topk, feature_map="softmax", BLKQ=64, BLKK=64, use_bf16=True,
-                 tie_feature_map_qk=True):
+                 tie_feature_map_qk=True, linear_scope="all"):
         R"""
         Args:
             head_dim: dimension of each head (64 or 128).
@@ -29,6 +29,10 @@ class SparseLinearAttention(nn.Module):
             use_bf16: bfloat16 (default) or float16 computation; the cast is done inside the module.
             tie_feature_map_qk: kept for signature compatibility; q and k always share the map type
                 (in the reference both choices select the same function, core.py:43-60).
+            linear_scope: not in the reference. "all" (default) is the reference's behaviour: the linear
+                branch sums over every token (core.py:92-96). "unselected" sums, for each query block, over
+                the KV blocks that block did not select (the scope drawn in assets/overview_of_SLA.png);
+                forward only.
         """
         super().__init__()
         self.dtype = torch.bfloat16 if use_bf16 else torch.float16
@@ -40,7 +44,10 @@ class SparseLinearAttention(nn.Module):
             raise NotImplementedError(f"Not supported feature map {feature_map}.")
         self.feature_map = feature_map
         self.tie_feature_map_qk = tie_feature_map_qk
-        self.impl_flags = 0
+        if linear_scope not in ("all", "unselected"):
+            raise NotImplementedError(f"Not supported linear scope {linear_scope}.")
+        self.linear_scope = linear_scope
+        self.impl_flags = ops.FLAG_LINEAR_UNSELECTED if linear_scope == "unselected" else 0
         self.init_weights_()
 
     def init_weights_(self):
@@ -58,6 +65,8 @@ class SparseLinearAttention(nn.Module):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         need_grad = torch.is_grad_enabled() and (
             q.requires_grad or k.requires_grad or v.requires_grad or self.proj_l.weight.requires_grad)
+        if need_grad and self.linear_scope == "unselected":
+            raise NotImplementedError("linear_scope='unselected' has no backward: call it under torch.no_grad()")
         bm = ops.block_map(q, k, self.topk, self.BLKQ, self.BLKK, want_cols=need_grad)  # on the given dtype
         q, k, v = q.to(self.dtype), k.to(self.dtype), v.to(self.dtype)
         o = ops.sla_attention(q, k, v, self.proj_l.weight, self.proj_l.bias, bm, self.BLKQ, self.BLKK,

@@ -93,9 +93,11 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   }
   if (!w || !lin_state || !ws) return SLA_ERR_NULL;
   WsLinearState wl = ws_linear_state(s);
-  if (ws_bytes < wl.total + ws_fwd_extra(s)) return SLA_ERR_WS_TOO_SMALL;
+  if (ws_bytes < ws_fwd_total(s)) return SLA_ERR_WS_TOO_SMALL;
   unsigned char* base = static_cast<unsigned char*>(ws);
   void* wbits = base + wl.total;
+  const bool unselected = (s->flags & SLA_FLAG_LINEAR_UNSELECTED) != 0;
+  if (unselected && legacy) return SLA_ERR_UNSUPPORTED;
   rc = convert_proj(s, w, bias, wbits, st);
   if (rc != SLA_OK) return rc;
   rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wl.partial), wl.nch, wl.rows, st);
@@ -103,6 +105,27 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   rc = run_state_proj(s, lin_state, wbits, st);
   if (rc != SLA_OK) return rc;
   FwdParams p = make_fwd(s, q, k, v, lut, o, o_s, lse, lin_state, wbits);
+  if (unselected) {
+    // sparse branch; then the same block lists once more without softmax on (phi(q), phi(k), v) for the
+    // selected blocks' share of the linear state, which the read-out takes off the all-token state
+    unsigned char* ub = base + wl.total + ws_fwd_extra(s);
+    WsUnselected wu = ws_unselected(s);
+    void* os_buf = o_s ? o_s : o;
+    FwdParams ps = make_fwd(s, q, k, v, lut, os_buf, nullptr, lse, nullptr, nullptr);
+    rc = run_sparse_fwd_tc(s, ps, st);
+    if (rc != SLA_OK) return rc;
+    rc = run_feature_map(s, q, ub + wu.phiq, st);
+    if (rc != SLA_OK) return rc;
+    rc = run_feature_map(s, k, ub + wu.phik, st);
+    if (rc != SLA_OK) return rc;
+    FwdParams pc = make_fwd(s, ub + wu.phiq, ub + wu.phik, v, lut, ub + wu.cnum, nullptr,
+                            reinterpret_cast<float*>(ub + wu.cden), nullptr, nullptr);
+    pc.plain = 1;
+    rc = run_sparse_fwd_tc(s, pc, st);
+    if (rc != SLA_OK) return rc;
+    FwdParams pr = make_fwd(s, ub + wu.phiq, k, v, lut, o, os_buf, lse, lin_state, wbits);
+    return run_linear_readout_unselected(s, pr, ub + wu.cnum, reinterpret_cast<const float*>(ub + wu.cden), st);
+  }
   if (legacy) return run_sparse_fwd_mma(s, p, true, st);
   // tcgen05 sparse branch with the linear read-out, proj_l and the final sum fused into its epilogue
   return run_sparse_fwd_tc(s, p, st);
@@ -157,6 +180,7 @@ int sla_bwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   if (s->flags & SLA_FLAG_SPARSE_ONLY)
     return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 0, st);
   if (!w || !lin_state || !dw || !dbias) return SLA_ERR_NULL;
+  if (s->flags & SLA_FLAG_LINEAR_UNSELECTED) return SLA_ERR_UNSUPPORTED;   // forward-only scope
   const bool legacy = (s->flags & SLA_FLAG_LEGACY_MMA) != 0;
   rc = convert_proj(s, w, nullptr, base + wb.wbits, st);
   if (rc != SLA_OK) return rc;

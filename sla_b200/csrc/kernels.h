@@ -17,6 +17,7 @@ struct FwdParams {
   const void* wbits;      // [D*D + D] 16-bit: W then bias
   int L, mb, topk;
   float scale_log2;       // softmax scale * log2(e)
+  int plain = 0;          // tcgen05 forward only: P = S without softmax, unnormalised O, row sums in `lse`
 };
 
 struct BwdParams {
@@ -52,6 +53,9 @@ int convert_proj(const sla_shape* s, const float* w, const float* bias, void* ou
 int run_sparse_fwd_mma(const sla_shape* s, const FwdParams& p, bool lin, cudaStream_t st);
 int run_sparse_fwd_tc(const sla_shape* s, const FwdParams& p, cudaStream_t st);
 int run_linear_readout(const sla_shape* s, const FwdParams& p, cudaStream_t st);
+int run_feature_map(const sla_shape* s, const void* x, void* out, cudaStream_t st);
+int run_linear_readout_unselected(const sla_shape* s, const FwdParams& p, const void* cnum, const float* cden,
+                                  cudaStream_t st);
 int run_state_proj(const sla_shape* s, void* lin_state, const void* wbits, cudaStream_t st);
 int read_tc_error(int* out, bool clear);
 void set_trace_buffer(long long* p);

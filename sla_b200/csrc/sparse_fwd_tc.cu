@@ -37,6 +37,7 @@ struct TcFwdParams {
   float scale_log2;
   // fused linear branch (core.py:90,95-100); feature < 0: sparse branch only
   int feature;             // sla_feature, or -1
+  int plain;               // no softmax: P = S (scale 1), O is left unnormalised and `lse` receives the row sums of P
   int store_os;            // also store the sparse branch output through tmOs
   const void* lin_state;   // [BH][2*D*D + D] T: H, z, H W^T
   const void* wbits;       // [D*D + D] T: W, bias
@@ -309,6 +310,22 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         uint32_t sv[64];
         tmem_ld_x64(s_addr, sv);
         tmem_wait_ld();
+        if (p.plain) {
+          // linear kernel over the selected blocks: keys past the end are zero rows, so S is 0 there
+          float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+          for (int c = 0; c < 64; c += 2) {
+            pk[c >> 1] = Elem<T>::pack2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
+            const float2 pr = Elem<T>::unpack2(pk[c >> 1]);      // the sum uses what the P.V GEMM sees
+            rs0 += pr.x; rs1 += pr.y;
+          }
+          l += rs0 + rs1;
+          tmem_st_x32(s_addr, pk);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(BAR(B_P + b));
+          continue;
+        }
         const int valid = L - (entry & 0x0fffffff) * 64;     // keys of this block that exist (kernel.py:57)
         // row maximum of the raw scores (the scale is positive, so it commutes with max); four
         // independent chains keep the dependent-issue latency off the critical path
@@ -377,9 +394,9 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     asm volatile("bar.sync 1, 128;\n" ::: "memory");
     if (!*abortp) {
       tc_fence_after();
-      const float inv = 1.0f / l;
+      const float inv = p.plain ? 1.0f : 1.0f / l;
       const int grow = tile * 128 + row;
-      if (grow < L) p.lse[static_cast<size_t>(bh) * L + grow] = m_used + log2f(l);   // kernel.py:81
+      if (grow < L) p.lse[static_cast<size_t>(bh) * L + grow] = p.plain ? l : m_used + log2f(l);   // kernel.py:81
       // 16-byte chunk ch of this thread's row inside a 128-row tile at `tile_base` (128B-swizzled slabs)
       auto chunk_addr = [&](uint32_t tile_base, int ch) {
         return tile_base + (ch >> 3) * Q_SLAB + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
@@ -642,6 +659,7 @@ static int launch_tc(const sla_shape* s, const FwdParams& fp, cudaStream_t st) {
   p.feature = fused ? s->feature_map : -1;
   p.store_os = fused && fp.o_s != nullptr && fp.o_s != fp.o;
   p.lin_state = fp.lin_state; p.wbits = fp.wbits;
+  p.plain = fp.plain;
   if (p.store_os && (rc = make_tmap_3d(&tos, fp.o_s, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
   if (fused) {
     // H W^T sits behind H and z in each head's record: D rows of D elements, records 2*D*D + D apart

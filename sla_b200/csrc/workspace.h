@@ -59,6 +59,27 @@ inline WsLinearState ws_linear_state(const sla_shape* s) {
 // extra bytes the fused forward needs after the linear-state workspace: proj weight + bias in 16 bit
 inline size_t ws_fwd_extra(const sla_shape* s) { return ws_round(size_t(s->D) * s->D * 2 + s->D * 2); }
 
+// the "unselected blocks" scope of the linear branch: phi(q), phi(k), C_num as 16-bit (B,H,L,D), C_den fp32 (B,H,L)
+struct WsUnselected {
+  size_t phiq, phik, cnum, cden, total;
+};
+inline WsUnselected ws_unselected(const sla_shape* s) {
+  WsUnselected w;
+  size_t n = size_t(s->B) * s->H * s->L;
+  size_t o = 0;
+  w.phiq = o; o += ws_round(n * s->D * 2);
+  w.phik = o; o += ws_round(n * s->D * 2);
+  w.cnum = o; o += ws_round(n * s->D * 2);
+  w.cden = o; o += ws_round(n * 4);
+  w.total = o;
+  return w;
+}
+inline size_t ws_fwd_total(const sla_shape* s) {
+  size_t t = ws_linear_state(s).total + ws_fwd_extra(s);
+  if (s->flags & SLA_FLAG_LINEAR_UNSELECTED) t += ws_unselected(s).total;
+  return t;
+}
+
 // ---- backward ----
 struct WsBwd {
   size_t wbits;     // 16-bit copy of W [D][D]

@@ -146,6 +146,9 @@ class _attention(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None, None
 
 
+FLAG_LINEAR_UNSELECTED = _lib.FLAG_LINEAR_UNSELECTED
+
+
 class _SLAFused(torch.autograd.Function):
     """core.py:88-100 (sparse branch + feature maps + linear branch + proj_l + sum) as one operator."""
 

@@ -123,3 +123,32 @@ def test_full_size_linearity_in_v_c3_head():
     a = ops._attention.apply(q, k, v, smap, lut, topk, 64, 64).float()
     b = ops._attention.apply(q, k, (2 * v), smap, lut, topk, 64, 64).float()
     assert_close_parity(b.cpu(), (2 * a).cpu(), cos_min=0.99999, l1_max=1e-3, what="linearity")
+
+
+@pytest.mark.parametrize("feat,D,BLKQ,L,ratio", [("softmax", 128, 64, 2000, 0.1), ("relu", 64, 128, 1100, 0.25),
+                                                 ("elu", 128, 128, 900, 0.2), ("softmax", 64, 64, 1024, 0.25)])
+def test_unselected_scope_vs_oracle(feat, D, BLKQ, L, ratio):
+    """linear_scope='unselected' (not in the reference's code: unpinned; checked against the CPU restatement,
+    which sums per-block states over the blocks a query block did not select). The linear part alone
+    (o - o_s) must agree too, so proj_l is given weights large enough for it to matter."""
+    import sla_b200
+    from oracle import sla_oracle as O
+    g = torch.Generator().manual_seed(L + D)
+    B, H = 1, 2
+    q, k, v = (torch.randn(B, H, L, D, generator=g).bfloat16() for _ in range(3))
+    w = torch.randn(D, D, generator=g) / D ** 0.5
+    b = torch.randn(D, generator=g) * 0.05
+    m = sla_b200.SparseLinearAttention(D, ratio, feat, BLKQ, 64, linear_scope="unselected").cuda()
+    with torch.no_grad():
+        m.proj_l.weight.copy_(w)
+        m.proj_l.bias.copy_(b)
+        o = m(q.cuda(), k.cuda(), v.cuda()).float().cpu()
+    o_ref, parts = O.sla_forward(q, k, v, w, b, ratio, feat, BLKQ, 64, linear_scope="unselected", return_parts=True)
+    assert_close_parity(o, o_ref.float(), what="unselected.o")
+    lin, lin_ref = o - parts["o_s"].float(), o_ref.float() - parts["o_s"].float()
+    assert_close_parity(lin, lin_ref, cos_min=0.995, l1_max=5e-2, what="unselected.linear_part")
+    # and it differs from the all-token scope (the test would pass vacuously otherwise)
+    o_all = O.sla_forward(q, k, v, w, b, ratio, feat, BLKQ, 64, linear_scope="all").float()
+    assert (o_all - o_ref.float()).abs().mean() > 5 * (o - o_ref.float()).abs().mean()
+    with pytest.raises(NotImplementedError):
+        m(q.cuda().requires_grad_(True), k.cuda(), v.cuda())
