@@ -34,7 +34,8 @@ __global__ void __launch_bounds__(256) colsum_kernel(const TIn* __restrict__ k, 
   float acc[N];
 #pragma unroll
   for (int i = 0; i < N; ++i) acc[i] = 0.f;
-  for (int r = row0 + rg; r < row1; r += RP) {
+#pragma unroll 8
+  for (int r = row0 + rg; r < row1; r += RP) {   // unrolled so that several loads are in flight per thread
     float v[N];
     VecLoad<TIn>::load(v, base + static_cast<size_t>(r) * D + c);
 #pragma unroll
@@ -85,6 +86,7 @@ __global__ void __launch_bounds__(256) pool_kernel(const TIn* __restrict__ q, co
   float acc[N];
 #pragma unroll
   for (int i = 0; i < N; ++i) acc[i] = 0.f;
+#pragma unroll 4
   for (int r = row0 + rg; r < row1; r += RP) {
     float v[N];
     VecLoad<TIn>::load(v, base + static_cast<size_t>(r) * D + c);
@@ -135,28 +137,42 @@ __global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
   __syncthreads();
 
   const TIn* pk = pooled_k + static_cast<size_t>(bh) * nb * D;
-  for (int j = tid; j < nb; j += blockDim.x) {
-    float acc[kTopkRows];
+  // two KV blocks per thread and pass: every shared-memory read of a pooled query value feeds two
+  // FMAs; each score is still one sequential fp32 sum over d
+  for (int j = tid; j < nb; j += 2 * blockDim.x) {
+    const int j1 = j + blockDim.x;
+    const bool has1 = j1 < nb;
+    const TIn* k0 = pk + static_cast<size_t>(j) * D;
+    const TIn* k1 = pk + static_cast<size_t>(has1 ? j1 : j) * D;
+    float acc0[kTopkRows], acc1[kTopkRows];
 #pragma unroll
-    for (int r = 0; r < kTopkRows; ++r) acc[r] = 0.f;
+    for (int r = 0; r < kTopkRows; ++r) acc0[r] = acc1[r] = 0.f;
 #pragma unroll 2
     for (int c = 0; c < D; c += N) {
-      float kv[N];
-      VecLoad<TIn>::load(kv, pk + static_cast<size_t>(j) * D + c);
+      float kv0[N], kv1[N];
+      VecLoad<TIn>::load(kv0, k0 + c);
+      VecLoad<TIn>::load(kv1, k1 + c);
 #pragma unroll
       for (int r = 0; r < kTopkRows; ++r) {
 #pragma unroll
         for (int e = 0; e < N; e += 4) {
           float4 qv = *reinterpret_cast<const float4*>(spq + r * D + c + e);
-          acc[r] = fmaf(qv.x, kv[e], acc[r]);
-          acc[r] = fmaf(qv.y, kv[e + 1], acc[r]);
-          acc[r] = fmaf(qv.z, kv[e + 2], acc[r]);
-          acc[r] = fmaf(qv.w, kv[e + 3], acc[r]);
+          acc0[r] = fmaf(qv.x, kv0[e], acc0[r]);
+          acc0[r] = fmaf(qv.y, kv0[e + 1], acc0[r]);
+          acc0[r] = fmaf(qv.z, kv0[e + 2], acc0[r]);
+          acc0[r] = fmaf(qv.w, kv0[e + 3], acc0[r]);
+          acc1[r] = fmaf(qv.x, kv1[e], acc1[r]);
+          acc1[r] = fmaf(qv.y, kv1[e + 1], acc1[r]);
+          acc1[r] = fmaf(qv.z, kv1[e + 2], acc1[r]);
+          acc1[r] = fmaf(qv.w, kv1[e + 3], acc1[r]);
         }
       }
     }
 #pragma unroll
-    for (int r = 0; r < kTopkRows; ++r) keys[r * nb + j] = order_key(round_to<TIn>(acc[r]));  // utils.py:59
+    for (int r = 0; r < kTopkRows; ++r) {
+      keys[r * nb + j] = order_key(round_to<TIn>(acc0[r]));  // utils.py:59
+      if (has1) keys[r * nb + j1] = order_key(round_to<TIn>(acc1[r]));
+    }
   }
   __syncthreads();
 

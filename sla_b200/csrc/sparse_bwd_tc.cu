@@ -454,26 +454,44 @@ template <typename T, int D>
 __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ o_s, const T* __restrict__ d_o,
                                                        const float* __restrict__ lse, float2* __restrict__ stats,
                                                        float* __restrict__ delta_out, int L, int Lpad) {
-  constexpr int EPL = D / 32;
+  // 64 rows per CTA, 8 per warp; a row is spread over LPR lanes with 16-byte loads, and the warp's
+  // loads of all its rows are issued before the first use.
+  constexpr int LPR = D / 8;              // lanes per row
+  constexpr int RPI = 32 / LPR;           // rows per warp iteration
+  constexpr int ITER = 8 / RPI;
   const int bh = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int r = blockIdx.x * 8 + warp;
-  if (r >= Lpad) return;
-  float s = 0.f;
-  if (r < L) {
-    const T* a = o_s + (static_cast<size_t>(bh) * L + r) * D + lane * EPL;
-    const T* b = d_o + (static_cast<size_t>(bh) * L + r) * D + lane * EPL;
+  const int sub = lane / LPR, col = (lane % LPR) * 8;
+  const int r_base = blockIdx.x * 64 + warp * 8;
+  uint4 a[ITER], b[ITER];
 #pragma unroll
-    for (int e = 0; e < EPL; e += 2) {
-      float2 x = Elem<T>::unpack2(*reinterpret_cast<const uint32_t*>(a + e));
-      float2 y = Elem<T>::unpack2(*reinterpret_cast<const uint32_t*>(b + e));
-      s += x.x * y.x + x.y * y.y;
+  for (int i = 0; i < ITER; ++i) {
+    const int r = r_base + i * RPI + sub;
+    if (r < L) {
+      const size_t off = (static_cast<size_t>(bh) * L + r) * D + col;
+      a[i] = *reinterpret_cast<const uint4*>(o_s + off);
+      b[i] = *reinterpret_cast<const uint4*>(d_o + off);
+    } else {
+      a[i] = b[i] = make_uint4(0u, 0u, 0u, 0u);
     }
   }
-  s = warp_sum(s);
-  if (lane == 0) {
-    float l = r < L ? lse[static_cast<size_t>(bh) * L + r] : INFINITY;
-    stats[static_cast<size_t>(bh) * Lpad + r] = make_float2(l, r < L ? s : 0.f);
-    if (r < L && delta_out) delta_out[static_cast<size_t>(bh) * L + r] = s;
+#pragma unroll
+  for (int i = 0; i < ITER; ++i) {
+    const int r = r_base + i * RPI + sub;
+    const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a[i]);
+    const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b[i]);
+    float s = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 x = Elem<T>::unpack2(aw[e]), y = Elem<T>::unpack2(bw[e]);
+      s += x.x * y.x + x.y * y.y;
+    }
+#pragma unroll
+    for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane % LPR == 0 && r < Lpad) {
+      float l = r < L ? lse[static_cast<size_t>(bh) * L + r] : INFINITY;
+      stats[static_cast<size_t>(bh) * Lpad + r] = make_float2(l, r < L ? s : 0.f);
+      if (r < L && delta_out) delta_out[static_cast<size_t>(bh) * L + r] = s;
+    }
   }
 }
 
@@ -522,7 +540,7 @@ static int run_bwd_tc_typed(const sla_shape* s, const BwdParams& bp, float2* sta
   // nothing is launched unless both kernels fit: the caller falls back to another path on BAD_SHAPE
   if (bwd_tc_smem_bytes(D, 2 * bp.mb) > 227 * 1024 || bwd_tc_smem_bytes(D, 2 * bp.topk) > 227 * 1024)
     return SLA_ERR_BAD_SHAPE;
-  bwd_prep_kernel<T, D><<<dim3(ceil_div(Lpad, 8), bh), 256, 0, st>>>(
+  bwd_prep_kernel<T, D><<<dim3(ceil_div(Lpad, 64), bh), 256, 0, st>>>(
       static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L, Lpad);
   SLA_LAUNCH_OK();
   int rc = launch_bwd_tc<T, D, BM, false>(s, bp, stats, Lpad, st);
