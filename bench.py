@@ -190,7 +190,10 @@ def load_reference_package():
     return mod
 
 
-def gpu_baselines(w, q, k, v, do, W, b, steps, warmup):
+def gpu_baselines(w, q, k, v, do, W, b, steps, warmup, backward=True):
+    """Same box, same inputs: the unmodified reference module (Triton, bf16) and FlashAttention-2 dense.
+    For the quantized workload both are forward-only 16-bit runs (the reference's own quantized module needs a
+    package that is not installed)."""
     out = {}
     sync = torch.cuda.synchronize
     try:
@@ -198,7 +201,8 @@ def gpu_baselines(w, q, k, v, do, W, b, steps, warmup):
         if ref is None:
             out["reference_triton"] = {"unavailable": "baseline/_ref not present"}
         else:
-            m = ref.SparseLinearAttention(w.D, w.topk, w.feature, w.BLKQ, w.BLKK).cuda()
+            BLKQ, BLKK = (128, 64) if w.quantized else (w.BLKQ, w.BLKK)
+            m = ref.SparseLinearAttention(w.D, w.topk, w.feature, BLKQ, BLKK).cuda()
             with torch.no_grad():
                 m.proj_l.weight.copy_(W)
                 m.proj_l.bias.copy_(b)
@@ -214,15 +218,19 @@ def gpu_baselines(w, q, k, v, do, W, b, steps, warmup):
                 qg.grad = kg.grad = vg.grad = None
 
             f = timed(fwd, steps, warmup, sync)
-            fb = timed(fwdbwd, steps, warmup, sync)
-            out["reference_triton"] = {"fwd_ms": f, "fwd_bwd_ms": fb,
-                                       "fwd_bwd_dense_equiv_tflops": w.dense_equiv_flops(True) / fb / 1e9}
+            out["reference_triton"] = {"fwd_ms": f}
+            if backward:
+                fb = timed(fwdbwd, steps, warmup, sync)
+                out["reference_triton"].update({"fwd_bwd_ms": fb,
+                                                "fwd_bwd_dense_equiv_tflops": w.dense_equiv_flops(True) / fb / 1e9})
     except Exception as e:  # noqa: BLE001
         out["reference_triton"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
     try:
         from flash_attn.flash_attn_interface import flash_attn_func
-        qf, kf, vf, dof = (t.transpose(1, 2).contiguous() for t in (q, k, v, do))
-        qf, kf, vf = (t.requires_grad_(True) for t in (qf, kf, vf))
+        qf, kf, vf = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+        dof = do.transpose(1, 2).contiguous() if backward else None
+        if backward:
+            qf, kf, vf = (t.requires_grad_(True) for t in (qf, kf, vf))
 
         def ffwd():
             with torch.no_grad():
@@ -234,9 +242,10 @@ def gpu_baselines(w, q, k, v, do, W, b, steps, warmup):
             qf.grad = kf.grad = vf.grad = None
 
         f = timed(ffwd, max(2, steps // 2), 2, sync)
-        fb = timed(ffb, max(2, steps // 2), 2, sync)
-        out["flash_attn_dense"] = {"fwd_ms": f, "fwd_bwd_ms": fb,
-                                   "fwd_bwd_tflops": w.dense_equiv_flops(True) / fb / 1e9}
+        out["flash_attn_dense"] = {"fwd_ms": f, "fwd_tflops": w.dense_equiv_flops(False) / f / 1e9}
+        if backward:
+            fb = timed(ffb, max(2, steps // 2), 2, sync)
+            out["flash_attn_dense"].update({"fwd_bwd_ms": fb, "fwd_bwd_tflops": w.dense_equiv_flops(True) / fb / 1e9})
     except Exception as e:  # noqa: BLE001
         out["flash_attn_dense"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
     return out
@@ -507,8 +516,8 @@ def main():
                                 "cores": torch.get_num_threads(), "kind": "port",
                                 "sample": f"1 of {w.units} (batch,head) units x {len(ts)} repeats, "
                                           f"forward+backward incl. block map ({sec:.2f} s each)"}
-    if rank == 0 and world == 1 and not args.no_baselines and not w.quantized and bwd:
-        line["gpu_baselines"] = gpu_baselines(w, q, k, v, do, W, b, max(3, min(10, args.steps // 2)), 3)
+    if rank == 0 and world == 1 and not args.no_baselines:
+        line["gpu_baselines"] = gpu_baselines(w, q, k, v, do, W, b, max(3, min(10, args.steps // 2)), 3, backward=bwd)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

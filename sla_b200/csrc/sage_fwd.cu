@@ -45,7 +45,13 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 enum : int { kSErrQ = 301, kSErrK = 302, kSErrV = 303, kSErrEmpty = 304, kSErrS = 305, kSErrP = 306,
              kSErrPv = 307, kSErrDrain = 308 };
 
-constexpr float kPShift = 8.0f;     // P in [0,1] is multiplied by 2^8 before rounding to e4m3 (max 448)
+// P is multiplied by 2^kPShift before rounding to e4m3 (largest finite value 448). The running maximum used
+// in the exponent may lag the true one by up to kLazy (log2 units) before O is rescaled, so P <= 2^kLazy and
+// P * 2^kPShift <= 256. Without the lag nearly every entry has some row of the warp whose maximum grew, and
+// each such rescale has to wait for the previous P.V GEMM: the softmax and the tensor pipe then alternate
+// instead of overlapping.
+constexpr float kPShift = 5.0f;
+constexpr float kLazy = 3.0f;
 
 // D = 128 only: rows of the 8-bit tensors are exactly one 128-byte swizzle atom.
 template <typename T>
@@ -204,7 +210,7 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int row = tid;
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const float sq = p.qscale[static_cast<size_t>(bh) * p.mb + tile] * p.scale_log2;
-    float m_used = -INFINITY, l = 0.f;
+    float m_true = -INFINITY, m_used = -INFINITY, l = 0.f;
     bool ok = !*abortp;
     for (int j = 0; ok && j < n_ent; ++j) {
       const int b = j & 1;
@@ -233,11 +239,12 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         im3 = max(im3, static_cast<int32_t>(sv[c + 3]));
       }
       const float mx = static_cast<float>(max(max(im0, im1), max(im2, im3))) * sc;
-      const bool need = mx > m_used;            // exact running maximum: P stays in [0, 1]
+      m_true = fmaxf(m_true, mx);
+      const bool need = m_true > m_used + kLazy;   // also true on the first block (m_used = -inf)
       if (j > 0 && __any_sync(0xffffffffu, need)) {
         if (!mbar_wait(BAR(B_PV + ((j - 1) & 1)), ((j - 1) >> 1) & 1, kSErrPv, p.err)) { ok = false; break; }
         tc_fence_after();
-        const float alpha = need ? ex2s(m_used - mx) : 1.0f;
+        const float alpha = need ? ex2s(m_used - m_true) : 1.0f;
 #pragma unroll
         for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t ov[32];
@@ -249,8 +256,8 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
       }
       if (need) {
-        l *= ex2s(m_used - mx);
-        m_used = mx;
+        l *= ex2s(m_used - m_true);
+        m_used = m_true;
       }
       uint32_t pk[16];
       float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;

@@ -29,11 +29,17 @@ def test_sage_sparse_branch(B, H, L, ratio, koff):
     bm = ops.block_map(q.cuda(), k.cuda(), ratio, 128, 64)
     got = ops.sage_sla_attention(q.cuda(), k.cuda(), v.cuda(), w, None, bm, sparse_only=True).float().cpu()
     lut = bm.lut.cpu().long()
-    ref_q = O.sage_sparse_fwd(q, k, v, lut, 128, 64, p_scale=256.0)
+    ref_q = O.sage_sparse_fwd(q, k, v, lut, 128, 64, p_scale=32.0)
     ref_f, _ = O.sparse_fwd_gather(q, k, v, lut, 128, 64)
     assert torch.isfinite(got).all()
-    assert_close_parity(got, ref_q, cos_min=0.999, l1_max=3e-2, what="vs quantized oracle")
+    # The kernel lets the running maximum in the exponent lag the true one by up to 2^3 before it rescales O, so
+    # its e4m3 rounding points differ from the oracle's (exact maximum): the two quantized results agree to
+    # about sqrt(2) x the quantization noise, and the kernel must be as close to the un-quantized result as the
+    # oracle's recipe is.
+    assert_close_parity(got, ref_q, cos_min=0.999, l1_max=5e-2, what="vs quantized oracle")
     assert cos_sim(got, ref_f) >= 0.995, "vs un-quantized sparse attention"
+    from helpers import rel_l1
+    assert rel_l1(got, ref_f) <= 1.1 * rel_l1(ref_q, ref_f) + 2e-3, (rel_l1(got, ref_f), rel_l1(ref_q, ref_f))
 
 
 def test_sage_module_matches_oracle_and_16bit_module():
