@@ -52,7 +52,6 @@ struct LinBwdParams {
 int convert_proj(const sla_shape* s, const float* w, const float* bias, void* out, cudaStream_t st);
 int run_sparse_fwd_mma(const sla_shape* s, const FwdParams& p, bool lin, cudaStream_t st);
 int run_sparse_fwd_tc(const sla_shape* s, const FwdParams& p, cudaStream_t st);
-int run_linear_readout(const sla_shape* s, const FwdParams& p, cudaStream_t st);
 int run_feature_map(const sla_shape* s, const void* x, void* out, cudaStream_t st);
 int run_linear_readout_unselected(const sla_shape* s, const FwdParams& p, const void* cnum, const float* cden,
                                   cudaStream_t st);

@@ -12,6 +12,8 @@
 // Kernel structure = sparse_fwd_tc.cu with BLKQ = 128: S = Q8 K8^T by kind::i8 (s32 accumulators in
 // TMEM), softmax in fp32 on S * sq * sk * scale * log2e, P written back to TMEM as e4m3 and multiplied
 // with the e4m3 V tile (MN-major B operand) by kind::f8f6f4.
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "tc_common.cuh"
@@ -27,6 +29,10 @@ struct SageParams {
   int* err;
   int L, mb, nb, topk;
   float scale_log2;
+  // fused linear read-out + proj_l + sum in the epilogue (SageSLA/core.py:148-158); feature < 0: sparse branch only
+  int feature;
+  const void* lin_state;   // [BH][2*D*D + D] T: H, z, H W^T
+  const void* wbits;       // [D*D + D] T: W, bias
 };
 
 __device__ __forceinline__ float ex2s(float x) {
@@ -43,7 +49,7 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 }
 
 enum : int { kSErrQ = 301, kSErrK = 302, kSErrV = 303, kSErrEmpty = 304, kSErrS = 305, kSErrP = 306,
-             kSErrPv = 307, kSErrDrain = 308 };
+             kSErrPv = 307, kSErrDrain = 308, kSErrQ16 = 309, kSErrHw = 310, kSErrPhi = 311, kSErrLin = 312 };
 
 // P is multiplied by 2^kPShift before rounding to e4m3 (largest finite value 448). The running maximum used
 // in the exponent may lag the true one by up to kLazy (log2 units) before O is rescaled, so P <= 2^kLazy and
@@ -57,21 +63,27 @@ constexpr float kLazy = 3.0f;
 template <typename T>
 __global__ void __launch_bounds__(192, 2)
 sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, SageParams p) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                   const __grid_constant__ CUtensorMap tmQ16, const __grid_constant__ CUtensorMap tmHW, SageParams p) {
   constexpr int D = 128;
   constexpr int Q_BYTES = 128 * 128, KV_BYTES = 64 * 128;      // 8-bit tiles
   constexpr int O_SLAB = 128 * 128;                            // 16-bit output staging, 2 slabs
   constexpr int NS = 4;                                        // ring stages (K and V each)
   constexpr uint32_t IDESC_S = idesc_i8(128, 64);
   constexpr uint32_t IDESC_PV = idesc_e4m3(128, D, 1);
+  constexpr int FMT16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr uint32_t IDESC_LIN = idesc_f16(FMT16, 128, D, 0, 1);   // phi(Q) (K-major) x H W^T (MN-major), 16-bit
+  constexpr int Q16_SLAB = 128 * 128, HW_STAGE = 64 * 256, HW_SLAB = 64 * 128;
   constexpr uint32_t TMEM_COLS = 256;
   constexpr int COL_O = 0, COL_S = D;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[4 * NS + 7];
+  __shared__ __align__(8) uint64_t bars[4 * NS + 11];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ float s_vscale[D];
+  __shared__ uint32_t s_zp[D / 2];   // z of the linear state, pairs of T
+  __shared__ float s_bias[D];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, bh = blockIdx.y;
@@ -92,6 +104,10 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   // (entry j signals pv_done[j & 1]: a parity wait only tells neighbouring phases apart)
   constexpr int B_Q = 0, B_K = 1, B_V = 1 + NS, B_KE = 1 + 2 * NS, B_VE = 1 + 3 * NS, B_S = 1 + 4 * NS,
                 B_P = 3 + 4 * NS, B_PV = 5 + 4 * NS;
+  // fused read-out: 16-bit Q tile landed in the K ring | H W^T landed in the V ring | phi(q) written | GEMM done
+  constexpr int B_Q16 = 7 + 4 * NS, B_HW = 8 + 4 * NS, B_PHI = 9 + 4 * NS, B_LIN = 10 + 4 * NS;
+  const bool fused = p.feature >= 0;
+  const uint32_t sQ16 = sK0, sHW = sV0;                // the rings are idle by then (4 x 8 KB each = 32 KB)
 
   if (tid == 0) {
     s_abort = *reinterpret_cast<volatile int*>(p.err) != 0;
@@ -103,6 +119,10 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int b = 0; b < 2; ++b) { mbar_init(BAR(B_S + b), 1); mbar_init(BAR(B_P + b), 128); }
     mbar_init(BAR(B_PV), 1);
     mbar_init(BAR(B_PV + 1), 1);
+    mbar_init(BAR(B_Q16), 1);
+    mbar_init(BAR(B_HW), 1);
+    mbar_init(BAR(B_PHI), 128);
+    mbar_init(BAR(B_LIN), 1);
     fence_barrier_init();
     fence_proxy_async_smem();
   }
@@ -116,6 +136,11 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   }
   for (int i = tid; i < D; i += 192) s_vscale[i] = p.vscale[static_cast<size_t>(bh) * D + i];
+  if (fused && tid < D) {
+    const T* rec = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (2 * D * D + D);
+    if (tid < D / 2) s_zp[tid] = reinterpret_cast<const uint32_t*>(rec + D * D)[tid];
+    s_bias[tid] = Elem<T>::to_f(static_cast<const T*>(p.wbits)[D * D + tid]);
+  }
   if (warp == 5) {
     tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
     tmem_relinquish();
@@ -150,6 +175,28 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tma_load_3d(sV0 + s * KV_BYTES, &tmV, BAR(B_V + s), 0, ulist[j] * 64, bh);
           issued_v = j + 1;
         }
+      }
+      if (fused && !*abortp) {
+        // 16-bit Q tile into the K ring once the last S GEMMs have read it, H W^T into the V ring once the last
+        // P.V GEMMs have (that load overlaps the feature map of the softmax warps)
+        bool ring_free = true;
+        for (int j = max(0, n_ent - NS); ring_free && j < n_ent; ++j)
+          ring_free = mbar_wait(BAR(B_KE + j % NS), (j / NS) & 1, kSErrEmpty, p.err);
+        if (ring_free) {
+          mbar_expect_tx(BAR(B_Q16), 2 * Q16_SLAB);
+          for (int c = 0; c < 2; ++c) tma_load_3d(sQ16 + c * Q16_SLAB, &tmQ16, BAR(B_Q16), c * 64, tile * 128, bh);
+          for (int j = max(0, n_ent - NS); ring_free && j < n_ent; ++j)
+            ring_free = mbar_wait(BAR(B_VE + j % NS), (j / NS) & 1, kSErrEmpty, p.err);
+          if (ring_free) {
+            mbar_expect_tx(BAR(B_HW), D * D * 2);
+            for (int r = 0; r < 2; ++r)
+              for (int c = 0; c < 2; ++c)
+                tma_load_3d(sHW + r * HW_STAGE + c * HW_SLAB, &tmHW, BAR(B_HW), c * 64, r * 64, bh);
+            if (*abortp) mbar_wait(BAR(B_HW), 0, kSErrDrain, p.err);
+          }
+          if (!ring_free || *abortp) mbar_wait(BAR(B_Q16), 0, kSErrDrain, p.err);
+        }
+        if (!ring_free) *abortp = 1;
       }
       if (*abortp) {
         mbar_wait(BAR(B_Q), 0, kSErrDrain, p.err);
@@ -202,6 +249,23 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tc_commit(BAR(B_PV + (j & 1)));
         }
         __syncwarp();
+      }
+      if (ok && fused) {
+        // LIN[128 x D] = phi(Q) (H W^T), 16-bit operands, into the idle S columns
+        ok = warp_all(mbar_wait(BAR(B_HW), 0, kSErrHw, p.err) && mbar_wait(BAR(B_PHI), 0, kSErrPhi, p.err));
+        if (ok) {
+          tc_fence_after();
+          const uint32_t a_lo = desc_lo(sQ16, 16);
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t hw_lo = desc_lo(sHW + (kk >> 2) * HW_STAGE, HW_SLAB) + (((kk & 3) * 2048) >> 4);
+              mma_ss(tmem + COL_S, a_lo + (((kk >> 2) * Q16_SLAB + (kk & 3) * 32) >> 4), hw_lo, IDESC_LIN, kk > 0 ? 1u : 0u);
+            }
+            tc_commit(BAR(B_LIN));
+          }
+          __syncwarp();
+        }
       }
       if (!ok) *abortp = 1;
     }
@@ -286,30 +350,126 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const float inv = 1.0f / l;                       // l carries the 2^kPShift of P
       const int grow = tile * 128 + row;
       if (grow < L) p.lse[static_cast<size_t>(bh) * L + grow] = m_used + log2f(l) - kPShift;
+      // 16-byte chunk ch of this thread's row inside a 128-row, 16-bit tile at `tile_base`
+      auto chunk_addr = [&](uint32_t tile_base, int ch) {
+        return tile_base + (ch >> 3) * O_SLAB + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
+      };
+      float rden = 0.f;
+      bool lin_ok = true;
+      if (fused) {
+        // ---- phi(q) of this thread's row, written over the row of the 16-bit Q tile (core.py:90) ----
+        lin_ok = mbar_wait(BAR(B_Q16), 0, kSErrQ16, p.err);
+        if (lin_ok) {
+          float dsum = 0.f;        // sum_d round(phi_d * z_d), core.py:95
+          auto emit_phi = [&](int ch, const float (&f)[8]) {
+            uint32_t w[4];
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t ov[32];
-        tmem_ld_x32(tmem + lane_addr + COL_O + c0, ov);
-        tmem_wait_ld();
-        const uint32_t slab = sO + (c0 >> 6) * O_SLAB + row * 128;
+            for (int i = 0; i < 4; ++i) {
+              w[i] = Elem<T>::pack2(f[2 * i], f[2 * i + 1]);
+              const float2 pz = Elem<T>::unpack2(Elem<T>::mul2(w[i], s_zp[ch * 4 + i]));   // each product rounded to T
+              dsum += pz.x + pz.y;
+            }
+            st_shared_v4(chunk_addr(sQ16, ch), w[0], w[1], w[2], w[3]);
+          };
+          auto load_x = [&](int ch, float (&f)[8]) {
+            uint32_t w0, w1, w2, w3;
+            ld_shared_v4(chunk_addr(sQ16, ch), w0, w1, w2, w3);
+            float2 a = Elem<T>::unpack2(w0), b2 = Elem<T>::unpack2(w1), c = Elem<T>::unpack2(w2), d = Elem<T>::unpack2(w3);
+            f[0] = a.x; f[1] = a.y; f[2] = b2.x; f[3] = b2.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+          };
+          if (p.feature == SLA_PHI_SOFTMAX) {
+            float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint32_t w[4];
+            for (int ch = 0; ch < D / 8; ++ch) {
+              float f[8];
+              load_x(ch, f);
+              mx0 = fmaxf(mx0, fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])));
+              mx1 = fmaxf(mx1, fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])));
+            }
+            const float neg_mx = -fmaxf(mx0, mx1) * kLog2e;
+            // exp(x - max) in fp32 is parked in the idle S columns of this thread's TMEM lane
+            float e0 = 0.f, e1 = 0.f;
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = c0 + q4 * 8 + 2 * e;
-            w[e] = Elem<T>::pack2(__uint_as_float(ov[q4 * 8 + 2 * e]) * inv * s_vscale[c],
-                                  __uint_as_float(ov[q4 * 8 + 2 * e + 1]) * inv * s_vscale[c + 1]);
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              uint32_t ev[32];
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                float f[8];
+                load_x((c0 >> 3) + q4, f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float e = ex2s(fmaf(f[i], kLog2e, neg_mx));
+                  if (i & 1) e1 += e; else e0 += e;
+                  ev[q4 * 8 + i] = __float_as_uint(e);
+                }
+              }
+              tmem_st_x32(tmem + lane_addr + COL_S + c0, ev);
+            }
+            tmem_wait_st();
+            const float inv_s = 1.f / (e0 + e1);
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              uint32_t ev[32];
+              tmem_ld_x32(tmem + lane_addr + COL_S + c0, ev);
+              tmem_wait_ld();
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(ev[q4 * 8 + i]) * inv_s;
+                emit_phi((c0 >> 3) + q4, f);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int ch = 0; ch < D / 8; ++ch) {
+              float f[8];
+              load_x(ch, f);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                if (p.feature == SLA_PHI_RELU) f[i] = fmaxf(f[i], 0.f);
+                else f[i] = f[i] > 0.f ? f[i] + 1.f : __expf(f[i]);      // elu(x) + 1
+              }
+              emit_phi(ch, f);
+            }
           }
-          const int chunk = ((c0 & 63) >> 3) + q4;
-          const uint32_t addr = slab + ((chunk ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
-                       : "memory");
+          rden = 1.f / round_to<T>(1e-5f + round_to<T>(dsum));
+          fence_proxy_async_smem();
+          tc_fence_before();
+          mbar_arrive(BAR(B_PHI));
+          lin_ok = mbar_wait(BAR(B_LIN), 0, kSErrLin, p.err);
+          if (lin_ok) tc_fence_after();
+        }
+        if (!lin_ok) *abortp = 1;
+      }
+      if (lin_ok) {
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t ov[32], lv[32];
+          tmem_ld_x32(tmem + lane_addr + COL_O + c0, ov);
+          if (fused) tmem_ld_x32(tmem + lane_addr + COL_S + c0, lv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int ci = q4 * 8 + 2 * e, c = c0 + ci;
+              w[e] = Elem<T>::pack2(__uint_as_float(ov[ci]) * inv * s_vscale[c],
+                                    __uint_as_float(ov[ci + 1]) * inv * s_vscale[c + 1]);
+              if (fused) {   // o = o_s + round(lin / den + bias) (core.py:96-100)
+                const uint32_t lin2 = Elem<T>::pack2(fmaf(__uint_as_float(lv[ci]), rden, s_bias[c]),
+                                                     fmaf(__uint_as_float(lv[ci + 1]), rden, s_bias[c + 1]));
+                w[e] = Elem<T>::add2(w[e], lin2);
+              }
+            }
+            st_shared_v4(chunk_addr(sO, (c0 >> 3) + q4), w[0], w[1], w[2], w[3]);
+          }
         }
       }
       fence_proxy_async_smem();
       asm volatile("bar.sync 1, 128;\n" ::: "memory");
-      if (tid == 0) {
+      if (tid == 0 && !*abortp) {
         for (int c = 0; c < 2; ++c) tma_store_3d(&tmO, sO + c * O_SLAB, c * 64, tile * 128, bh);
         tma_store_commit();
         tma_store_wait_all();
@@ -333,10 +493,10 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // One CTA per block of `blk` rows: symmetric abs-max INT8, scale = amax / 127 (zero blocks get scale 1e-8/127).
 // z = 0: Q in blocks of 128 rows; z = 1: K - mean in blocks of 64 rows.
 template <typename T>
-__global__ void __launch_bounds__(256) sage_quant_qk_kernel(const T* __restrict__ q, const T* __restrict__ k,
-                                                            const float* __restrict__ kmean, int8_t* __restrict__ q8,
-                                                            int8_t* __restrict__ k8, float* __restrict__ qscale,
-                                                            float* __restrict__ kscale, int L, int mb, int nb) {
+__global__ void __launch_bounds__(256, 3) sage_quant_qk_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                               const float* __restrict__ kmean, int8_t* __restrict__ q8,
+                                                               int8_t* __restrict__ k8, float* __restrict__ qscale,
+                                                               float* __restrict__ kscale, int L, int mb, int nb) {
   constexpr int D = 128;
   __shared__ float red[8];
   const bool is_k = blockIdx.z == 1;
@@ -349,25 +509,27 @@ __global__ void __launch_bounds__(256) sage_quant_qk_kernel(const T* __restrict_
   float mean[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) mean[e] = is_k ? kmean[static_cast<size_t>(bh) * D + c + e] : 0.f;
-  float vals[8][8];                             // up to 8 rows per thread (128 rows / 16 row groups)
+  // The rows stay packed in registers (4 words per row) between the abs-max pass and the rounding pass, which
+  // keeps three CTAs per SM resident; all loads of a thread are issued up front.
+  uint4 raw[8];                                 // up to 8 rows per thread (128 rows / 16 row groups)
   const int rows_per_thread = blk / 16;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = ib * blk + (tid >> 4) + 16 * i;
+    raw[i] = (i < rows_per_thread && r < L) ? *reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * D + c)
+                                            : make_uint4(0u, 0u, 0u, 0u);
+  }
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int r = ib * blk + (tid >> 4) + 16 * i;
     if (i < rows_per_thread && r < L) {
-      uint4 raw = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * D + c);
-      const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
+      const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw[i]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float2 f = Elem<T>::unpack2(u[e]);
-        vals[i][2 * e] = f.x - mean[2 * e];
-        vals[i][2 * e + 1] = f.y - mean[2 * e + 1];
-        amax = fmaxf(amax, fmaxf(fabsf(vals[i][2 * e]), fabsf(vals[i][2 * e + 1])));
+        amax = fmaxf(amax, fmaxf(fabsf(f.x - mean[2 * e]), fabsf(f.y - mean[2 * e + 1])));
       }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) vals[i][e] = 0.f;
     }
   }
   amax = warp_max(amax);
@@ -382,11 +544,13 @@ __global__ void __launch_bounds__(256) sage_quant_qk_kernel(const T* __restrict_
   for (int i = 0; i < 8; ++i) {
     const int r = ib * blk + (tid >> 4) + 16 * i;
     if (i < rows_per_thread && r < L) {
+      const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw[i]);
       uint32_t w[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        int b0 = __float2int_rn(vals[i][4 * h] * inv), b1 = __float2int_rn(vals[i][4 * h + 1] * inv);
-        int b2 = __float2int_rn(vals[i][4 * h + 2] * inv), b3 = __float2int_rn(vals[i][4 * h + 3] * inv);
+        float2 f0 = Elem<T>::unpack2(u[2 * h]), f1 = Elem<T>::unpack2(u[2 * h + 1]);
+        int b0 = __float2int_rn((f0.x - mean[4 * h]) * inv), b1 = __float2int_rn((f0.y - mean[4 * h + 1]) * inv);
+        int b2 = __float2int_rn((f1.x - mean[4 * h + 2]) * inv), b3 = __float2int_rn((f1.y - mean[4 * h + 3]) * inv);
         w[h] = (b0 & 0xff) | ((b1 & 0xff) << 8) | ((b2 & 0xff) << 16) | (static_cast<uint32_t>(b3 & 0xff) << 24);
       }
       *reinterpret_cast<uint2*>(dst + static_cast<size_t>(r) * D + c) = make_uint2(w[0], w[1]);
@@ -461,7 +625,8 @@ __global__ void __launch_bounds__(256) sage_quant_v_kernel(const T* __restrict__
 
 template <typename T>
 static int run_sage_typed(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
-                          void* o_s, float* lse, unsigned char* ws, cudaStream_t st) {
+                          void* o_s, float* lse, unsigned char* ws, const void* lin_state, const void* wbits,
+                          cudaStream_t st) {
   const int bh = s->B * s->H, L = s->L, D = 128;
   const int mb = ceil_div(L, 128), nb = ceil_div(L, 64);
   WsSage w = ws_sage(s);
@@ -485,12 +650,21 @@ static int run_sage_typed(const sla_shape* s, const void* q, const void* k, cons
   sage_quant_v_kernel<T><<<dim3(nb, bh), 256, 0, st>>>(static_cast<const T*>(v), vs, v8, L);
   SLA_LAUNCH_OK();
 
-  CUtensorMap tq, tk, tv, to;
+  CUtensorMap tq, tk, tv, to, tq16, thw;
   if ((rc = make_tmap_3d_u8(&tq, q8, 128, L, bh, 128)) != SLA_OK) return rc;
   if ((rc = make_tmap_3d_u8(&tk, k8, 128, L, bh, 64)) != SLA_OK) return rc;
   if ((rc = make_tmap_3d_u8(&tv, v8, 128, L, bh, 64)) != SLA_OK) return rc;
   if ((rc = make_tmap_3d(&to, o_s, s->dtype, D, L, bh, 128)) != SLA_OK) return rc;
+  const bool fused = lin_state != nullptr;
+  tq16 = to; thw = to;
+  if (fused) {
+    if ((rc = make_tmap_3d(&tq16, q, s->dtype, D, L, bh, 128)) != SLA_OK) return rc;
+    const char* hw = static_cast<const char*>(lin_state) + (size_t(D) * D + D) * 2;   // H W^T behind H and z
+    if ((rc = make_tmap_rows(&thw, hw, s->dtype, D, D, bh, size_t(2 * D * D + D) * 2, 64)) != SLA_OK) return rc;
+  }
   tc::SageParams p;
+  p.feature = fused ? s->feature_map : -1;
+  p.lin_state = lin_state; p.wbits = wbits;
   p.lut = lut; p.qscale = qs; p.kscale = ks; p.vscale = vs; p.lse = lse;
   p.err = tc_error_word();
   if (p.err == nullptr) return SLA_ERR_CUDA;
@@ -500,7 +674,7 @@ static int run_sage_typed(const sla_shape* s, const void* q, const void* k, cons
   const int smem = 1024 + 2 * 128 * 128 + 2 * 4 * 64 * 128 + s->topk * 8 + 16;
   if (smem > 113 * 1024) return SLA_ERR_BAD_TOPK;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  kern<<<dim3(mb, bh), 192, smem, st>>>(tq, tk, tv, to, p);
+  kern<<<dim3(mb, bh), 192, smem, st>>>(tq, tk, tv, to, tq16, thw, p);
   SLA_LAUNCH_OK();
   return SLA_OK;
 }
@@ -523,19 +697,19 @@ extern "C" int sage_sla_fwd(const sla_shape* s, const void* q, const void* k, co
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   unsigned char* base = static_cast<unsigned char*>(ws);
   float* lse = reinterpret_cast<float*>(base + wsz.lse);
-  // sparse branch into o
-  rc = s->dtype == SLA_BF16 ? run_sage_typed<__nv_bfloat16>(s, q, k, v, lut, o, lse, base, st)
-                            : run_sage_typed<__half>(s, q, k, v, lut, o, lse, base, st);
-  if (rc != SLA_OK || (s->flags & SLA_FLAG_SPARSE_ONLY)) return rc;
-  // linear branch + proj_l exactly as in the 16-bit path (SageSLA/core.py:148-158)
-  if (!w || !lin_state) return SLA_ERR_NULL;
-  WsLinearState wl = ws_linear_state(s);
+  const void* state = nullptr;
   void* wbits = base + wsz.wbits;
-  if ((rc = convert_proj(s, w, bias, wbits, st)) != SLA_OK) return rc;
-  if ((rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wsz.lin + wl.partial), wl.nch, wl.rows, st)) != SLA_OK) return rc;
-  if ((rc = run_state_proj(s, lin_state, wbits, st)) != SLA_OK) return rc;
-  FwdParams p;
-  p.q = q; p.k = k; p.v = v; p.lut = lut; p.o = o; p.o_s = o; p.lse = lse; p.lin_state = lin_state; p.wbits = wbits;
-  p.L = s->L; p.mb = ceil_div(s->L, s->BLKQ); p.topk = s->topk; p.scale_log2 = softmax_scale(s) * kLog2e;
-  return run_linear_readout(s, p, st);
+  if (!(s->flags & SLA_FLAG_SPARSE_ONLY)) {
+    // linear-branch state first (SageSLA/core.py:148-158 uses the same branch as the 16-bit module); the
+    // read-out, proj_l and the final sum run in the epilogue of the quantized kernel
+    if (!w || !lin_state) return SLA_ERR_NULL;
+    if (!aligned16(lin_state)) return SLA_ERR_BAD_ALIGN;
+    WsLinearState wl = ws_linear_state(s);
+    if ((rc = convert_proj(s, w, bias, wbits, st)) != SLA_OK) return rc;
+    if ((rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wsz.lin + wl.partial), wl.nch, wl.rows, st)) != SLA_OK) return rc;
+    if ((rc = run_state_proj(s, lin_state, wbits, st)) != SLA_OK) return rc;
+    state = lin_state;
+  }
+  return s->dtype == SLA_BF16 ? run_sage_typed<__nv_bfloat16>(s, q, k, v, lut, o, lse, base, state, wbits, st)
+                              : run_sage_typed<__half>(s, q, k, v, lut, o, lse, base, state, wbits, st);
 }
