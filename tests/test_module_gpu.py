@@ -152,3 +152,28 @@ def test_unselected_scope_vs_oracle(feat, D, BLKQ, L, ratio):
     assert (o_all - o_ref.float()).abs().mean() > 5 * (o - o_ref.float()).abs().mean()
     with pytest.raises(NotImplementedError):
         m(q.cuda().requires_grad_(True), k.cuda(), v.cuda())
+
+
+def test_forward_is_cuda_graph_capturable():
+    """The whole forward (block map, linear state, fused tcgen05 kernel) enqueues on the caller's stream only and
+    never synchronises (the top-k count comes from shapes, utils.py:61-62), so it can be captured into a CUDA
+    graph; the replay must reproduce the eager result bit for bit."""
+    import sla_b200
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(1, 2, 2048, 128, generator=g).bfloat16().cuda() for _ in range(3))
+    m = sla_b200.SparseLinearAttention(128, 0.1).cuda()
+    with torch.no_grad():
+        m.proj_l.weight.copy_(torch.randn(128, 128, generator=g) * 0.05)
+        eager = m(q, k, v)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            m(q, k, v)                      # warm-up on the side stream (function attributes, symbol lookups)
+        torch.cuda.current_stream().wait_stream(s)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = m(q, k, v)
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+    assert torch.equal(out, eager)
