@@ -58,7 +58,9 @@ int run_linear_readout_unselected(const sla_shape* s, const FwdParams& p, const 
 int run_state_proj(const sla_shape* s, void* lin_state, const void* wbits, cudaStream_t st);
 int read_tc_error(int* out, bool clear);
 void set_trace_buffer(long long* p);
+long long* trace_buffer();
 int run_sparse_bwd_tc(const sla_shape* s, const BwdParams& p, void* stats, cudaStream_t st);
+int run_sparse_bwd_dq_pair(const sla_shape* s, const BwdParams& p, const void* stats, int Lpad, cudaStream_t st);
 int run_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, float* partial,
                      int nch, int rows, cudaStream_t st);
 int run_linear_state_static(const sla_shape* s, const void* k, const void* v, void* lin_state, cudaStream_t st);

@@ -472,7 +472,7 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (tid == 0 && !*abortp) {
         for (int c = 0; c < 2; ++c) tma_store_3d(&tmO, sO + c * O_SLAB, c * 64, tile * 128, bh);
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read();
       }
     }
   }

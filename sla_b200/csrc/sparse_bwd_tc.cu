@@ -107,7 +107,8 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   // 0 x_full | 1..NS y_full | NS+1..2NS y_empty | then t_full[2], c_full[2], acc_done
   constexpr int B_X = 0, B_YF = 1, B_YE = 1 + NS, B_T = 1 + 2 * NS, B_C = 3 + 2 * NS, B_ACC = 5 + 2 * NS, B_XT = 6 + 2 * NS;
 
-  if (tid == 0) {
+  if (warp == 16 && lane == 0) {
+    // the producer lane sets the barriers up itself and requests the stationary tiles before it merges the lists
     s_abort = *reinterpret_cast<volatile int*>(p.err) != 0;
     mbar_init(BAR(B_X), 1);
     for (int s = 0; s < NS; ++s) {
@@ -122,6 +123,13 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     mbar_init(BAR(B_XT), 512);
     fence_barrier_init();
     fence_proxy_async_smem();
+    if (!s_abort) {
+      mbar_expect_tx(BAR(B_X), 2 * X_BYTES);
+      for (int c = 0; c < SLABS; ++c) {
+        tma_load_3d(sX1 + c * X_SLAB, &tmX1, BAR(B_X), c * 64, tile * 128, bh);
+        tma_load_3d(sX2 + c * X_SLAB, &tmX2, BAR(B_X), c * 64, tile * 128, bh);
+      }
+    }
   }
   if (warp == 16) {
     if (lane == 0) {
@@ -152,18 +160,15 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     for (int i = lane; i < na; i += 32) ra[i] = ga[i];
     for (int i = lane; i < nb2; i += 32) rb[i] = gb[i];
     __syncwarp();
-    if (lane == 0) {
-      int a = 0, b = 0, n = 0;
-      const int full = (!KVS && BM == 128) ? 3 : 1;
-      while (a < na || b < nb2) {
-        int va = a < na ? ra[a] : 0x7fffffff;
-        int vb = b < nb2 ? rb[b] : 0x7fffffff;
-        if (va == vb) { ulist[n++] = va | (3 << 28); ++a; ++b; }
-        else if (va < vb) { ulist[n++] = va | (full << 28); ++a; }
-        else { ulist[n++] = vb | (2 << 28); ++b; }
-      }
-      s_n_entries = n;
+    int n;
+    if (!KVS && BM == 128) {
+      for (int i = lane; i < na; i += 32) ulist[i] = ra[i] | (3 << 28);
+      n = na;
+      __syncwarp();
+    } else {
+      n = warp_union_lists(ra, na, rb, nb2, ulist, 1 << 28, 2 << 28, lane);
     }
+    if (lane == 0) s_n_entries = n;
   }
   if (warp == 17) {
     tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
@@ -186,11 +191,6 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   if (warp == 16) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0 && !*abortp) {
-      mbar_expect_tx(BAR(B_X), 2 * X_BYTES);
-      for (int c = 0; c < SLABS; ++c) {
-        tma_load_3d(sX1 + c * X_SLAB, &tmX1, BAR(B_X), c * 64, tile * 128, bh);
-        tma_load_3d(sX2 + c * X_SLAB, &tmX2, BAR(B_X), c * 64, tile * 128, bh);
-      }
       int issued = 0;
       for (int j = 0; j < n_ent; ++j) {
         const int s = j % NS, use = j / NS;
@@ -428,7 +428,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
             for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO2, sX2 + c * X_SLAB, c * 64, tile * 128, bh);
         }
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read();
       }
     }
   }
@@ -447,6 +447,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
 // Diagnostic timeline buffer (2 x 1024 int64), set through sla_debug_set_trace.
 static long long* g_trace_buffer = nullptr;
 void set_trace_buffer(long long* p) { g_trace_buffer = p; }
+long long* trace_buffer() { return g_trace_buffer; }
 
 // delta = rowsum(o_s * dO) (kernel.py:102-105) and lse, interleaved into a padded (B*H, Lpad) array;
 // rows in [L, Lpad) get lse = +inf, delta = 0 so that they contribute P = 0.
@@ -543,7 +544,10 @@ static int run_bwd_tc_typed(const sla_shape* s, const BwdParams& bp, float2* sta
   bwd_prep_kernel<T, D><<<dim3(ceil_div(Lpad, 64), bh), 256, 0, st>>>(
       static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L, Lpad);
   SLA_LAUNCH_OK();
-  int rc = launch_bwd_tc<T, D, BM, false>(s, bp, stats, Lpad, st);
+  // dQ: the kernel that takes list entries in pairs (sparse_bwd_dq_tc.cu); this file's dQ variant only when
+  // that one's shared-memory need does not fit
+  int rc = run_sparse_bwd_dq_pair(s, bp, stats, Lpad, st);
+  if (rc == SLA_ERR_BAD_SHAPE) rc = launch_bwd_tc<T, D, BM, false>(s, bp, stats, Lpad, st);
   if (rc != SLA_OK) return rc;
   return launch_bwd_tc<T, D, BM, true>(s, bp, stats, Lpad, st);
 }

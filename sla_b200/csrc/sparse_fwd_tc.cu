@@ -139,25 +139,15 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int32_t* src = p.lut + (static_cast<size_t>(bh) * p.mb + (BM == 128 ? tile : 2 * tile)) * p.topk;
     for (int i = lane; i < rows * p.topk; i += 32) raw[i] = src[i];
     __syncwarp();
-    if (lane == 0) {
-      if (BM == 128) {
-        for (int i = 0; i < p.topk; ++i) ulist[i] = raw[i] | (3 << 28);
-        s_n_entries = p.topk;
-      } else {
-        const int32_t* ra = raw;
-        const int32_t* rb = raw + p.topk;
-        const int nbv = rows == 2 ? p.topk : 0;
-        int a = 0, b = 0, n = 0;
-        while (a < p.topk || b < nbv) {
-          int va = a < p.topk ? ra[a] : 0x7fffffff;
-          int vb = b < nbv ? rb[b] : 0x7fffffff;
-          if (va == vb) { ulist[n++] = va | (3 << 28); ++a; ++b; }
-          else if (va < vb) { ulist[n++] = va | (1 << 28); ++a; }
-          else { ulist[n++] = vb | (2 << 28); ++b; }
-        }
-        s_n_entries = n;
-      }
+    int n;
+    if (BM == 128) {
+      for (int i = lane; i < p.topk; i += 32) ulist[i] = raw[i] | (3 << 28);
+      n = p.topk;
+      __syncwarp();
+    } else {
+      n = warp_union_lists(raw, p.topk, raw + p.topk, rows == 2 ? p.topk : 0, ulist, 1 << 28, 2 << 28, lane);
     }
+    if (lane == 0) s_n_entries = n;
   }
   if (warp == 5) {
     tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
@@ -425,7 +415,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (tid == 0) {
           for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO, sQ + c * Q_SLAB, c * 64, tile * 128, bh);
           tma_store_commit();
-          tma_store_wait_all();
+          tma_store_wait_read();
         }
       } else {
         // ---- phi(q) of this thread's row, written over the row in the Q tile (core.py:90) ----
@@ -546,7 +536,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmOs, sV0 + c * Q_SLAB, c * 64, tile * 128, bh);
           for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO, sQ + c * Q_SLAB, c * 64, tile * 128, bh);
           tma_store_commit();
-          tma_store_wait_all();
+          tma_store_wait_read();
         }
       }
     }

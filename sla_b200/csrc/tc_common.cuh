@@ -90,6 +90,93 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, uint32_t
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
+// Enough before the CTA's shared memory goes away: the copy engine has READ the staged tiles (the writes to global
+// memory complete in the background; kernel completion makes them visible).
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+
+// ---- union of two ascending index lists, by one warp ----
+// out = ascending union of a[0, na) and b[0, nb) (each strictly ascending); an element carries flag_a, flag_b or both.
+// Every lane of the warp calls this; ranks come from binary searches in the other list, so the cost is
+// O(log n) shared-memory round trips per 32 elements instead of one per element for a serial merge.
+__device__ __forceinline__ int lower_bound_i32(const int32_t* x, int n, int v) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (x[mid] < v) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+__device__ inline bool warp_is_ascending(const int32_t* x, int n, int lane) {
+  bool ok = true;
+  for (int i = lane; i + 1 < n; i += 32) ok = ok && x[i] < x[i + 1];
+  return __all_sync(0xffffffffu, ok);
+}
+__device__ inline int warp_union_lists(const int32_t* a, int na, const int32_t* b, int nb, int32_t* out,
+                                       int32_t flag_a, int32_t flag_b, int lane) {
+  if (!warp_is_ascending(a, na, lane) || !warp_is_ascending(b, nb, lane)) {
+    // Lists in arbitrary order (torch.topk(sorted=False) gives no order, utils.py:64): a two-pointer walk by
+    // one lane still emits every element of both lists, possibly once per list; the flags keep that correct.
+    int n = 0;
+    if (lane == 0) {
+      int i = 0, j = 0;
+      while (i < na || j < nb) {
+        const int va = i < na ? a[i] : 0x7fffffff, vb = j < nb ? b[j] : 0x7fffffff;
+        if (va == vb) { out[n++] = va | flag_a | flag_b; ++i; ++j; }
+        else if (va < vb) { out[n++] = va | flag_a; ++i; }
+        else { out[n++] = vb | flag_b; ++j; }
+      }
+    }
+    n = __shfl_sync(0xffffffffu, n, 0);
+    __syncwarp();
+    return n;
+  }
+  const uint32_t lt = (1u << lane) - 1u;
+  if (na <= 32 && nb <= 32) {
+    // short lists (the usual top-k): one element of each list per lane, all-pairs comparison through shuffles
+    const int va = lane < na ? a[lane] : 0x7fffffff, vb = lane < nb ? b[lane] : 0x7fffffff;
+    int less_b = 0, less_a = 0;
+    bool dup_a = false, dup_b = false;
+#pragma unroll 8
+    for (int j = 0; j < 32; ++j) {
+      const int bj = __shfl_sync(0xffffffffu, vb, j), aj = __shfl_sync(0xffffffffu, va, j);
+      less_b += (j < nb && bj < va);
+      dup_a = dup_a || (j < nb && bj == va);
+      less_a += (j < na && aj < vb);
+      dup_b = dup_b || (j < na && aj == vb);
+    }
+    const uint32_t ma = __ballot_sync(0xffffffffu, lane < na && dup_a);
+    const uint32_t mb = __ballot_sync(0xffffffffu, lane < nb && dup_b);
+    if (lane < na) out[lane + less_b - __popc(ma & lt)] = va | (dup_a ? (flag_a | flag_b) : flag_a);
+    if (lane < nb && !dup_b) out[less_a + lane - __popc(mb & lt)] = vb | flag_b;
+    __syncwarp();
+    return na + nb - __popc(ma);
+  }
+  int dups = 0;                                   // elements of a seen so far that are also in b
+  for (int base = 0; base < na; base += 32) {
+    const int i = base + lane;
+    const bool valid = i < na;
+    const int va = valid ? a[i] : 0x7fffffff;
+    const int lb = valid ? lower_bound_i32(b, nb, va) : 0;
+    const bool dup = valid && lb < nb && b[lb] == va;
+    const uint32_t m = __ballot_sync(0xffffffffu, dup);
+    // rank = elements of a below va + elements of b below va that are not in a
+    if (valid) out[i + lb - dups - __popc(m & lt)] = va | (dup ? (flag_a | flag_b) : flag_a);
+    dups += __popc(m);
+  }
+  int dups_b = 0;                                 // elements of b seen so far that are also in a
+  for (int base = 0; base < nb; base += 32) {
+    const int i = base + lane;
+    const bool valid = i < nb;
+    const int vb = valid ? b[i] : 0x7fffffff;
+    const int la = valid ? lower_bound_i32(a, na, vb) : 0;
+    const bool dup = valid && la < na && a[la] == vb;
+    const uint32_t m = __ballot_sync(0xffffffffu, dup);
+    if (valid && !dup) out[la + i - dups_b - __popc(m & lt)] = vb | flag_b;
+    dups_b += __popc(m);
+  }
+  __syncwarp();
+  return na + nb - dups;
+}
 
 // ---- tensor memory ----
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
