@@ -14,7 +14,7 @@ namespace tc {
 // bounded wait that ran out. Once it is non-zero every CTA of the tcgen05 kernels leaves as soon as it
 // notices.
 
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s: far above any legitimate wait (microseconds)
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
@@ -54,13 +54,21 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
-// Bounded wait. Returns false (after recording `code`) if the phase did not complete within the
-// spin limit or another CTA has already reported a failure.
+// Bounded wait. Returns false (after recording `code`) if the phase did not complete within kWaitLimitNs of
+// wall-clock time or another CTA has already reported a failure. The bound is on elapsed time, not on the
+// number of polls: a try_wait on a pending phase may itself suspend the thread for a while.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code, int* err) {
   if (mbar_test(bar, parity)) return true;
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t it = 0;; ++it) {
     if (mbar_try(bar, parity)) return true;
-    if ((it & 4095u) == 4095u && *reinterpret_cast<volatile int*>(err) != 0) return false;
+    if ((it & 63u) == 63u && *reinterpret_cast<volatile int*>(err) != 0) return false;
+    if (global_timer_ns() - t0 > kWaitLimitNs) break;
   }
   atomicCAS(err, 0, code);
   return false;
