@@ -263,6 +263,8 @@ def main():
     ap.add_argument("--no-baselines", action="store_true", help="skip the on-GPU reference/flash-attn timings")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--legacy-mma", action="store_true", help="force the mma.sync kernels")
+    ap.add_argument("--graph", action="store_true",
+                    help="also time the step replayed from CUDA graphs (sla_b200.graphed); reported as graph_ms_per_step")
     ap.add_argument("--topk", type=float, default=None, help="override the workload's top-k ratio (c5 sweeps 0.05/0.1/0.2)")
     args = ap.parse_args()
 
@@ -353,6 +355,18 @@ def main():
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    graph_ms = None
+    if args.graph and bwd and not w.quantized:
+        fast = sla_b200.graphed(m, qg, kg, vg)
+
+        def step_graph():
+            o = fast(qg, kg, vg)
+            o.backward(do)
+            qg.grad = kg.grad = vg.grad = None
+            m.proj_l.weight.grad = m.proj_l.bias.grad = None
+
+        graph_ms = timed(step_graph, args.steps, 3, sync)
+        check_device("the graph replay")
     fwd_ms = timed(step_fwd, args.steps, 2, sync)
     if world > 1:
         t = torch.tensor([fwd_ms], dtype=torch.float64, device=dev)
@@ -519,6 +533,7 @@ def main():
         "fwd_ms": fwd_ms, "fwd_bwd_ms": ms,
         "fwd_dense_equiv_tflops": world * w.dense_equiv_flops(False) / fwd_ms / 1e9,
         "sparse_actual_tflops": world * (w.sparse_flops(bwd) + w.linear_flops(bwd)) / ms / 1e9,
+        "graph_ms_per_step": graph_ms,
         "mask_ms": kernels["block_map"]["ms"], "fwd_ms_excluding_mask": fwd_ms - kernels["block_map"]["ms"],
         "fwd_bwd_ms_excluding_mask": ms - kernels["block_map"]["ms"],
         "e2e": {"value": world * dense_fb / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,

@@ -11,10 +11,11 @@ import sys
 import types
 
 from .core import SageSparseLinearAttention, SparseLinearAttention
+from .graphs import graphed
 from .ops import _attention, block_map, get_block_map, sage_sla_attention, sla_attention
 
 __all__ = ["SparseLinearAttention", "SageSparseLinearAttention", "get_block_map", "_attention", "block_map",
-           "sla_attention", "sage_sla_attention", "install_aliases"]
+           "sla_attention", "sage_sla_attention", "install_aliases", "graphed"]
 
 
 def install_aliases() -> None:
