@@ -180,24 +180,28 @@ def test_forward_is_cuda_graph_capturable():
 
 
 def test_graphed_forward_backward_matches_eager():
-    """Forward AND backward captured into CUDA graphs (sla_b200.graphed) reproduce the eager results."""
+    """Forward AND backward captured into CUDA graphs (sla_b200.graphed) reproduce the eager results. The graphed
+    module is captured before anything else touches its parameters (autograd nodes created earlier on another
+    stream would break the capture); a twin module with the same weights gives the eager results."""
     import sla_b200
     g = torch.Generator().manual_seed(12)
     q, k, v, do = (torch.randn(2, 2, 1024, 128, generator=g).bfloat16().cuda() for _ in range(4))
-    m = sla_b200.SparseLinearAttention(128, 0.2).cuda()
+    w = torch.randn(128, 128, generator=g) * 0.05
+    m_graph = sla_b200.SparseLinearAttention(128, 0.2).cuda()
+    m_eager = sla_b200.SparseLinearAttention(128, 0.2).cuda()
     with torch.no_grad():
-        m.proj_l.weight.copy_(torch.randn(128, 128, generator=g) * 0.05)
-    qe, ke, ve = (t.clone().requires_grad_(True) for t in (q, k, v))
-    oe = m(qe, ke, ve)
-    oe.backward(do)
-    dw_e = m.proj_l.weight.grad.clone()
-    m.proj_l.weight.grad = m.proj_l.bias.grad = None
-    fast = sla_b200.graphed(m, qe, ke, ve)
-    m.proj_l.weight.grad = m.proj_l.bias.grad = None
+        m_graph.proj_l.weight.copy_(w)
+        m_eager.proj_l.weight.copy_(w)
     qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    fast = sla_b200.graphed(m_graph, qg, kg, vg)
+    m_graph.proj_l.weight.grad = m_graph.proj_l.bias.grad = None
     og = fast(qg, kg, vg)
     og.backward(do)
+    qe, ke, ve = (t.clone().requires_grad_(True) for t in (q, k, v))
+    oe = m_eager(qe, ke, ve)
+    oe.backward(do)
     torch.cuda.synchronize()
     assert torch.equal(og, oe)
-    for a, b in ((qg.grad, qe.grad), (kg.grad, ke.grad), (vg.grad, ve.grad), (m.proj_l.weight.grad, dw_e)):
+    for a, b in ((qg.grad, qe.grad), (kg.grad, ke.grad), (vg.grad, ve.grad),
+                 (m_graph.proj_l.weight.grad, m_eager.proj_l.weight.grad)):
         assert torch.equal(a, b)
