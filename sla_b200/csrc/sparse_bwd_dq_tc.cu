@@ -135,10 +135,10 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       for (int s = 0; s < NV; ++s) { mbar_init(BAR(B_VF + s), 1); mbar_init(BAR(B_VE + s), 1); }
       mbar_init(BAR(B_T1), 1);
       mbar_init(BAR(B_T2), 1);
-      mbar_init(BAR(B_T1C), 512);
-      mbar_init(BAR(B_C), 512);
+      mbar_init(BAR(B_T1C), 16);     // one arrival per compute warp
+      mbar_init(BAR(B_C), 16);
       mbar_init(BAR(B_ACC), 1);
-      mbar_init(BAR(B_XT), 512);
+      mbar_init(BAR(B_XT), 16);
       mbar_init(BAR(B_LIST), 1);
       fence_barrier_init();
       fence_proxy_async_smem();
@@ -309,7 +309,7 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         tc_fence_before();
       }
     }
-    mbar_arrive(BAR(B_XT));
+    mbar_arrive_warp(BAR(B_XT), lane);
     if (ok) ok = list_ready();
     const int n_pairs = s_n_entries >> 1;
     if (trc) trc[4] = clock64() - clk0;
@@ -326,7 +326,7 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       tmem_ld_x32(t1, sv);
       tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(BAR(B_T1C));                               // T1 may be overwritten with the next pair's scores
+      mbar_arrive_warp(BAR(B_T1C), lane);                               // T1 may be overwritten with the next pair's scores
       float pf[32];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
@@ -346,7 +346,7 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       tmem_st_x16(t2, ds);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(BAR(B_C));
+      mbar_arrive_warp(BAR(B_C), lane);
     }
     if (ok && n_pairs > 0) ok = mbar_wait(BAR(B_ACC), 0, kQErrAcc, p.err);
     if (trc) trc[6] = clock64() - clk0;

@@ -117,10 +117,10 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(BAR(B_T + b), 1);
-      mbar_init(BAR(B_C + b), 256);
+      mbar_init(BAR(B_C + b), 8);      // one arrival per warp of the buffer's two compute groups
     }
     mbar_init(BAR(B_ACC), 1);
-    mbar_init(BAR(B_XT), 512);
+    mbar_init(BAR(B_XT), 16);
     fence_barrier_init();
     fence_proxy_async_smem();
     if (!s_abort) {
@@ -329,7 +329,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         tmem_wait_st();
         tc_fence_before();
       }
-      mbar_arrive(BAR(B_XT));
+      mbar_arrive_warp(BAR(B_XT), lane);
     }
     for (int j = buf; ok && j < n_ent; j += 2) {
       long long* trc = ((warp & 3) == 0 && lane == 0) ? tr : nullptr;
@@ -375,7 +375,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       tmem_st_x16(t2, ds);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(BAR(B_C + buf));
+      mbar_arrive_warp(BAR(B_C + buf), lane);
       trace_ev(trc, 2 + ch, j, 3);
     }
     if (ok && n_ent > 0) ok = mbar_wait(BAR(B_ACC), 0, kBErrAcc, p.err);

@@ -102,6 +102,14 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 // memory complete in the background; kernel completion makes them visible).
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
 
+// One arrival per warp instead of 32: every lane's earlier writes (shared memory, or tensor memory behind a
+// tcgen05.wait + fence::before_thread_sync) are ordered before the warp barrier, and the arrival of lane 0
+// releases them. The barrier is initialised with the number of WARPS.
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
 // ---- union of two ascending index lists, by one warp ----
 // out = ascending union of a[0, na) and b[0, nb) (each strictly ascending); an element carries flag_a, flag_b or both.
 // Every lane of the warp calls this; ranks come from binary searches in the other list, so the cost is
