@@ -134,7 +134,8 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
 static int sparse_bwd_impl(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s,
                            const float* lse, const void* do_s, const int32_t* lut, const int32_t* col_offsets,
                            const int32_t* col_index, void* dq, void* dk, void* dv, unsigned char* ws,
-                           int accumulate_legacy, cudaStream_t st) {
+                           int accumulate_legacy, cudaStream_t st, const void* lin_dh = nullptr,
+                           const float* lin_dz = nullptr) {
   WsSparseBwd w = ws_sparse_bwd(s);
   BwdParams p;
   p.q = q; p.k = k; p.v = v; p.o_s = o_s; p.d_o = do_s; p.lse = lse;
@@ -142,6 +143,7 @@ static int sparse_bwd_impl(const sla_shape* s, const void* q, const void* k, con
   p.col_offsets = col_offsets; p.col_index = col_index; p.dq = dq; p.dk = dk; p.dv = dv;
   p.L = s->L; p.mb = ceil_div(s->L, s->BLKQ); p.nb = ceil_div(s->L, s->BLKK); p.topk = s->topk;
   p.scale = softmax_scale(s); p.scale_log2 = p.scale * kLog2e; p.accumulate = accumulate_legacy;
+  p.lin_dh = lin_dh; p.lin_dz = lin_dz;
   if (!(s->flags & SLA_FLAG_LEGACY_MMA)) {
     int rc = run_sparse_bwd_tc(s, p, ws + w.stats, st);
     if (rc != SLA_ERR_BAD_SHAPE) return rc;   // lists too long for the tcgen05 kernel's shared memory
@@ -193,13 +195,16 @@ int sla_bwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   lp.dz = reinterpret_cast<float*>(base + wb.dz);
   lp.dw_part = reinterpret_cast<float*>(base + wb.dw_part);
   lp.dw = dw; lp.dbias = dbias; lp.L = s->L; lp.nch = wb.nch; lp.rows = wb.rows;
-  // Linear branch first (plain stores), then the sparse kernels add their part: the tcgen05 kernels
-  // through TMA reduce-add stores, the mma.sync kernels by reading the tile back.
-  (void)legacy;
+  // Linear branch first (plain stores), then the sparse kernels add their part: the tcgen05 dQ kernel through TMA
+  // reduce-add stores, the mma.sync kernels by reading the tile back. With the tcgen05 kernels the linear
+  // branch's dk, dv are not a pass of their own: the dK/dV kernel computes them in its epilogue from dH and dz.
+  const bool fuse_kv = !legacy && sparse_bwd_tc_fits(s);
   lp.accumulate = 0;
+  lp.skip_kv = fuse_kv ? 1 : 0;
   rc = run_linear_bwd(s, lp, st);
   if (rc != SLA_OK) return rc;
-  return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 1, st);
+  return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 1, st,
+                         fuse_kv ? lp.dh : nullptr, fuse_kv ? lp.dz : nullptr);
 }
 
 }  // extern "C"

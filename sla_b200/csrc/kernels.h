@@ -31,6 +31,10 @@ struct BwdParams {
   int L, mb, nb, topk;
   float scale, scale_log2;
   int accumulate;         // dq/dk/dv already hold the linear branch's contribution
+  // tcgen05 path only: compute the linear branch's dk, dv in the epilogue of the dK/dV kernel (then dk, dv are
+  // plainly stored, whatever `accumulate` says). lin_dh: [BH][D*D] 16-bit dH, lin_dz: [BH][D] fp32.
+  const void* lin_dh = nullptr;
+  const float* lin_dz = nullptr;
 };
 
 struct LinBwdParams {
@@ -47,6 +51,7 @@ struct LinBwdParams {
   float *dw, *dbias;
   int L, nch, rows;
   int accumulate;         // add to what dq/dk/dv already hold instead of overwriting
+  int skip_kv = 0;        // stop after dq and the per-head reductions (dk, dv are produced elsewhere)
 };
 
 int convert_proj(const sla_shape* s, const float* w, const float* bias, void* out, cudaStream_t st);
@@ -60,6 +65,7 @@ int read_tc_error(int* out, bool clear);
 void set_trace_buffer(long long* p);
 long long* trace_buffer();
 int run_sparse_bwd_tc(const sla_shape* s, const BwdParams& p, void* stats, cudaStream_t st);
+bool sparse_bwd_tc_fits(const sla_shape* s);
 int run_sparse_bwd_dq_pair(const sla_shape* s, const BwdParams& p, const void* stats, int Lpad, cudaStream_t st);
 int run_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, float* partial,
                      int nch, int rows, cudaStream_t st);

@@ -339,7 +339,7 @@ static int launch_lin_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_
     dw_final_kernel<<<ceil_div(dd + D, 256), 256, 0, st>>>(p.dw_part, p.dw, p.dbias, bh, dd, D);
     SLA_LAUNCH_OK();
   }
-  {
+  if (!p.skip_kv) {
     auto kern = linear_bwd_kv_kernel<T, D, FEAT>;
     int smem = dd * 2 + 4 * 64 * D * 2 + D * 4;
     SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

@@ -42,6 +42,9 @@ struct TcBwdParams {
   int L, Lpad, mb, nb, topk, max_entries;
   int accumulate;            // add the result to what dq / dk / dv already hold (the linear branch's part)
   float scale, scale_log2;
+  // dK/dV variant only: the linear branch's dk, dv computed in the epilogue (feature < 0: not fused)
+  int lin_feature;           // sla_feature or -1
+  const float* dz;           // [BH][D] fp32 gradient of z = sum phi(k)
 };
 
 __device__ __forceinline__ float ex2b(float x) {
@@ -60,14 +63,14 @@ __device__ __forceinline__ void trace_ev(long long* tr, int role, int j, int ev)
 }
 
 enum : int { kBErrX = 201, kBErrYFull = 202, kBErrYEmpty = 203, kBErrTFull = 204, kBErrCFull = 205,
-             kBErrAcc = 206, kBErrDrain = 207 };
+             kBErrAcc = 206, kBErrDrain = 207, kBErrDh = 208, kBErrPhi = 209, kBErrLin = 210 };
 
 template <typename T, int D, int BM, bool KVS>
 __global__ void __launch_bounds__(576, 1)
 sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                      const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
                      const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
-                     TcBwdParams p) {
+                     const __grid_constant__ CUtensorMap tmDH, TcBwdParams p) {
   constexpr int SLABS = D / 64;
   constexpr int X_SLAB = 128 * 128, Y_SLAB = 64 * 128;
   constexpr int X_BYTES = SLABS * X_SLAB, Y_BYTES = SLABS * Y_SLAB;
@@ -84,7 +87,9 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   constexpr int COL_ACC1 = 0, COL_ACC2 = D, COL_X1 = D, COL_X2 = D + D / 2, COL_T = 2 * D;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * NS + 7];
+  __shared__ __align__(8) uint64_t bars[2 * NS + 10];
+  __shared__ float s_dz[KVS ? D : 1];              // fused linear backward: gradient of z
+  __shared__ float s_e[KVS ? 3 : 1][4][128];       // row-wide maxima / sums handed between the four compute groups
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_n_entries;
   __shared__ int s_abort;
@@ -106,6 +111,9 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   auto BAR = [&](int i) { return bar0 + 8u * i; };
   // 0 x_full | 1..NS y_full | NS+1..2NS y_empty | then t_full[2], c_full[2], acc_done
   constexpr int B_X = 0, B_YF = 1, B_YE = 1 + NS, B_T = 1 + 2 * NS, B_C = 3 + 2 * NS, B_ACC = 5 + 2 * NS, B_XT = 6 + 2 * NS;
+  // fused linear dk, dv (dK/dV variant): dH landed in stage 0 | phi(k) written over the K tile | the two GEMMs done
+  constexpr int B_DH = 7 + 2 * NS, B_PHIK = 8 + 2 * NS, B_LIN = 9 + 2 * NS;
+  const bool lin = KVS && p.lin_feature >= 0;
 
   if (warp == 16 && lane == 0) {
     // the producer lane sets the barriers up itself and requests the stationary tiles before it merges the lists
@@ -121,6 +129,9 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     }
     mbar_init(BAR(B_ACC), 1);
     mbar_init(BAR(B_XT), 16);
+    mbar_init(BAR(B_DH), 1);
+    mbar_init(BAR(B_PHIK), 16);
+    mbar_init(BAR(B_LIN), 1);
     fence_barrier_init();
     fence_proxy_async_smem();
     if (!s_abort) {
@@ -174,6 +185,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
+  if (KVS && p.lin_feature >= 0 && tid < D) s_dz[tid] = p.dz[static_cast<size_t>(bh) * D + tid];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -208,6 +220,19 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
           bulk_load_1d(sStat0 + s * STAT_BYTES, p.stats + static_cast<size_t>(bh) * p.Lpad + row0, STAT_BYTES,
                        BAR(B_YF + s));
         issued = j + 1;
+      }
+      if (lin && !*abortp) {
+        // dH of this head (D x D) into stage 0 once its last streamed tiles have been consumed
+        const int uses0 = (n_ent + NS - 1) / NS;
+        bool free0 = uses0 == 0 || mbar_wait(BAR(B_YE), (uses0 - 1) & 1, kBErrYEmpty, p.err);
+        if (!free0) *abortp = 1;
+        else {
+          mbar_expect_tx(BAR(B_DH), D * D * 2);
+          for (int r = 0; r < D / 64; ++r)
+            for (int c = 0; c < SLABS; ++c)
+              tma_load_3d(sY0 + c * (D * 128) + r * (64 * 128), &tmDH, BAR(B_DH), c * 64, r * 64, bh);
+          if (*abortp) mbar_wait(BAR(B_DH), 0, kBErrDrain, p.err);
+        }
       }
       if (*abortp) {
         mbar_wait(BAR(B_X), 0, kBErrDrain, p.err);
@@ -291,6 +316,33 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       if (ok) {
         if (elect_one()) tc_commit(BAR(B_ACC));
         __syncwarp();
+      }
+      if (ok && lin) {
+        // linear branch (core.py:91-94 backwards): dV += phi(K) dH and dphi_k = V dH^T, with phi(K) written over
+        // the K tile by the compute groups and dH ([i][j], one D x D tile) read once as MN-major and once as
+        // K-major B operand
+        ok = warp_all(mbar_wait(BAR(B_DH), 0, kBErrDh, p.err) && mbar_wait(BAR(B_PHIK), 0, kBErrPhi, p.err));
+        if (ok) {
+          tc_fence_after();
+          constexpr uint32_t IDESC_DPHI = idesc_f16(FMT, 128, D, 0, 0);
+          const uint32_t dh_mn = desc_lo(sY0, D * 128), dh_k = desc_lo(sY0, 16);
+          const uint32_t acc_v = n_ent > 0 ? 1u : 0u;
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t xo = ((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4;          // K-major A: phi(K), V
+              mma_ss(tmem + COL_ACC2, x1_lo + xo, dh_mn + ((kk * 2048) >> 4), IDESC_ACC, kk > 0 ? 1u : acc_v);
+            }
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t xo = ((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4;
+              const uint32_t ho = ((kk >> 2) * (D * 128) + (kk & 3) * 32) >> 4;        // K-major B: rows i, k = j
+              mma_ss(tmem + COL_T, x2_lo + xo, dh_k + ho, IDESC_DPHI, kk > 0 ? 1u : 0u);
+            }
+            tc_commit(BAR(B_LIN));
+          }
+          __syncwarp();
+        }
       }
       if (!ok) *abortp = 1;
     }
@@ -384,6 +436,131 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     asm volatile("bar.sync 1, 512;\n" ::: "memory");
     if (!*abortp) {
       tc_fence_after();
+      if (lin) {
+        // ---- fused backward of the linear branch for this key tile (core.py:91-94):
+        //   dphi_k = V dH^T + dz,  dk_lin = phi'(k) dphi_k,  dv_lin = phi(k) dH
+        // Each compute group owns D/4 columns of every row: it forms phi(k) for them (row-wide maxima and sums go
+        // through s_e), writes phi(k) over the K tile as the A operand of the dV GEMM, and afterwards turns its
+        // columns of dphi_k into dk_lin and adds the sparse branch's dK.
+        constexpr int CW = D / 4;                             // columns per group
+        const int c_lo = wg * CW;
+        auto chunk_addr = [&](uint32_t tile_base, int c8) {
+          return tile_base + (c8 >> 3) * X_SLAB + row * 128 + (((c8 & 7) ^ (row & 7)) << 4);
+        };
+        auto exchange = [&](int slot, float mine, bool take_max) {
+          s_e[slot][wg][row] = mine;
+          asm volatile("bar.sync 1, 512;\n" ::: "memory");
+          float r = s_e[slot][0][row];
+#pragma unroll
+          for (int g2 = 1; g2 < 4; ++g2) r = take_max ? fmaxf(r, s_e[slot][g2][row]) : r + s_e[slot][g2][row];
+          return r;
+        };
+        float x[CW];
+#pragma unroll
+        for (int c8 = 0; c8 < CW / 8; ++c8) {
+          uint32_t w0, w1, w2, w3;
+          ld_shared_v4(chunk_addr(sX1, c_lo / 8 + c8), w0, w1, w2, w3);
+          const uint32_t w[4] = {w0, w1, w2, w3};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = Elem<T>::unpack2(w[i]);
+            x[c8 * 8 + 2 * i] = f.x; x[c8 * 8 + 2 * i + 1] = f.y;
+          }
+        }
+        if (p.lin_feature == SLA_PHI_SOFTMAX) {
+          float mx = x[0];
+#pragma unroll
+          for (int c = 1; c < CW; ++c) mx = fmaxf(mx, x[c]);
+          mx = exchange(0, mx, true);
+          float sm = 0.f;
+#pragma unroll
+          for (int c = 0; c < CW; ++c) { x[c] = __expf(x[c] - mx); sm += x[c]; }
+          const float inv_s = 1.f / exchange(1, sm, false);
+#pragma unroll
+          for (int c = 0; c < CW; ++c) x[c] *= inv_s;
+        } else {
+#pragma unroll
+          for (int c = 0; c < CW; ++c) {
+            if (p.lin_feature == SLA_PHI_RELU) x[c] = fmaxf(x[c], 0.f);
+            else x[c] = x[c] > 0.f ? x[c] + 1.f : __expf(x[c]);      // elu(x) + 1
+          }
+        }
+        const bool key_live = grow < L;                        // rows past the end: K was zero-filled, phi must be 0
+        uint32_t phi[CW / 2];                                  // phi(k) rounded to T (core.py:91)
+#pragma unroll
+        for (int c = 0; c < CW; c += 2) phi[c >> 1] = key_live ? Elem<T>::pack2(x[c], x[c + 1]) : 0u;
+#pragma unroll
+        for (int c8 = 0; c8 < CW / 8; ++c8)
+          st_shared_v4(chunk_addr(sX1, c_lo / 8 + c8), phi[4 * c8], phi[4 * c8 + 1], phi[4 * c8 + 2], phi[4 * c8 + 3]);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive_warp(BAR(B_PHIK), lane);
+        const bool lin_ok = mbar_wait(BAR(B_LIN), 0, kBErrLin, p.err);
+        if (!lin_ok) *abortp = 1;
+        float dk_out[CW];
+        float ps = 0.f;                                        // sum_i phi_i dphi_i of this group's columns
+        if (lin_ok) {
+          tc_fence_after();
+          uint32_t tv[CW];
+          if constexpr (CW == 32) tmem_ld_x32(tmem + lane_addr + COL_T + c_lo, tv); else tmem_ld_x16(tmem + lane_addr + COL_T + c_lo, tv);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < CW; c += 2) {
+            const float2 ph = Elem<T>::unpack2(phi[c >> 1]);
+            x[c] = ph.x; x[c + 1] = ph.y;
+            dk_out[c] = __uint_as_float(tv[c]) + s_dz[c_lo + c];
+            dk_out[c + 1] = __uint_as_float(tv[c + 1]) + s_dz[c_lo + c + 1];
+            ps += ph.x * dk_out[c] + ph.y * dk_out[c + 1];
+          }
+        }
+        // every compute thread takes part in the exchange, whatever its wait returned (a named barrier is not bounded)
+        if (p.lin_feature == SLA_PHI_SOFTMAX) ps = exchange(2, ps, false);
+        if (lin_ok) {
+          if (p.lin_feature == SLA_PHI_SOFTMAX) {
+#pragma unroll
+            for (int c = 0; c < CW; ++c) dk_out[c] = x[c] * (dk_out[c] - ps);
+          } else if (p.lin_feature == SLA_PHI_RELU) {
+#pragma unroll
+            for (int c = 0; c < CW; ++c) dk_out[c] = x[c] > 0.f ? dk_out[c] : 0.f;
+          } else {
+#pragma unroll
+            for (int c = 0; c < CW; ++c) dk_out[c] = x[c] > 1.f ? dk_out[c] : x[c] * dk_out[c];   // x > 0 iff phi > 1
+          }
+          // + the sparse branch's dK (times the softmax scale, kernel.py:236); dV already holds both parts
+          uint32_t ak[CW], av[CW];
+          if (n_ent > 0) {
+            if constexpr (CW == 32) tmem_ld_x32(tmem + lane_addr + COL_ACC1 + c_lo, ak); else tmem_ld_x16(tmem + lane_addr + COL_ACC1 + c_lo, ak);
+          } else {
+#pragma unroll
+            for (int c = 0; c < CW; ++c) ak[c] = 0u;
+          }
+          if constexpr (CW == 32) tmem_ld_x32(tmem + lane_addr + COL_ACC2 + c_lo, av); else tmem_ld_x16(tmem + lane_addr + COL_ACC2 + c_lo, av);
+          tmem_wait_ld();
+#pragma unroll
+          for (int c8 = 0; c8 < CW / 8; ++c8) {
+            uint32_t wk[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int c = c8 * 8 + 2 * i;
+              wk[i] = Elem<T>::pack2(fmaf(__uint_as_float(ak[c]), p.scale, dk_out[c]),
+                                     fmaf(__uint_as_float(ak[c + 1]), p.scale, dk_out[c + 1]));
+              wv[i] = Elem<T>::pack2(__uint_as_float(av[c]), __uint_as_float(av[c + 1]));
+            }
+            st_shared_v4(chunk_addr(sX1, c_lo / 8 + c8), wk[0], wk[1], wk[2], wk[3]);
+            st_shared_v4(chunk_addr(sX2, c_lo / 8 + c8), wv[0], wv[1], wv[2], wv[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 512;\n" ::: "memory");
+        if (tid == 0 && !*abortp) {
+          for (int c = 0; c < SLABS; ++c) {
+            tma_store_3d(&tmO1, sX1 + c * X_SLAB, c * 64, tile * 128, bh);
+            tma_store_3d(&tmO2, sX2 + c * X_SLAB, c * 64, tile * 128, bh);
+          }
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+      } else {
       // accumulators -> T, staged over the (idle) stationary tiles in the swizzled slab layout, then
       // TMA stores; rows past the end of the sequence are clipped by the copy engine.
       // dQ: group g converts columns [g D/4, +D/4) of acc1. KVS: groups 0,1 halves of acc1 (dK), 2,3 of acc2 (dV).
@@ -430,6 +607,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         tma_store_commit();
         tma_store_wait_read();
       }
+      }   // !lin
     }
   }
   // ------------------------------ teardown ------------------------------
@@ -500,11 +678,12 @@ static int bwd_tc_smem_bytes(int D, int max_entries) {
   const int NS = D == 128 ? 4 : 6;
   return 1024 + 2 * 128 * D * 2 + NS * 2 * 64 * D * 2 + NS * 512 + 2 * max_entries * 4 + 16;
 }
+constexpr int kBwdStaticSmem = 8 * 1024;   // statically allocated shared memory of the kernels (barriers, exchange slots)
 
 template <typename T, int D, int BM, bool KVS>
 static int launch_bwd_tc(const sla_shape* s, const BwdParams& bp, const float2* stats, int Lpad, cudaStream_t st) {
   const int bh = s->B * s->H;
-  CUtensorMap x1, x2, y1, y2, o1, o2;
+  CUtensorMap x1, x2, y1, y2, o1, o2, dh;
   int rc;
   const void *X1 = KVS ? bp.k : bp.q, *X2 = KVS ? bp.v : bp.d_o, *Y1 = KVS ? bp.q : bp.k, *Y2 = KVS ? bp.d_o : bp.v;
   void *O1 = KVS ? bp.dk : bp.dq, *O2 = KVS ? bp.dv : bp.dq;
@@ -514,6 +693,9 @@ static int launch_bwd_tc(const sla_shape* s, const BwdParams& bp, const float2* 
   if ((rc = make_tmap_3d(&y2, Y2, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
   if ((rc = make_tmap_3d(&o1, O1, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
   if ((rc = make_tmap_3d(&o2, O2, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  const bool lin = KVS && bp.lin_dh != nullptr;
+  dh = o1;
+  if (lin && (rc = make_tmap_rows(&dh, bp.lin_dh, s->dtype, D, D, bh, size_t(D) * D * 2, 64)) != SLA_OK) return rc;
   tc::TcBwdParams p;
   p.list = KVS ? bp.col_index : bp.lut;
   p.offsets = bp.col_offsets;
@@ -523,14 +705,16 @@ static int launch_bwd_tc(const sla_shape* s, const BwdParams& bp, const float2* 
   p.trace = g_trace_buffer ? g_trace_buffer + (KVS ? 1024 : 0) : nullptr;
   p.L = s->L; p.Lpad = Lpad; p.mb = bp.mb; p.nb = bp.nb; p.topk = bp.topk;
   p.scale = bp.scale; p.scale_log2 = bp.scale_log2; p.accumulate = bp.accumulate;
+  p.lin_feature = lin ? s->feature_map : -1;
+  p.dz = bp.lin_dz;
   const int max_entries = KVS ? 2 * bp.mb : 2 * bp.topk;
   p.max_entries = max_entries;
   const int smem = bwd_tc_smem_bytes(D, max_entries);
-  if (smem > 227 * 1024) return SLA_ERR_BAD_SHAPE;
+  if (smem + kBwdStaticSmem > 227 * 1024) return SLA_ERR_BAD_SHAPE;
   auto kern = tc::sparse_bwd_tc_kernel<T, D, BM, KVS>;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int tiles = KVS ? ceil_div(bp.nb, 2) : ceil_div(s->L, 128);
-  kern<<<dim3(tiles, bh), 576, smem, st>>>(x1, x2, y1, y2, o1, o2, p);
+  kern<<<dim3(tiles, bh), 576, smem, st>>>(x1, x2, y1, y2, o1, o2, dh, p);
   SLA_LAUNCH_OK();
   return SLA_OK;
 }
@@ -539,8 +723,7 @@ template <typename T, int D, int BM>
 static int run_bwd_tc_typed(const sla_shape* s, const BwdParams& bp, float2* stats, int Lpad, cudaStream_t st) {
   const int bh = s->B * s->H;
   // nothing is launched unless both kernels fit: the caller falls back to another path on BAD_SHAPE
-  if (bwd_tc_smem_bytes(D, 2 * bp.mb) > 227 * 1024 || bwd_tc_smem_bytes(D, 2 * bp.topk) > 227 * 1024)
-    return SLA_ERR_BAD_SHAPE;
+  if (!sparse_bwd_tc_fits(s)) return SLA_ERR_BAD_SHAPE;
   bwd_prep_kernel<T, D><<<dim3(ceil_div(Lpad, 64), bh), 256, 0, st>>>(
       static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L, Lpad);
   SLA_LAUNCH_OK();
@@ -550,6 +733,14 @@ static int run_bwd_tc_typed(const sla_shape* s, const BwdParams& bp, float2* sta
   if (rc == SLA_ERR_BAD_SHAPE) rc = launch_bwd_tc<T, D, BM, false>(s, bp, stats, Lpad, st);
   if (rc != SLA_OK) return rc;
   return launch_bwd_tc<T, D, BM, true>(s, bp, stats, Lpad, st);
+}
+
+// Whether the tcgen05 backward kernels fit this shape (so that a caller can decide what to fuse into them before
+// it launches anything).
+bool sparse_bwd_tc_fits(const sla_shape* s) {
+  const int mb = ceil_div(s->L, s->BLKQ);
+  return bwd_tc_smem_bytes(s->D, 2 * mb) + kBwdStaticSmem <= 227 * 1024 &&
+         bwd_tc_smem_bytes(s->D, 2 * s->topk) + kBwdStaticSmem <= 227 * 1024;
 }
 
 // `stats` must hold B*H*Lpad float2 with Lpad = ceil(L/128)*128.
