@@ -164,7 +164,8 @@ SLA_API int sla_bwd(const sla_shape* shape, const void* q, const void* k, const 
 
 /* Replaces SageSLA/core.py:100-158 (SageSparseLinearAttention.forward after get_block_map and the
  * casts): INT8 Q.K^T with per-block scales and K-mean smoothing, FP8 e4m3 P.V, then the same
- * linear branch and proj_l. BLKQ must be 128 and BLKK 64 (SageSLA/README.md:16-17). */
+ * linear branch and proj_l. BLKQ must be 128 and BLKK 64 (SageSLA/README.md:16-17), D 64 or 128
+ * (SageSLA/core.py:112). */
 SLA_API int sage_sla_fwd(const sla_shape* shape, const void* q, const void* k, const void* v,
                  const int32_t* lut, const float* w, const float* bias, void* o, void* lin_state,
                  void* ws, size_t ws_bytes, sla_stream_t stream);

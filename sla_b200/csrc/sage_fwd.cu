@@ -59,23 +59,24 @@ enum : int { kSErrQ = 301, kSErrK = 302, kSErrV = 303, kSErrEmpty = 304, kSErrS 
 constexpr float kPShift = 5.0f;
 constexpr float kLazy = 3.0f;
 
-// D = 128 only: rows of the 8-bit tensors are exactly one 128-byte swizzle atom.
-template <typename T>
+// Rows of the 8-bit tensors are one 128-byte swizzle atom whatever D is: with D = 64 the upper half of a row is
+// padding that no GEMM reads (the S GEMM takes D / 32 K-steps inside the atom, the P.V GEMM has N = D).
+template <typename T, int D>
 __global__ void __launch_bounds__(192, 2)
 sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                    const __grid_constant__ CUtensorMap tmQ16, const __grid_constant__ CUtensorMap tmHW, SageParams p) {
-  constexpr int D = 128;
-  constexpr int Q_BYTES = 128 * 128, KV_BYTES = 64 * 128;      // 8-bit tiles
-  constexpr int O_SLAB = 128 * 128;                            // 16-bit output staging, 2 slabs
+  constexpr int DP = 128;                                      // bytes per row of the 8-bit tensors
+  constexpr int Q_BYTES = 128 * DP, KV_BYTES = 64 * DP;        // 8-bit tiles
+  constexpr int O_SLAB = 128 * 128, NSLAB = D / 64;            // 16-bit output staging, slabs of 64 columns
   constexpr int NS = 4;                                        // ring stages (K and V each)
   constexpr uint32_t IDESC_S = idesc_i8(128, 64);
-  constexpr uint32_t IDESC_PV = idesc_e4m3(128, D, 1);
+  constexpr uint32_t IDESC_PV = idesc_e4m3(128, D, 1);     // N = D: the first D bytes of each V8 row
   constexpr int FMT16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   constexpr uint32_t IDESC_LIN = idesc_f16(FMT16, 128, D, 0, 1);   // phi(Q) (K-major) x H W^T (MN-major), 16-bit
-  constexpr int Q16_SLAB = 128 * 128, HW_STAGE = 64 * 256, HW_SLAB = 64 * 128;
+  constexpr int Q16_SLAB = 128 * 128, HW_STAGE = 64 * D * 2, HW_SLAB = 64 * 128;
   constexpr uint32_t TMEM_COLS = 256;
-  constexpr int COL_O = 0, COL_S = D;
+  constexpr int COL_O = 0, COL_S = DP;
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[4 * NS + 11];
@@ -183,14 +184,14 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int j = max(0, n_ent - NS); ring_free && j < n_ent; ++j)
           ring_free = mbar_wait(BAR(B_KE + j % NS), (j / NS) & 1, kSErrEmpty, p.err);
         if (ring_free) {
-          mbar_expect_tx(BAR(B_Q16), 2 * Q16_SLAB);
-          for (int c = 0; c < 2; ++c) tma_load_3d(sQ16 + c * Q16_SLAB, &tmQ16, BAR(B_Q16), c * 64, tile * 128, bh);
+          mbar_expect_tx(BAR(B_Q16), NSLAB * Q16_SLAB);
+          for (int c = 0; c < NSLAB; ++c) tma_load_3d(sQ16 + c * Q16_SLAB, &tmQ16, BAR(B_Q16), c * 64, tile * 128, bh);
           for (int j = max(0, n_ent - NS); ring_free && j < n_ent; ++j)
             ring_free = mbar_wait(BAR(B_VE + j % NS), (j / NS) & 1, kSErrEmpty, p.err);
           if (ring_free) {
             mbar_expect_tx(BAR(B_HW), D * D * 2);
-            for (int r = 0; r < 2; ++r)
-              for (int c = 0; c < 2; ++c)
+            for (int r = 0; r < NSLAB; ++r)
+              for (int c = 0; c < NSLAB; ++c)
                 tma_load_3d(sHW + r * HW_STAGE + c * HW_SLAB, &tmHW, BAR(B_HW), c * 64, r * 64, bh);
             if (*abortp) mbar_wait(BAR(B_HW), 0, kSErrDrain, p.err);
           }
@@ -214,7 +215,7 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t d = tmem + COL_S + (j & 1) * 64;
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)   // K = 32 int8 = 32 bytes per step inside the 128-byte row
+          for (int kk = 0; kk < D / 32; ++kk)   // K = 32 int8 = 32 bytes per step inside the 128-byte row
             mma_ss_i8(d, q_lo + ((kk * 32) >> 4), k_lo + ((kk * 32) >> 4), IDESC_S, kk > 0 ? 1u : 0u);
           tc_commit(BAR(B_S + (j & 1)));
           tc_commit(BAR(B_KE + j % NS));
@@ -470,7 +471,7 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       fence_proxy_async_smem();
       asm volatile("bar.sync 1, 128;\n" ::: "memory");
       if (tid == 0 && !*abortp) {
-        for (int c = 0; c < 2; ++c) tma_store_3d(&tmO, sO + c * O_SLAB, c * 64, tile * 128, bh);
+        for (int c = 0; c < NSLAB; ++c) tma_store_3d(&tmO, sO + c * O_SLAB, c * 64, tile * 128, bh);
         tma_store_commit();
         tma_store_wait_read();
       }
@@ -492,37 +493,38 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // ---------------------------------------------------------------------------------------------
 // One CTA per block of `blk` rows: symmetric abs-max INT8, scale = amax / 127 (zero blocks get scale 1e-8/127).
 // z = 0: Q in blocks of 128 rows; z = 1: K - mean in blocks of 64 rows.
-template <typename T>
+// The 8-bit rows are written 128 bytes apart whatever D is (the pad of a D = 64 row is never read).
+template <typename T, int D>
 __global__ void __launch_bounds__(256, 3) sage_quant_qk_kernel(const T* __restrict__ q, const T* __restrict__ k,
                                                                const float* __restrict__ kmean, int8_t* __restrict__ q8,
                                                                int8_t* __restrict__ k8, float* __restrict__ qscale,
                                                                float* __restrict__ kscale, int L, int mb, int nb) {
-  constexpr int D = 128;
+  constexpr int TPR = D / 8, RPP = 256 / TPR;   // threads per row (8 elements each), rows per pass
   __shared__ float red[8];
   const bool is_k = blockIdx.z == 1;
   const int blk = is_k ? 64 : 128, nblk = is_k ? nb : mb;
   if (static_cast<int>(blockIdx.x) >= nblk) return;
   const int bh = blockIdx.y, ib = blockIdx.x, tid = threadIdx.x;
   const T* src = (is_k ? k : q) + static_cast<size_t>(bh) * L * D;
-  int8_t* dst = (is_k ? k8 : q8) + static_cast<size_t>(bh) * L * D;
-  const int c = (tid & 15) * 8;                 // 16 threads per row, 8 elements each
+  int8_t* dst = (is_k ? k8 : q8) + static_cast<size_t>(bh) * L * 128;
+  const int c = (tid % TPR) * 8;
   float mean[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) mean[e] = is_k ? kmean[static_cast<size_t>(bh) * D + c + e] : 0.f;
   // The rows stay packed in registers (4 words per row) between the abs-max pass and the rounding pass, which
   // keeps three CTAs per SM resident; all loads of a thread are issued up front.
   uint4 raw[8];                                 // up to 8 rows per thread (128 rows / 16 row groups)
-  const int rows_per_thread = blk / 16;
+  const int rows_per_thread = blk / RPP;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int r = ib * blk + (tid >> 4) + 16 * i;
+    const int r = ib * blk + tid / TPR + RPP * i;
     raw[i] = (i < rows_per_thread && r < L) ? *reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * D + c)
                                             : make_uint4(0u, 0u, 0u, 0u);
   }
   float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int r = ib * blk + (tid >> 4) + 16 * i;
+    const int r = ib * blk + tid / TPR + RPP * i;
     if (i < rows_per_thread && r < L) {
       const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw[i]);
 #pragma unroll
@@ -542,7 +544,7 @@ __global__ void __launch_bounds__(256, 3) sage_quant_qk_kernel(const T* __restri
   if (tid == 0) (is_k ? kscale : qscale)[static_cast<size_t>(bh) * nblk + ib] = scale;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int r = ib * blk + (tid >> 4) + 16 * i;
+    const int r = ib * blk + tid / TPR + RPP * i;
     if (i < rows_per_thread && r < L) {
       const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw[i]);
       uint32_t w[2];
@@ -553,25 +555,25 @@ __global__ void __launch_bounds__(256, 3) sage_quant_qk_kernel(const T* __restri
         int b2 = __float2int_rn((f1.x - mean[4 * h + 2]) * inv), b3 = __float2int_rn((f1.y - mean[4 * h + 3]) * inv);
         w[h] = (b0 & 0xff) | ((b1 & 0xff) << 8) | ((b2 & 0xff) << 16) | (static_cast<uint32_t>(b3 & 0xff) << 24);
       }
-      *reinterpret_cast<uint2*>(dst + static_cast<size_t>(r) * D + c) = make_uint2(w[0], w[1]);
+      *reinterpret_cast<uint2*>(dst + static_cast<size_t>(r) * 128 + c) = make_uint2(w[0], w[1]);
     }
   }
 }
 
 // per-channel abs-max of V over chunks of 512 rows: partial[bh][chunk][D]
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(256) sage_v_amax_kernel(const T* __restrict__ v, float* __restrict__ partial,
                                                           int L, int nch) {
-  constexpr int D = 128;
-  __shared__ float red[16][D];
+  constexpr int TPR = D / 8, RPP = 256 / TPR;
+  __shared__ float red[RPP][D];
   const int bh = blockIdx.y, ch = blockIdx.x, tid = threadIdx.x;
-  const int rg = tid >> 4, c = (tid & 15) * 8;
+  const int rg = tid / TPR, c = (tid % TPR) * 8;
   const T* base = v + static_cast<size_t>(bh) * L * D;
   float am[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) am[e] = 0.f;
   const int row1 = min(L, (ch + 1) * 512);
-  for (int r = ch * 512 + rg; r < row1; r += 16) {
+  for (int r = ch * 512 + rg; r < row1; r += RPP) {
     uint4 raw = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(r) * D + c);
     const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
@@ -587,28 +589,28 @@ __global__ void __launch_bounds__(256) sage_v_amax_kernel(const T* __restrict__ 
   if (tid < D) {
     float m = 0.f;
 #pragma unroll
-    for (int g = 0; g < 16; ++g) m = fmaxf(m, red[g][tid]);
+    for (int g = 0; g < RPP; ++g) m = fmaxf(m, red[g][tid]);
     partial[(static_cast<size_t>(bh) * nch + ch) * D + tid] = m;
   }
 }
 __global__ void sage_v_scale_kernel(const float* __restrict__ partial, float* __restrict__ vscale, int nch) {
-  const int bh = blockIdx.x, d = threadIdx.x;
+  const int bh = blockIdx.x, d = threadIdx.x, D = blockDim.x;
   float m = 0.f;
-  for (int c = 0; c < nch; ++c) m = fmaxf(m, partial[(static_cast<size_t>(bh) * nch + c) * 128 + d]);
-  vscale[static_cast<size_t>(bh) * 128 + d] = fmaxf(m, 1e-8f) / 448.f;
+  for (int c = 0; c < nch; ++c) m = fmaxf(m, partial[(static_cast<size_t>(bh) * nch + c) * D + d]);
+  vscale[static_cast<size_t>(bh) * D + d] = fmaxf(m, 1e-8f) / 448.f;
 }
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(256) sage_quant_v_kernel(const T* __restrict__ v, const float* __restrict__ vscale,
                                                            uint8_t* __restrict__ v8, int L) {
-  constexpr int D = 128;
+  constexpr int TPR = D / 8, RPP = 256 / TPR;
   const int bh = blockIdx.y, tid = threadIdx.x;
-  const int c = (tid & 15) * 8;
+  const int c = (tid % TPR) * 8;
   float inv[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) inv[e] = 1.f / vscale[static_cast<size_t>(bh) * D + c + e];
   const T* base = v + static_cast<size_t>(bh) * L * D;
-  uint8_t* out = v8 + static_cast<size_t>(bh) * L * D;
-  for (int r = blockIdx.x * 64 + (tid >> 4); r < min(L, (static_cast<int>(blockIdx.x) + 1) * 64); r += 16) {
+  uint8_t* out = v8 + static_cast<size_t>(bh) * L * 128;
+  for (int r = blockIdx.x * 64 + tid / TPR; r < min(L, (static_cast<int>(blockIdx.x) + 1) * 64); r += RPP) {
     uint4 raw = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(r) * D + c);
     const uint32_t* u = reinterpret_cast<const uint32_t*>(&raw);
     float f[8];
@@ -619,15 +621,15 @@ __global__ void __launch_bounds__(256) sage_quant_v_kernel(const T* __restrict__
       f[2 * e + 1] = t.y * inv[2 * e + 1];
     }
     uint2 w = make_uint2(tc::pack_e4m3x4(f[0], f[1], f[2], f[3]), tc::pack_e4m3x4(f[4], f[5], f[6], f[7]));
-    *reinterpret_cast<uint2*>(out + static_cast<size_t>(r) * D + c) = w;
+    *reinterpret_cast<uint2*>(out + static_cast<size_t>(r) * 128 + c) = w;
   }
 }
 
-template <typename T>
+template <typename T, int D>
 static int run_sage_typed(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
                           void* o_s, float* lse, unsigned char* ws, const void* lin_state, const void* wbits,
                           cudaStream_t st) {
-  const int bh = s->B * s->H, L = s->L, D = 128;
+  const int bh = s->B * s->H, L = s->L;
   const int mb = ceil_div(L, 128), nb = ceil_div(L, 64);
   WsSage w = ws_sage(s);
   float* kmean = reinterpret_cast<float*>(ws + w.kmean);
@@ -640,14 +642,14 @@ static int run_sage_typed(const sla_shape* s, const void* q, const void* k, cons
   float* vs = reinterpret_cast<float*>(ws + w.vscale);
   int rc = run_k_mean(s, k, part, kmean, st);
   if (rc != SLA_OK) return rc;
-  sage_quant_qk_kernel<T><<<dim3(nb, bh, 2), 256, 0, st>>>(static_cast<const T*>(q), static_cast<const T*>(k), kmean,
+  sage_quant_qk_kernel<T, D><<<dim3(nb, bh, 2), 256, 0, st>>>(static_cast<const T*>(q), static_cast<const T*>(k), kmean,
                                                           q8, k8, qs, ks, L, mb, nb);
   SLA_LAUNCH_OK();
-  sage_v_amax_kernel<T><<<dim3(w.nch, bh), 256, 0, st>>>(static_cast<const T*>(v), part, L, w.nch);
+  sage_v_amax_kernel<T, D><<<dim3(w.nch, bh), 256, 0, st>>>(static_cast<const T*>(v), part, L, w.nch);
   SLA_LAUNCH_OK();
   sage_v_scale_kernel<<<bh, D, 0, st>>>(part, vs, w.nch);
   SLA_LAUNCH_OK();
-  sage_quant_v_kernel<T><<<dim3(nb, bh), 256, 0, st>>>(static_cast<const T*>(v), vs, v8, L);
+  sage_quant_v_kernel<T, D><<<dim3(nb, bh), 256, 0, st>>>(static_cast<const T*>(v), vs, v8, L);
   SLA_LAUNCH_OK();
 
   CUtensorMap tq, tk, tv, to, tq16, thw;
@@ -670,7 +672,7 @@ static int run_sage_typed(const sla_shape* s, const void* q, const void* k, cons
   if (p.err == nullptr) return SLA_ERR_CUDA;
   p.L = L; p.mb = mb; p.nb = nb; p.topk = s->topk;
   p.scale_log2 = softmax_scale(s) * kLog2e;
-  auto kern = tc::sage_fwd_tc_kernel<T>;
+  auto kern = tc::sage_fwd_tc_kernel<T, D>;
   const int smem = 1024 + 2 * 128 * 128 + 2 * 4 * 64 * 128 + s->topk * 8 + 16;
   if (smem > 113 * 1024) return SLA_ERR_BAD_TOPK;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -689,7 +691,7 @@ extern "C" int sage_sla_fwd(const sla_shape* s, const void* q, const void* k, co
   int rc = validate_shape(s);
   if (rc != SLA_OK) return rc;
   if (s->BLKQ != 128 || s->BLKK != 64) return SLA_ERR_BAD_SHAPE;   // SageSLA/README.md:16-17
-  if (s->D != 128) return SLA_ERR_UNSUPPORTED;                     // 8-bit rows must fill a 128-byte swizzle atom
+  if (s->D != 64 && s->D != 128) return SLA_ERR_UNSUPPORTED;       // SageSLA/core.py:112
   if ((rc = check_device_arch()) != SLA_OK) return rc;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(ws)) return SLA_ERR_BAD_ALIGN;
   WsSage wsz = ws_sage(s);
@@ -710,6 +712,9 @@ extern "C" int sage_sla_fwd(const sla_shape* s, const void* q, const void* k, co
     if ((rc = run_state_proj(s, lin_state, wbits, st)) != SLA_OK) return rc;
     state = lin_state;
   }
-  return s->dtype == SLA_BF16 ? run_sage_typed<__nv_bfloat16>(s, q, k, v, lut, o, lse, base, state, wbits, st)
-                              : run_sage_typed<__half>(s, q, k, v, lut, o, lse, base, state, wbits, st);
+  if (s->D == 64)
+    return s->dtype == SLA_BF16 ? run_sage_typed<__nv_bfloat16, 64>(s, q, k, v, lut, o, lse, base, state, wbits, st)
+                                : run_sage_typed<__half, 64>(s, q, k, v, lut, o, lse, base, state, wbits, st);
+  return s->dtype == SLA_BF16 ? run_sage_typed<__nv_bfloat16, 128>(s, q, k, v, lut, o, lse, base, state, wbits, st)
+                              : run_sage_typed<__half, 128>(s, q, k, v, lut, o, lse, base, state, wbits, st);
 }

@@ -134,9 +134,9 @@ struct WsSage {
   size_t wbits;    // 16-bit W + bias
   size_t kmean;    // fp32 [BH][D]
   size_t colsum;   // fp32 [BH][NCH][D] partial column sums of K, then [BH][NCH][D] column abs-max of V
-  size_t q8;       // int8 [BH][L][D]
-  size_t k8;       // int8 [BH][L][D]
-  size_t v8;       // e4m3 [BH][L][D]
+  size_t q8;       // int8 [BH][L][128] (rows padded to one 128-byte swizzle atom when D = 64)
+  size_t k8;       // int8 [BH][L][128]
+  size_t v8;       // e4m3 [BH][L][128]
   size_t qscale;   // fp32 [BH][M_BLOCKS]
   size_t kscale;   // fp32 [BH][N_BLOCKS]
   size_t vscale;   // fp32 [BH][D]
@@ -154,9 +154,9 @@ inline WsSage ws_sage(const sla_shape* s) {
   w.wbits = o;  o += ws_fwd_extra(s);
   w.kmean = o;  o += ws_round(bh * s->D * 4);
   w.colsum = o; o += ws_round(bh * w.nch * s->D * 4 * 2);
-  w.q8 = o;     o += ws_round(bh * size_t(s->L) * s->D);
-  w.k8 = o;     o += ws_round(bh * size_t(s->L) * s->D);
-  w.v8 = o;     o += ws_round(bh * size_t(s->L) * s->D);
+  w.q8 = o;     o += ws_round(bh * size_t(s->L) * 128);
+  w.k8 = o;     o += ws_round(bh * size_t(s->L) * 128);
+  w.v8 = o;     o += ws_round(bh * size_t(s->L) * 128);
   w.qscale = o; o += ws_round(bh * mb * 4);
   w.kscale = o; o += ws_round(bh * nb * 4);
   w.vscale = o; o += ws_round(bh * s->D * 4);

@@ -18,12 +18,12 @@ def _inputs(B, H, L, D, seed, k_offset=0.0):
     return q.bfloat16(), k.bfloat16(), v.bfloat16()
 
 
-@pytest.mark.parametrize("B,H,L,ratio,koff", [(1, 2, 1000, 0.3, 0.0), (2, 1, 2500, 0.1, 2.0), (1, 1, 128, 1.0, 0.5),
-                                              (1, 1, 1104, 0.25, 1.0)])
-def test_sage_sparse_branch(B, H, L, ratio, koff):
+@pytest.mark.parametrize("B,H,L,ratio,koff,D", [(1, 2, 1000, 0.3, 0.0, 128), (2, 1, 2500, 0.1, 2.0, 128),
+                                                (1, 1, 128, 1.0, 0.5, 128), (1, 1, 1104, 0.25, 1.0, 128),
+                                                (1, 2, 1000, 0.3, 0.5, 64), (2, 1, 1931, 0.15, 1.0, 64)])
+def test_sage_sparse_branch(B, H, L, ratio, koff, D):
     from oracle import sla_oracle as O
     from sla_b200 import ops
-    D = 128
     q, k, v = _inputs(B, H, L, D, L, koff)
     w = torch.zeros(D, D, device="cuda")
     bm = ops.block_map(q.cuda(), k.cuda(), ratio, 128, 64)
@@ -42,15 +42,16 @@ def test_sage_sparse_branch(B, H, L, ratio, koff):
     assert rel_l1(got, ref_f) <= 1.1 * rel_l1(ref_q, ref_f) + 2e-3, (rel_l1(got, ref_f), rel_l1(ref_q, ref_f))
 
 
-def test_sage_module_matches_oracle_and_16bit_module():
+@pytest.mark.parametrize("D,feature", [(128, "softmax"), (64, "softmax"), (64, "elu")])
+def test_sage_module_matches_oracle_and_16bit_module(D, feature):
     import sla_b200
     from oracle import sla_oracle as O
-    B, H, L, D = 1, 2, 1500, 128
+    B, H, L = 1, 2, 1500
     q, k, v = _inputs(B, H, L, D, 7, 1.0)
     g = torch.Generator().manual_seed(3)
     w, b = torch.randn(D, D, generator=g) * 0.05, torch.randn(D, generator=g) * 0.05
-    sage = sla_b200.SageSparseLinearAttention(D, 0.2, "softmax").cuda()
-    full = sla_b200.SparseLinearAttention(D, 0.2, "softmax", BLKQ=128, BLKK=64).cuda()
+    sage = sla_b200.SageSparseLinearAttention(D, 0.2, feature).cuda()
+    full = sla_b200.SparseLinearAttention(D, 0.2, feature, BLKQ=128, BLKK=64).cuda()
     for m in (sage, full):
         with torch.no_grad():
             m.proj_l.weight.copy_(w)
@@ -59,7 +60,7 @@ def test_sage_module_matches_oracle_and_16bit_module():
         o_sage, sp = sage(q.cuda(), k.cuda(), v.cuda(), return_sparsity=True)
         o_full = full(q.cuda(), k.cuda(), v.cuda())
     assert o_sage.dtype == torch.bfloat16 and sp == 4 / 24
-    ref = O.sla_forward(q, k, v, w, b, 0.2, "softmax", 128, 64, torch.bfloat16)
+    ref = O.sla_forward(q, k, v, w, b, 0.2, feature, 128, 64, torch.bfloat16)
     assert cos_sim(o_sage.float().cpu(), ref.float()) >= 0.995
     assert cos_sim(o_sage.float().cpu(), o_full.float().cpu()) >= 0.995
 
@@ -68,7 +69,7 @@ def test_sage_rejects_other_block_sizes_and_head_dims():
     import sla_b200
     with pytest.raises(ValueError):
         sla_b200.SageSparseLinearAttention(128, 0.2, BLKQ=64, BLKK=64)
-    m = sla_b200.SageSparseLinearAttention(64, 0.5).cuda()
-    x = torch.randn(1, 1, 256, 64, device="cuda").bfloat16()
-    with pytest.raises(NotImplementedError):
+    m = sla_b200.SageSparseLinearAttention(32, 0.5).cuda()
+    x = torch.randn(1, 1, 256, 32, device="cuda").bfloat16()
+    with pytest.raises(AssertionError):      # SageSLA/core.py:112
         m(x, x, x)
