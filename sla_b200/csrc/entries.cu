@@ -201,6 +201,7 @@ int sla_bwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   const bool fuse_kv = !legacy && sparse_bwd_tc_fits(s);
   lp.accumulate = 0;
   lp.skip_kv = fuse_kv ? 1 : 0;
+  lp.tc_pass_a = legacy ? 0 : 1;
   rc = run_linear_bwd(s, lp, st);
   if (rc != SLA_OK) return rc;
   return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 1, st,

@@ -52,6 +52,7 @@ struct LinBwdParams {
   int L, nch, rows;
   int accumulate;         // add to what dq/dk/dv already hold instead of overwriting
   int skip_kv = 0;        // stop after dq and the per-head reductions (dk, dv are produced elsewhere)
+  int tc_pass_a = 0;      // run pass A (dq, G, dz, db) as the tcgen05 kernel where it applies
 };
 
 int convert_proj(const sla_shape* s, const float* w, const float* bias, void* out, cudaStream_t st);
@@ -73,5 +74,6 @@ int run_linear_state_static(const sla_shape* s, const void* k, const void* v, vo
 int run_k_mean(const sla_shape* s, const void* k, float* partial, float* kmean, cudaStream_t st);
 int run_sparse_bwd_mma(const sla_shape* s, const BwdParams& p, cudaStream_t st);
 int run_linear_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_t st);
+int run_linear_bwd_q_tc(const sla_shape* s, const LinBwdParams& p, cudaStream_t st);
 
 }  // namespace sla

@@ -321,7 +321,9 @@ __global__ void __launch_bounds__(128) linear_bwd_kv_kernel(LinBwdParams p) {
 template <typename T, int D, int FEAT>
 static int launch_lin_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_t st) {
   const int bh = s->B * s->H, dd = D * D;
-  {
+  int rc_a = p.tc_pass_a ? run_linear_bwd_q_tc(s, p, st) : SLA_ERR_UNSUPPORTED;
+  if (rc_a != SLA_OK && rc_a != SLA_ERR_UNSUPPORTED) return rc_a;
+  if (rc_a != SLA_OK) {
     auto kern = linear_bwd_q_kernel<T, D, FEAT>;
     int smem = 5 * dd * 2 + 2 * D * 4;
     SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
