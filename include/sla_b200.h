@@ -60,10 +60,13 @@ enum sla_op { SLA_OP_BLOCK_MAP = 0, SLA_OP_FWD = 1, SLA_OP_BWD = 2, SLA_OP_LINEA
 enum sla_flags {
   SLA_FLAG_SPARSE_ONLY = 1, /* skip the linear branch and proj_l (the `_attention` operator) */
   SLA_FLAG_LEGACY_MMA = 2,  /* use the mma.sync kernels instead of the tcgen05 ones */
-  SLA_FLAG_LINEAR_UNSELECTED = 4 /* sla_fwd only: the linear branch of query block i sums over the KV blocks
+  SLA_FLAG_LINEAR_UNSELECTED = 4, /* sla_fwd only: the linear branch of query block i sums over the KV blocks
                                     that block did NOT select (the scope drawn in assets/overview_of_SLA.png)
                                     instead of over all tokens (core.py:92-96). Forward only: sla_bwd returns
                                     SLA_ERR_UNSUPPORTED with this flag. */
+  SLA_FLAG_STATE_READY = 8       /* sla_fwd only: sla_fwd_prepare has already run for this shape on the same
+                                    k, v, w, bias, lin_state and workspace (and has completed, or is ordered
+                                    before this call on the stream) */
 };
 
 typedef struct sla_shape {
@@ -153,6 +156,13 @@ SLA_API int sla_linear_state_static(const sla_shape* shape, const void* k, const
 SLA_API int sla_fwd(const sla_shape* shape, const void* q, const void* k, const void* v,
             const int32_t* lut, const float* w, const float* bias, void* o, void* o_s, float* lse,
             void* lin_state, void* ws, size_t ws_bytes, sla_stream_t stream);
+
+/* The part of sla_fwd that depends on k, v and proj_l only (core.py:91,93-94 and the 16-bit copy of the
+ * projection): a caller may run it on a second stream next to sla_block_map, which depends on q and k only,
+ * and then call sla_fwd with SLA_FLAG_STATE_READY and the same lin_state and workspace. No counterpart in the
+ * reference, where PyTorch runs these operators one after the other. */
+SLA_API int sla_fwd_prepare(const sla_shape* shape, const void* k, const void* v, const float* w,
+                    const float* bias, void* lin_state, void* ws, size_t ws_bytes, sla_stream_t stream);
 
 /* Replaces the autograd backward of sparse_linear_attention/core.py:88-100 (kernel.py:277-320 for
  * the sparse branch; PyTorch autograd of core.py:90-100 for the rest). dw (D,D) and dbias (D) are

@@ -14,12 +14,12 @@ LIB_PATH = os.path.join(_HERE, "libsla_b200.so")
 SLA_BF16, SLA_FP16, SLA_FP32 = 0, 1, 2
 PHI = {"softmax": 0, "relu": 1, "elu": 2}
 OP_BLOCK_MAP, OP_FWD, OP_BWD, OP_LINEAR_STATE, OP_SAGE_FWD, OP_SPARSE_BWD = 0, 1, 2, 3, 4, 5
-FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA, FLAG_LINEAR_UNSELECTED = 1, 2, 4
+FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA, FLAG_LINEAR_UNSELECTED, FLAG_STATE_READY = 1, 2, 4, 8
 
 # every symbol include/sla_b200.h declares
 EXPORTS = (
     "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_debug_set_trace", "sla_topk_count", "sla_workspace_bytes",
-    "sla_block_map", "sla_column_lists", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_linear_state_static", "sla_fwd", "sla_bwd",
+    "sla_block_map", "sla_column_lists", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_linear_state_static", "sla_fwd", "sla_fwd_prepare", "sla_bwd",
     "sage_sla_fwd",
 )
 
@@ -71,6 +71,8 @@ def _load() -> C.CDLL:
     lib.sla_linear_state.argtypes = [sp, vp, vp, vp, vp, C.c_size_t, vp]
     lib.sla_linear_state_static.restype = C.c_int
     lib.sla_linear_state_static.argtypes = [sp, vp, vp, vp, vp]
+    lib.sla_fwd_prepare.restype = C.c_int
+    lib.sla_fwd_prepare.argtypes = [sp, vp, vp, f32p, f32p, vp, vp, C.c_size_t, vp]
     lib.sla_fwd.restype = C.c_int
     lib.sla_fwd.argtypes = [sp, vp, vp, vp, i32p, f32p, f32p, vp, vp, f32p, vp, vp, C.c_size_t, vp]
     lib.sla_bwd.restype = C.c_int

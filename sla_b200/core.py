@@ -48,6 +48,7 @@ class SparseLinearAttention(nn.Module):
             raise NotImplementedError(f"Not supported linear scope {linear_scope}.")
         self.linear_scope = linear_scope
         self.impl_flags = ops.FLAG_LINEAR_UNSELECTED if linear_scope == "unselected" else 0
+        self.overlap_linear_state = True   # run the linear-branch state next to the block-mask prediction
         self.init_weights_()
 
     def init_weights_(self):
@@ -67,10 +68,21 @@ class SparseLinearAttention(nn.Module):
             q.requires_grad or k.requires_grad or v.requires_grad or self.proj_l.weight.requires_grad)
         if need_grad and self.linear_scope == "unselected":
             raise NotImplementedError("linear_scope='unselected' has no backward: call it under torch.no_grad()")
+        # The linear-branch state needs k, v and proj_l only and the block map q and k only: the state kernels go to
+        # a second stream and run next to the (latency-bound) mask prediction; both join before the attention kernel.
+        kc, vc = k.to(self.dtype), v.to(self.dtype)
+        prep = None
+        if self.overlap_linear_state and self.linear_scope == "all":
+            nb = (k.shape[2] + self.BLKK - 1) // self.BLKK
+            side = ops.side_stream(q.device)
+            prep = ops.prepare_linear(kc, vc, self.proj_l.weight, self.proj_l.bias, ops.topk_count(nb, self.topk),
+                                      self.BLKQ, self.BLKK, self.feature_map, self.impl_flags, stream=side)
         bm = ops.block_map(q, k, self.topk, self.BLKQ, self.BLKK, want_cols=need_grad)  # on the given dtype
-        q, k, v = q.to(self.dtype), k.to(self.dtype), v.to(self.dtype)
+        if prep is not None:
+            torch.cuda.current_stream(q.device).wait_stream(side)
+        q, k, v = q.to(self.dtype), kc, vc
         o = ops.sla_attention(q, k, v, self.proj_l.weight, self.proj_l.bias, bm, self.BLKQ, self.BLKK,
-                              self.feature_map, self.impl_flags)
+                              self.feature_map, self.impl_flags, prep)
         o = o.to(dtype)
         if return_sparsity:
             return o, bm.topk / bm.n_blocks

@@ -78,6 +78,25 @@ int sla_linear_state_static(const sla_shape* s, const void* k, const void* v, vo
   return run_linear_state_static(s, k, v, lin_state, static_cast<cudaStream_t>(stream));
 }
 
+int sla_fwd_prepare(const sla_shape* s, const void* k, const void* v, const float* w, const float* bias,
+                    void* lin_state, void* ws, size_t ws_bytes, sla_stream_t stream) {
+  if (!k || !v || !w || !lin_state || !ws) return SLA_ERR_NULL;
+  int rc = check_common(s);
+  if (rc != SLA_OK) return rc;
+  if (!all_aligned({k, v, lin_state, ws})) return SLA_ERR_BAD_ALIGN;
+  if (s->flags & SLA_FLAG_SPARSE_ONLY) return SLA_ERR_UNSUPPORTED;
+  WsLinearState wl = ws_linear_state(s);
+  if (ws_bytes < ws_fwd_total(s)) return SLA_ERR_WS_TOO_SMALL;
+  unsigned char* base = static_cast<unsigned char*>(ws);
+  void* wbits = base + wl.total;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rc = convert_proj(s, w, bias, wbits, st);
+  if (rc != SLA_OK) return rc;
+  rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wl.partial), wl.nch, wl.rows, st);
+  if (rc != SLA_OK) return rc;
+  return run_state_proj(s, lin_state, wbits, st);
+}
+
 int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
             const float* w, const float* bias, void* o, void* o_s, float* lse, void* lin_state, void* ws,
             size_t ws_bytes, sla_stream_t stream) {
@@ -98,12 +117,14 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   void* wbits = base + wl.total;
   const bool unselected = (s->flags & SLA_FLAG_LINEAR_UNSELECTED) != 0;
   if (unselected && legacy) return SLA_ERR_UNSUPPORTED;
-  rc = convert_proj(s, w, bias, wbits, st);
-  if (rc != SLA_OK) return rc;
-  rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wl.partial), wl.nch, wl.rows, st);
-  if (rc != SLA_OK) return rc;
-  rc = run_state_proj(s, lin_state, wbits, st);
-  if (rc != SLA_OK) return rc;
+  if (!(s->flags & SLA_FLAG_STATE_READY)) {
+    rc = convert_proj(s, w, bias, wbits, st);
+    if (rc != SLA_OK) return rc;
+    rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wl.partial), wl.nch, wl.rows, st);
+    if (rc != SLA_OK) return rc;
+    rc = run_state_proj(s, lin_state, wbits, st);
+    if (rc != SLA_OK) return rc;
+  }
   FwdParams p = make_fwd(s, q, k, v, lut, o, o_s, lse, lin_state, wbits);
   if (unselected) {
     // sparse branch; then the same block lists once more without softmax on (phi(q), phi(k), v) for the

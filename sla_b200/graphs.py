@@ -1,7 +1,8 @@
 """CUDA-graph capture of a module's forward and backward.
 
-Every launch of this library goes to the caller's stream and nothing synchronises (the top-k count comes from the
-shapes, utils.py:61-62), so a whole forward + backward of ``SparseLinearAttention`` can be captured once and
+Every launch of this library goes to the caller's stream, or to a second stream that forks from it and joins it
+again inside the same forward (the linear-branch state, next to the block map), and nothing synchronises (the top-k
+count comes from the shapes, utils.py:61-62), so a whole forward + backward of ``SparseLinearAttention`` can be captured once and
 replayed: about twenty kernel launches, the workspace allocations and the Python glue between them collapse into
 two graph launches per step. That matters for short sequences, where the step is launch-bound.
 

@@ -147,22 +147,75 @@ class _attention(torch.autograd.Function):
 
 
 FLAG_LINEAR_UNSELECTED = _lib.FLAG_LINEAR_UNSELECTED
+topk_count = _lib.topk_count
+
+
+@dataclass
+class LinearPrep:
+    """What `prepare_linear` left for `sla_attention`: the linear-branch state and the forward workspace."""
+    lin_state: torch.Tensor
+    ws: torch.Tensor
+    key: tuple
+
+
+_side_streams = {}
+
+
+def side_stream(device) -> torch.cuda.Stream:
+    """One extra stream per device for work that runs next to the block-mask prediction."""
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if idx not in _side_streams:
+        _side_streams[idx] = torch.cuda.Stream(device=idx)
+    return _side_streams[idx]
+
+
+def prepare_linear(k, v, weight, bias, L_blocks_topk: int, BLKQ=64, BLKK=64, feature="softmax",
+                   impl_flags: int = 0, stream: Optional[torch.cuda.Stream] = None) -> LinearPrep:
+    """The part of the forward that needs k, v and proj_l only (core.py:91,93-94): the linear-branch state
+    H, z and H W^T. With `stream` given it is launched there, after everything already queued on the current
+    stream, so that it overlaps the block-mask prediction the caller launches next; the caller joins with
+    ``torch.cuda.current_stream().wait_stream(stream)`` before `sla_attention(..., prep=...)`. Buffers are
+    allocated on the current stream (they are used there afterwards)."""
+    _require_cuda(k, v, weight)
+    B, H, L, D = k.shape
+    shape = make_shape(B, H, L, D, BLKQ, BLKK, L_blocks_topk, k.dtype, feature, flags=impl_flags)
+    dev = k.device
+    lin_state = torch.empty((B, H, 2 * D * D + D), dtype=k.dtype, device=dev)
+    ws = _workspace(shape, _lib.OP_FWD, dev)
+    w, b = weight.detach(), (bias.detach() if bias is not None else None)
+    if stream is not None:
+        stream.wait_stream(torch.cuda.current_stream(dev))
+        handle = C.c_void_p(stream.cuda_stream)
+    else:
+        handle = _stream(k)
+    check(lib.sla_fwd_prepare(C.byref(shape), _p(k), _p(v), _p(w), _p(b), _p(lin_state), _p(ws), ws.numel(), handle))
+    return LinearPrep(lin_state, ws, (B, H, L, D, BLKQ, BLKK, L_blocks_topk, k.dtype, feature, impl_flags))
 
 
 class _SLAFused(torch.autograd.Function):
     """core.py:88-100 (sparse branch + feature maps + linear branch + proj_l + sum) as one operator."""
 
     @staticmethod
-    def forward(ctx, q, k, v, weight, bias, bm: BlockMap, BLKQ, BLKK, feature, need_grad, impl_flags):
+    def forward(ctx, q, k, v, weight, bias, bm: BlockMap, BLKQ, BLKK, feature, need_grad, impl_flags, prep):
         B, H, L, D = q.shape
         shape = make_shape(B, H, L, D, BLKQ, BLKK, bm.topk, q.dtype, feature, flags=impl_flags)
         dev = q.device
         o = torch.empty_like(q)
         o_s = torch.empty_like(q) if need_grad else None
         lse = torch.empty((B, H, L), dtype=torch.float32, device=dev)
-        lin_state = torch.empty((B, H, 2 * D * D + D), dtype=q.dtype, device=dev)
-        ws = _workspace(shape, _lib.OP_FWD, dev)
-        check(lib.sla_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o), _p(o_s),
+        if prep is not None:
+            if prep.key != (B, H, L, D, BLKQ, BLKK, bm.topk, q.dtype, feature, impl_flags):
+                raise ValueError("prepare_linear was called for another shape or configuration")
+            lin_state, ws = prep.lin_state, prep.ws
+            fwd_shape = make_shape(B, H, L, D, BLKQ, BLKK, bm.topk, q.dtype, feature,
+                                   flags=impl_flags | _lib.FLAG_STATE_READY)
+        else:
+            lin_state = torch.empty((B, H, 2 * D * D + D), dtype=q.dtype, device=dev)
+            ws = _workspace(shape, _lib.OP_FWD, dev)
+            fwd_shape = shape
+        check(lib.sla_fwd(C.byref(fwd_shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o), _p(o_s),
                           _p(lse), _p(lin_state), _p(ws), ws.numel(), _stream(q)))
         if need_grad:
             ctx.save_for_backward(q, k, v, o_s, lse, lin_state, weight, bm.lut, bm.col_offsets, bm.col_index)
@@ -183,18 +236,19 @@ class _SLAFused(torch.autograd.Function):
         check(lib.sla_bwd(C.byref(shape), _p(q), _p(k), _p(v), _p(o_s), _p(lse), _p(d_o), _p(lut), _p(co), _p(ci),
                           _p(weight), _p(lin_state), _p(dq), _p(dk), _p(dv), _p(dw), _p(db), _p(ws), ws.numel(),
                           _stream(q)))
-        return dq, dk, dv, dw, (db if ctx.has_bias else None), None, None, None, None, None, None
+        return dq, dk, dv, dw, (db if ctx.has_bias else None), None, None, None, None, None, None, None
 
 
 def sla_attention(q, k, v, weight, bias, bm: BlockMap, BLKQ=64, BLKK=64, feature="softmax",
-                  impl_flags: int = 0):
-    """o = o_s + proj_l(o_l) for q, k, v already in the 16-bit compute dtype."""
+                  impl_flags: int = 0, prep: Optional[LinearPrep] = None):
+    """o = o_s + proj_l(o_l) for q, k, v already in the 16-bit compute dtype. `prep`: the result of
+    `prepare_linear` on the same k, v, weight, bias (already joined into the current stream)."""
     _require_cuda(q, k, v, weight)
     need_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (q, k, v, weight, bias))
     if need_grad and bm.col_offsets is None:
         raise RuntimeError("the block map was built without column lists (want_cols=True) but a backward is needed")
-    return _SLAFused.apply(q, k, v, weight, bias, bm, BLKQ, BLKK, feature, need_grad, impl_flags)
+    return _SLAFused.apply(q, k, v, weight, bias, bm, BLKQ, BLKK, feature, need_grad, impl_flags, prep)
 
 
 def sage_sla_attention(q, k, v, weight, bias, bm: BlockMap, feature="softmax", sparse_only: bool = False):

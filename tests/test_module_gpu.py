@@ -205,3 +205,28 @@ def test_graphed_forward_backward_matches_eager():
     for a, b in ((qg.grad, qe.grad), (kg.grad, ke.grad), (vg.grad, ve.grad),
                  (m_graph.proj_l.weight.grad, m_eager.proj_l.weight.grad)):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("D,BLKQ,L,feat", [(128, 64, 1500, "softmax"), (64, 128, 1000, "elu")])
+def test_linear_state_on_side_stream_changes_nothing(D, BLKQ, L, feat):
+    """The module launches the linear-branch state (sla_fwd_prepare) on a second stream next to the block map and
+    calls sla_fwd with SLA_FLAG_STATE_READY: same kernels on the same data, so forward and gradients are
+    bit-identical to the single-stream order."""
+    import sla_b200
+    g = torch.Generator().manual_seed(11)
+    q, k, v, do = (torch.randn(1, 2, L, D, generator=g).bfloat16().cuda() for _ in range(4))
+    m2 = sla_b200.SparseLinearAttention(D, 0.2, feat, BLKQ, 64).cuda()
+    res = {}
+    for overlap in (True, False):
+        m2.overlap_linear_state = overlap
+        with torch.no_grad():
+            m2.proj_l.weight.copy_(torch.randn(D, D, generator=torch.Generator().manual_seed(5)) * 0.05)
+            m2.proj_l.bias.fill_(0.01)
+        m2.zero_grad()
+        qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+        o = m2(qg, kg, vg)
+        o.backward(do)
+        torch.cuda.synchronize()
+        res[overlap] = (o.detach(), qg.grad, kg.grad, vg.grad, m2.proj_l.weight.grad.clone(), m2.proj_l.bias.grad.clone())
+    for a, b in zip(res[True], res[False]):
+        assert torch.equal(a, b)
