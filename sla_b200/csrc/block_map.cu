@@ -3,6 +3,8 @@
 // Follows sparse_linear_attention/utils.py:21-67 including its rounding points: the column mean, the
 // smoothed K, the pooled means and the pooled scores are each rounded to the input dtype.
 // All kernels here are HBM/L2-bound integer/compare work; none uses tensor cores.
+#include <type_traits>
+
 #include "common.cuh"
 #include "workspace.h"
 
@@ -113,9 +115,10 @@ __device__ inline uint32_t order_key(float x) {
 }
 
 constexpr int kTopkRows = 8;  // query-block rows per CTA == warps per CTA
+constexpr int kScoreStages = 5;   // depth of each thread's private prefetch ring of pooled-K chunks
 
 // One CTA scores kTopkRows query-block rows against every KV block of the head, then each warp
-// selects the top-k of one row by a 4-pass radix select on order-preserving keys and writes the
+// selects the top-k of one row by a bitwise search for the k-th largest order-preserving key and writes the
 // selected indices in ascending order; ties at the k-th score go to the lower index.
 template <typename TIn, int D>
 __global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
@@ -123,55 +126,68 @@ __global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
     int8_t* __restrict__ sparse_map, int32_t* __restrict__ col_offsets, int mb, int nb, int topk) {
   constexpr int N = VecLoad<TIn>::N;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* spq = reinterpret_cast<float*>(smem_raw);                        // [R][D]
-  uint32_t* hist = reinterpret_cast<uint32_t*>(spq + kTopkRows * D);       // [R][256]
-  uint32_t* keys = hist + kTopkRows * 256;                                 // [R][nb]
+  float2* spq = reinterpret_cast<float2*>(smem_raw);                      // [R][D], every value twice: (q, q)
+  uint32_t* keys = reinterpret_cast<uint32_t*>(spq + kTopkRows * D);       // [R][nb]
   const int bh = blockIdx.y, row_base = blockIdx.x * kTopkRows;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   for (int i = tid; i < kTopkRows * D; i += blockDim.x) {
     int r = i / D, d = i % D;
     int row = row_base + r;
-    spq[i] = row < mb ? Elem<TIn>::to_f(pooled_q[(static_cast<size_t>(bh) * mb + row) * D + d]) : 0.f;
+    const float qv = row < mb ? Elem<TIn>::to_f(pooled_q[(static_cast<size_t>(bh) * mb + row) * D + d]) : 0.f;
+    spq[i] = make_float2(qv, qv);
   }
   __syncthreads();
 
   const TIn* pk = pooled_k + static_cast<size_t>(bh) * nb * D;
-  // two KV blocks per thread and pass: every shared-memory read of a pooled query value feeds two
-  // FMAs; each score is still one sequential fp32 sum over d
+  unsigned char* ring = reinterpret_cast<unsigned char*>(keys + kTopkRows * nb);   // [stages][2][threads] x 16 B
+  auto slot_off = [&](int st, int h) { return ((st * 2 + h) * (kTopkRows * 32) + tid) * 16; };
+  auto slot = [&](int st, int h) { return smem_u32(ring) + slot_off(st, h); };
+  // two KV blocks per thread and pass, their two sums kept as the halves of one packed fp32 FMA (fma.rn.f32x2:
+  // two independent round-to-nearest FMAs, so each score is still one sequential fp32 sum over d)
   for (int j = tid; j < nb; j += 2 * blockDim.x) {
     const int j1 = j + blockDim.x;
     const bool has1 = j1 < nb;
     const TIn* k0 = pk + static_cast<size_t>(j) * D;
     const TIn* k1 = pk + static_cast<size_t>(has1 ? j1 : j) * D;
-    float acc0[kTopkRows], acc1[kTopkRows];
+    float2 acc[kTopkRows];       // .x: block j, .y: block j1
 #pragma unroll
-    for (int r = 0; r < kTopkRows; ++r) acc0[r] = acc1[r] = 0.f;
-#pragma unroll 2
-    for (int c = 0; c < D; c += N) {
+    for (int r = 0; r < kTopkRows; ++r) acc[r] = make_float2(0.f, 0.f);
+    // The two pooled-K rows of this thread come through a private ring of 16-byte slots filled by cp.async
+    // kScoreStages - 1 steps ahead: a thread's own loads are 256 bytes apart from its neighbours', so what bounds
+    // this loop is the latency of those loads, not their number.
+#pragma unroll
+    for (int st = 0; st < kScoreStages - 1; ++st) {
+      cp_async16(slot(st, 0), k0 + st * N, true);
+      cp_async16(slot(st, 1), k1 + st * N, true);
+      cp_async_commit();
+    }
+#pragma unroll
+    for (int ci = 0; ci < D / N; ++ci) {
+      const int c = ci * N, pf = ci + kScoreStages - 1;
+      if (pf < D / N) {
+        cp_async16(slot(pf % kScoreStages, 0), k0 + pf * N, true);
+        cp_async16(slot(pf % kScoreStages, 1), k1 + pf * N, true);
+      }
+      cp_async_commit();
+      cp_async_wait<kScoreStages - 1>();
       float kv0[N], kv1[N];
-      VecLoad<TIn>::load(kv0, k0 + c);
-      VecLoad<TIn>::load(kv1, k1 + c);
+      VecLoad<TIn>::load(kv0, reinterpret_cast<const TIn*>(ring + slot_off(ci % kScoreStages, 0)));
+      VecLoad<TIn>::load(kv1, reinterpret_cast<const TIn*>(ring + slot_off(ci % kScoreStages, 1)));
 #pragma unroll
       for (int r = 0; r < kTopkRows; ++r) {
 #pragma unroll
-        for (int e = 0; e < N; e += 4) {
-          float4 qv = *reinterpret_cast<const float4*>(spq + r * D + c + e);
-          acc0[r] = fmaf(qv.x, kv0[e], acc0[r]);
-          acc0[r] = fmaf(qv.y, kv0[e + 1], acc0[r]);
-          acc0[r] = fmaf(qv.z, kv0[e + 2], acc0[r]);
-          acc0[r] = fmaf(qv.w, kv0[e + 3], acc0[r]);
-          acc1[r] = fmaf(qv.x, kv1[e], acc1[r]);
-          acc1[r] = fmaf(qv.y, kv1[e + 1], acc1[r]);
-          acc1[r] = fmaf(qv.z, kv1[e + 2], acc1[r]);
-          acc1[r] = fmaf(qv.w, kv1[e + 3], acc1[r]);
+        for (int e = 0; e < N; e += 2) {
+          const float4 qq = *reinterpret_cast<const float4*>(spq + r * D + c + e);   // (q_e, q_e, q_e+1, q_e+1)
+          acc[r] = __ffma2_rn(make_float2(qq.x, qq.y), make_float2(kv0[e], kv1[e]), acc[r]);
+          acc[r] = __ffma2_rn(make_float2(qq.z, qq.w), make_float2(kv0[e + 1], kv1[e + 1]), acc[r]);
         }
       }
     }
 #pragma unroll
     for (int r = 0; r < kTopkRows; ++r) {
-      keys[r * nb + j] = order_key(round_to<TIn>(acc0[r]));  // utils.py:59
-      if (has1) keys[r * nb + j1] = order_key(round_to<TIn>(acc1[r]));
+      keys[r * nb + j] = order_key(round_to<TIn>(acc[r].x));  // utils.py:59
+      if (has1) keys[r * nb + j1] = order_key(round_to<TIn>(acc[r].y));
     }
   }
   __syncthreads();
@@ -179,55 +195,35 @@ __global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
   const int row = row_base + warp;
   if (row >= mb) return;
   const uint32_t* kr = keys + warp * nb;
-  uint32_t* h = hist + warp * 256;
-  // radix select: find the key of the topk-th largest element
-  uint32_t prefix = 0, prefix_mask = 0;
-  int need = topk;
-  for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int b = lane; b < 256; b += 32) h[b] = 0;
-    __syncwarp();
-    for (int j = lane; j < nb; j += 32) {
-      uint32_t key = kr[j];
-      if ((key & prefix_mask) == prefix) atomicAdd(&h[(key >> shift) & 255u], 1u);
-    }
-    __syncwarp();
-    // lane owns bins [255 - 8*lane - 7, 255 - 8*lane], scanned from the top
-    uint32_t cnt[8];
-    uint32_t lane_sum = 0;
+  // Key of the topk-th largest element, one bit at a time from the top: the largest value v with
+  // count(key >= v) >= topk. Counting is a compare and an add per key and one warp reduction per bit; no
+  // histogram, so rows whose scores share their high bits (all of them) cost the same as any other.
+  // The first 32 * kKeyRegs keys of the row sit in registers (all of them up to 512 KV blocks), the rest is re-read
+  // from shared memory; a missing key is 0, below every candidate (a candidate has at least one bit set).
+  constexpr int kKeyRegs = 16;
+  uint32_t kreg[kKeyRegs];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      cnt[i] = h[255 - 8 * lane - i];
-      lane_sum += cnt[i];
-    }
-    uint32_t incl = lane_sum;
+  for (int i = 0; i < kKeyRegs; ++i) kreg[i] = lane + 32 * i < nb ? kr[lane + 32 * i] : 0u;
+  // Scores were rounded to TIn: their keys have kLowZero low bits clear, and no candidate with one of those bits
+  // set can be the k-th largest key.
+  constexpr int kLowZero = std::is_same<TIn, __nv_bfloat16>::value ? 16 : (std::is_same<TIn, __half>::value ? 13 : 0);
+  uint32_t prefix = 0;
+  for (int bit = 31; bit >= kLowZero; --bit) {
+    const uint32_t cand = prefix | (1u << bit);
+    int c0 = 0, c1 = 0;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
+    for (int i = 0; i < kKeyRegs; i += 2) {
+      c0 += kreg[i] >= cand ? 1 : 0;
+      c1 += kreg[i + 1] >= cand ? 1 : 0;
     }
-    uint32_t excl = incl - lane_sum;
-    bool owner = excl < static_cast<uint32_t>(need) && incl >= static_cast<uint32_t>(need);
-    uint32_t sel_bin = 0, above = 0;
-    if (owner) {
-      uint32_t run = excl;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (run < static_cast<uint32_t>(need) && run + cnt[i] >= static_cast<uint32_t>(need)) {
-          sel_bin = 255 - 8 * lane - i;
-          above = run;
-        }
-        run += cnt[i];
-      }
-    }
-    uint32_t ob = __ballot_sync(0xffffffffu, owner);
-    int src = __ffs(ob) - 1;
-    sel_bin = __shfl_sync(0xffffffffu, sel_bin, src);
-    above = __shfl_sync(0xffffffffu, above, src);
-    need -= static_cast<int>(above);
-    prefix |= sel_bin << shift;
-    prefix_mask |= 255u << shift;
-    __syncwarp();
+    for (int j = lane + 32 * kKeyRegs; j < nb; j += 32) c0 += kr[j] >= cand ? 1 : 0;
+    if (__reduce_add_sync(0xffffffffu, c0 + c1) >= topk) prefix = cand;
   }
+  int above = 0;
+#pragma unroll
+  for (int i = 0; i < kKeyRegs; ++i) above += kreg[i] > prefix ? 1 : 0;
+  for (int j = lane + 32 * kKeyRegs; j < nb; j += 32) above += kr[j] > prefix ? 1 : 0;
+  const int need = topk - __reduce_add_sync(0xffffffffu, above);
   const uint32_t thr = prefix;  // key of the k-th largest; `need` of the elements equal to it are taken
   int32_t* out = lut + (static_cast<size_t>(bh) * mb + row) * topk;
   int8_t* map_row = sparse_map ? sparse_map + (static_cast<size_t>(bh) * mb + row) * nb : nullptr;
@@ -346,7 +342,7 @@ static int launch_block_map(const sla_shape* s, const TIn* q, const TIn* k, int3
   pool_kernel<TIn, D><<<dim3(max(mb, nb), bh, 2), 256, 0, st>>>(q, k, kmean, pq, pk, L, s->BLKQ, s->BLKK);
   SLA_LAUNCH_OK();
   if (want_cols) SLA_CUDA_OK(cudaMemsetAsync(col_offsets, 0, sizeof(int32_t) * size_t(bh) * (nb + 1), st));
-  size_t smem = size_t(kTopkRows) * (D + 256 + nb) * 4;
+  size_t smem = (size_t(kTopkRows) * (2 * D + nb) * 4 + 15) / 16 * 16 + size_t(kScoreStages) * 2 * kTopkRows * 32 * 16;
   if (smem > 200 * 1024) return SLA_ERR_BAD_SHAPE;
   auto kern = score_topk_kernel<TIn, D>;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
