@@ -64,9 +64,9 @@ enum sla_flags {
                                     that block did NOT select (the scope drawn in assets/overview_of_SLA.png)
                                     instead of over all tokens (core.py:92-96). Forward only: sla_bwd returns
                                     SLA_ERR_UNSUPPORTED with this flag. */
-  SLA_FLAG_STATE_READY = 8       /* sla_fwd only: sla_fwd_prepare has already run for this shape on the same
-                                    k, v, w, bias, lin_state and workspace (and has completed, or is ordered
-                                    before this call on the stream) */
+  SLA_FLAG_STATE_READY = 8       /* sla_fwd / sage_sla_fwd only: sla_fwd_prepare / sage_sla_prepare has already run
+                                    for this shape on the same inputs, lin_state and workspace (and has completed,
+                                    or is ordered before this call on the stream) */
 };
 
 typedef struct sla_shape {
@@ -179,6 +179,12 @@ SLA_API int sla_bwd(const sla_shape* shape, const void* q, const void* k, const 
 SLA_API int sage_sla_fwd(const sla_shape* shape, const void* q, const void* k, const void* v,
                  const int32_t* lut, const float* w, const float* bias, void* o, void* lin_state,
                  void* ws, size_t ws_bytes, sla_stream_t stream);
+
+/* The part of sage_sla_fwd that does not need the block map: the linear-branch state and the quantized copies of
+ * q, k, v (SageSLA/core.py:102-108,127-129). A caller may run it on a second stream next to sla_block_map and then
+ * call sage_sla_fwd with SLA_FLAG_STATE_READY and the same lin_state and workspace. */
+SLA_API int sage_sla_prepare(const sla_shape* shape, const void* q, const void* k, const void* v, const float* w,
+                     const float* bias, void* lin_state, void* ws, size_t ws_bytes, sla_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -20,7 +20,7 @@ FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA, FLAG_LINEAR_UNSELECTED, FLAG_STATE_READY = 1,
 EXPORTS = (
     "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_debug_set_trace", "sla_topk_count", "sla_workspace_bytes",
     "sla_block_map", "sla_column_lists", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_linear_state_static", "sla_fwd", "sla_fwd_prepare", "sla_bwd",
-    "sage_sla_fwd",
+    "sage_sla_fwd", "sage_sla_prepare",
 )
 
 
@@ -78,6 +78,8 @@ def _load() -> C.CDLL:
     lib.sla_bwd.restype = C.c_int
     lib.sla_bwd.argtypes = [sp, vp, vp, vp, vp, f32p, vp, i32p, i32p, i32p, f32p, vp, vp, vp, vp, f32p, f32p,
                             vp, C.c_size_t, vp]
+    lib.sage_sla_prepare.restype = C.c_int
+    lib.sage_sla_prepare.argtypes = [sp, vp, vp, vp, f32p, f32p, vp, vp, C.c_size_t, vp]
     lib.sage_sla_fwd.restype = C.c_int
     lib.sage_sla_fwd.argtypes = [sp, vp, vp, vp, i32p, f32p, f32p, vp, vp, vp, C.c_size_t, vp]
     return lib

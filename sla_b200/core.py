@@ -103,6 +103,7 @@ class SageSparseLinearAttention(nn.Module):
         if feature_map not in _FEATURES:
             raise NotImplementedError(f"Not supported feature map {feature_map}.")
         self.feature_map = feature_map
+        self.overlap_prepare = True
         self.init_weights_()
 
     def init_weights_(self):
@@ -114,10 +115,21 @@ class SageSparseLinearAttention(nn.Module):
         dtype = q.dtype
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         assert q.size(-1) in [64, 128], "headdim should be in [64, 128]."
+        # quantization pre-passes and linear-branch state on a second stream next to the block-mask prediction
+        qc, kc, vc = q.to(self.dtype), k.to(self.dtype), v.to(self.dtype)
+        prep = None
+        if self.overlap_prepare:
+            side = ops.side_stream(q.device)
+            with torch.no_grad():
+                prep = ops.sage_prepare(qc, kc, vc, self.proj_l.weight, self.proj_l.bias,
+                                        ops.topk_count((k.shape[2] + 63) // 64, self.topk), self.feature_map,
+                                        stream=side)
         bm = ops.block_map(q, k, self.topk, 128, 64)
-        q, k, v = q.to(self.dtype), k.to(self.dtype), v.to(self.dtype)
+        if prep is not None:
+            torch.cuda.current_stream(q.device).wait_stream(side)
+        q, k, v = qc, kc, vc
         with torch.no_grad():
-            o = ops.sage_sla_attention(q, k, v, self.proj_l.weight, self.proj_l.bias, bm, self.feature_map)
+            o = ops.sage_sla_attention(q, k, v, self.proj_l.weight, self.proj_l.bias, bm, self.feature_map, prep=prep)
         o = o.to(dtype)
         if return_sparsity:
             return o, bm.topk / bm.n_blocks

@@ -625,10 +625,10 @@ __global__ void __launch_bounds__(256) sage_quant_v_kernel(const T* __restrict__
   }
 }
 
+// The quantization pre-passes: need q, k, v only.
 template <typename T, int D>
-static int run_sage_typed(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
-                          void* o_s, float* lse, unsigned char* ws, const void* lin_state, const void* wbits,
-                          cudaStream_t st) {
+static int run_sage_quant_typed(const sla_shape* s, const void* q, const void* k, const void* v, unsigned char* ws,
+                                cudaStream_t st) {
   const int bh = s->B * s->H, L = s->L;
   const int mb = ceil_div(L, 128), nb = ceil_div(L, 64);
   WsSage w = ws_sage(s);
@@ -651,7 +651,23 @@ static int run_sage_typed(const sla_shape* s, const void* q, const void* k, cons
   SLA_LAUNCH_OK();
   sage_quant_v_kernel<T, D><<<dim3(nb, bh), 256, 0, st>>>(static_cast<const T*>(v), vs, v8, L);
   SLA_LAUNCH_OK();
+  return SLA_OK;
+}
 
+// The attention kernel on the quantized copies.
+template <typename T, int D>
+static int run_sage_main_typed(const sla_shape* s, const void* q, const int32_t* lut, void* o_s, float* lse,
+                               unsigned char* ws, const void* lin_state, const void* wbits, cudaStream_t st) {
+  const int bh = s->B * s->H, L = s->L;
+  const int mb = ceil_div(L, 128), nb = ceil_div(L, 64);
+  WsSage w = ws_sage(s);
+  int8_t* q8 = reinterpret_cast<int8_t*>(ws + w.q8);
+  int8_t* k8 = reinterpret_cast<int8_t*>(ws + w.k8);
+  uint8_t* v8 = ws + w.v8;
+  float* qs = reinterpret_cast<float*>(ws + w.qscale);
+  float* ks = reinterpret_cast<float*>(ws + w.kscale);
+  float* vs = reinterpret_cast<float*>(ws + w.vscale);
+  int rc;
   CUtensorMap tq, tk, tv, to, tq16, thw;
   if ((rc = make_tmap_3d_u8(&tq, q8, 128, L, bh, 128)) != SLA_OK) return rc;
   if ((rc = make_tmap_3d_u8(&tk, k8, 128, L, bh, 64)) != SLA_OK) return rc;
@@ -683,38 +699,84 @@ static int run_sage_typed(const sla_shape* s, const void* q, const void* k, cons
 
 }  // namespace sla
 
+namespace sla {
+
+static int sage_quant(const sla_shape* s, const void* q, const void* k, const void* v, unsigned char* ws, cudaStream_t st) {
+  if (s->D == 64)
+    return s->dtype == SLA_BF16 ? run_sage_quant_typed<__nv_bfloat16, 64>(s, q, k, v, ws, st)
+                                : run_sage_quant_typed<__half, 64>(s, q, k, v, ws, st);
+  return s->dtype == SLA_BF16 ? run_sage_quant_typed<__nv_bfloat16, 128>(s, q, k, v, ws, st)
+                              : run_sage_quant_typed<__half, 128>(s, q, k, v, ws, st);
+}
+static int sage_main(const sla_shape* s, const void* q, const int32_t* lut, void* o, float* lse, unsigned char* ws,
+                     const void* state, const void* wbits, cudaStream_t st) {
+  if (s->D == 64)
+    return s->dtype == SLA_BF16 ? run_sage_main_typed<__nv_bfloat16, 64>(s, q, lut, o, lse, ws, state, wbits, st)
+                                : run_sage_main_typed<__half, 64>(s, q, lut, o, lse, ws, state, wbits, st);
+  return s->dtype == SLA_BF16 ? run_sage_main_typed<__nv_bfloat16, 128>(s, q, lut, o, lse, ws, state, wbits, st)
+                              : run_sage_main_typed<__half, 128>(s, q, lut, o, lse, ws, state, wbits, st);
+}
+static int sage_check(const sla_shape* s) {
+  int rc = validate_shape(s);
+  if (rc != SLA_OK) return rc;
+  if (s->BLKQ != 128 || s->BLKK != 64) return SLA_ERR_BAD_SHAPE;   // SageSLA/README.md:16-17
+  if (s->D != 64 && s->D != 128) return SLA_ERR_UNSUPPORTED;       // SageSLA/core.py:112
+  return check_device_arch();
+}
+// linear-branch state (SageSLA/core.py:148-158 uses the same branch as the 16-bit module); the read-out, proj_l
+// and the final sum run in the epilogue of the quantized kernel
+static int sage_state(const sla_shape* s, const void* k, const void* v, const float* w, const float* bias,
+                      void* lin_state, unsigned char* base, cudaStream_t st) {
+  WsSage wsz = ws_sage(s);
+  WsLinearState wl = ws_linear_state(s);
+  void* wbits = base + wsz.wbits;
+  int rc;
+  if ((rc = convert_proj(s, w, bias, wbits, st)) != SLA_OK) return rc;
+  if ((rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wsz.lin + wl.partial), wl.nch, wl.rows, st)) != SLA_OK) return rc;
+  return run_state_proj(s, lin_state, wbits, st);
+}
+
+}  // namespace sla
+
+extern "C" int sage_sla_prepare(const sla_shape* s, const void* q, const void* k, const void* v, const float* w,
+                                const float* bias, void* lin_state, void* ws, size_t ws_bytes, sla_stream_t stream) {
+  using namespace sla;
+  if (!q || !k || !v || !ws) return SLA_ERR_NULL;
+  int rc = sage_check(s);
+  if (rc != SLA_OK) return rc;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(ws)) return SLA_ERR_BAD_ALIGN;
+  if (ws_bytes < ws_sage(s).total) return SLA_ERR_WS_TOO_SMALL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned char* base = static_cast<unsigned char*>(ws);
+  if (!(s->flags & SLA_FLAG_SPARSE_ONLY)) {
+    if (!w || !lin_state) return SLA_ERR_NULL;
+    if (!aligned16(lin_state)) return SLA_ERR_BAD_ALIGN;
+    if ((rc = sage_state(s, k, v, w, bias, lin_state, base, st)) != SLA_OK) return rc;
+  }
+  return sage_quant(s, q, k, v, base, st);
+}
+
 extern "C" int sage_sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
                             const float* w, const float* bias, void* o, void* lin_state, void* ws, size_t ws_bytes,
                             sla_stream_t stream) {
   using namespace sla;
   if (!q || !k || !v || !lut || !o || !ws) return SLA_ERR_NULL;
-  int rc = validate_shape(s);
+  int rc = sage_check(s);
   if (rc != SLA_OK) return rc;
-  if (s->BLKQ != 128 || s->BLKK != 64) return SLA_ERR_BAD_SHAPE;   // SageSLA/README.md:16-17
-  if (s->D != 64 && s->D != 128) return SLA_ERR_UNSUPPORTED;       // SageSLA/core.py:112
-  if ((rc = check_device_arch()) != SLA_OK) return rc;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(ws)) return SLA_ERR_BAD_ALIGN;
   WsSage wsz = ws_sage(s);
   if (ws_bytes < wsz.total) return SLA_ERR_WS_TOO_SMALL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   unsigned char* base = static_cast<unsigned char*>(ws);
   float* lse = reinterpret_cast<float*>(base + wsz.lse);
+  const bool ready = (s->flags & SLA_FLAG_STATE_READY) != 0;   // sage_sla_prepare has filled lin_state and ws
   const void* state = nullptr;
-  void* wbits = base + wsz.wbits;
   if (!(s->flags & SLA_FLAG_SPARSE_ONLY)) {
-    // linear-branch state first (SageSLA/core.py:148-158 uses the same branch as the 16-bit module); the
-    // read-out, proj_l and the final sum run in the epilogue of the quantized kernel
     if (!w || !lin_state) return SLA_ERR_NULL;
     if (!aligned16(lin_state)) return SLA_ERR_BAD_ALIGN;
-    WsLinearState wl = ws_linear_state(s);
-    if ((rc = convert_proj(s, w, bias, wbits, st)) != SLA_OK) return rc;
-    if ((rc = run_linear_state(s, k, v, lin_state, reinterpret_cast<float*>(base + wsz.lin + wl.partial), wl.nch, wl.rows, st)) != SLA_OK) return rc;
-    if ((rc = run_state_proj(s, lin_state, wbits, st)) != SLA_OK) return rc;
+    if (!ready && (rc = sage_state(s, k, v, w, bias, lin_state, base, st)) != SLA_OK) return rc;
     state = lin_state;
   }
-  if (s->D == 64)
-    return s->dtype == SLA_BF16 ? run_sage_typed<__nv_bfloat16, 64>(s, q, k, v, lut, o, lse, base, state, wbits, st)
-                                : run_sage_typed<__half, 64>(s, q, k, v, lut, o, lse, base, state, wbits, st);
-  return s->dtype == SLA_BF16 ? run_sage_typed<__nv_bfloat16, 128>(s, q, k, v, lut, o, lse, base, state, wbits, st)
-                              : run_sage_typed<__half, 128>(s, q, k, v, lut, o, lse, base, state, wbits, st);
+  if (!ready && (rc = sage_quant(s, q, k, v, base, st)) != SLA_OK) return rc;
+  return sage_main(s, q, lut, o, lse, base, state, base + wsz.wbits, st);
 }

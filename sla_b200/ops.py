@@ -251,16 +251,46 @@ def sla_attention(q, k, v, weight, bias, bm: BlockMap, BLKQ=64, BLKK=64, feature
     return _SLAFused.apply(q, k, v, weight, bias, bm, BLKQ, BLKK, feature, need_grad, impl_flags, prep)
 
 
-def sage_sla_attention(q, k, v, weight, bias, bm: BlockMap, feature="softmax", sparse_only: bool = False):
+def sage_prepare(q, k, v, weight, bias, topk: int, feature="softmax", sparse_only: bool = False,
+                 stream: Optional[torch.cuda.Stream] = None) -> LinearPrep:
+    """What the quantized forward needs besides the block map (linear-branch state, INT8 q and k, e4m3 v), launched
+    on `stream` (after everything already queued on the current stream) so that it overlaps the block-mask
+    prediction; join with ``torch.cuda.current_stream().wait_stream(stream)`` before
+    `sage_sla_attention(..., prep=...)`."""
+    _require_cuda(q, k, v, weight)
+    B, H, L, D = q.shape
+    flags = _lib.FLAG_SPARSE_ONLY if sparse_only else 0
+    shape = make_shape(B, H, L, D, 128, 64, topk, q.dtype, feature, flags=flags)
+    lin_state = torch.empty((B, H, 2 * D * D + D), dtype=q.dtype, device=q.device)
+    ws = _workspace(shape, _lib.OP_SAGE_FWD, q.device)
+    w, b = weight.detach(), (bias.detach() if bias is not None else None)
+    if stream is not None:
+        stream.wait_stream(torch.cuda.current_stream(q.device))
+        handle = C.c_void_p(stream.cuda_stream)
+    else:
+        handle = _stream(q)
+    check(lib.sage_sla_prepare(C.byref(shape), _p(q), _p(k), _p(v), _p(w), _p(b), _p(lin_state), _p(ws), ws.numel(),
+                               handle))
+    return LinearPrep(lin_state, ws, (B, H, L, D, 128, 64, topk, q.dtype, feature, flags))
+
+
+def sage_sla_attention(q, k, v, weight, bias, bm: BlockMap, feature="softmax", sparse_only: bool = False,
+                       prep: Optional[LinearPrep] = None):
     """SageSLA/core.py:100-158: quantized sparse branch + linear branch + proj_l. Forward only.
     ``sparse_only`` returns the quantized sparse branch alone (the o_s of SageSLA/core.py:114)."""
     _require_cuda(q, k, v, weight)
     B, H, L, D = q.shape
-    shape = make_shape(B, H, L, D, 128, 64, bm.topk, q.dtype, feature,
-                       flags=_lib.FLAG_SPARSE_ONLY if sparse_only else 0)
+    flags = _lib.FLAG_SPARSE_ONLY if sparse_only else 0
     o = torch.empty_like(q)
-    lin_state = torch.empty((B, H, 2 * D * D + D), dtype=q.dtype, device=q.device)
-    ws = _workspace(shape, _lib.OP_SAGE_FWD, q.device)
+    if prep is not None:
+        if prep.key != (B, H, L, D, 128, 64, bm.topk, q.dtype, feature, flags):
+            raise ValueError("sage_prepare was called for another shape or configuration")
+        lin_state, ws = prep.lin_state, prep.ws
+        flags |= _lib.FLAG_STATE_READY
+    shape = make_shape(B, H, L, D, 128, 64, bm.topk, q.dtype, feature, flags=flags)
+    if prep is None:
+        lin_state = torch.empty((B, H, 2 * D * D + D), dtype=q.dtype, device=q.device)
+        ws = _workspace(shape, _lib.OP_SAGE_FWD, q.device)
     check(lib.sage_sla_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o),
                            _p(lin_state), _p(ws), ws.numel(), _stream(q)))
     return o

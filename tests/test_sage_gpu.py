@@ -73,3 +73,20 @@ def test_sage_rejects_other_block_sizes_and_head_dims():
     x = torch.randn(1, 1, 256, 32, device="cuda").bfloat16()
     with pytest.raises(AssertionError):      # SageSLA/core.py:112
         m(x, x, x)
+
+
+def test_sage_prepare_on_side_stream_changes_nothing():
+    """The module runs sage_sla_prepare (quantized copies + linear-branch state) on a second stream next to the
+    block map and calls sage_sla_fwd with SLA_FLAG_STATE_READY: same kernels, bit-identical output."""
+    import sla_b200
+    q, k, v = _inputs(1, 2, 1300, 128, 21, 1.0)
+    m = sla_b200.SageSparseLinearAttention(128, 0.25, "softmax").cuda()
+    with torch.no_grad():
+        m.proj_l.weight.copy_(torch.randn(128, 128, generator=torch.Generator().manual_seed(2)) * 0.05)
+    outs = []
+    for overlap in (True, False):
+        m.overlap_prepare = overlap
+        with torch.no_grad():
+            outs.append(m(q.cuda(), k.cuda(), v.cuda()))
+        torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1])
