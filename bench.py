@@ -265,6 +265,9 @@ def main():
     ap.add_argument("--legacy-mma", action="store_true", help="force the mma.sync kernels")
     ap.add_argument("--graph", action="store_true",
                     help="also time the step replayed from CUDA graphs (sla_b200.graphed); reported as graph_ms_per_step")
+    ap.add_argument("--single-stream", action="store_true",
+                    help="keep every launch on one stream (the modules otherwise run the linear-branch state and "
+                         "the quantization pre-passes on a second stream next to the block map)")
     ap.add_argument("--topk", type=float, default=None, help="override the workload's top-k ratio (c5 sweeps 0.05/0.1/0.2)")
     args = ap.parse_args()
 
@@ -307,6 +310,8 @@ def main():
         m = sla_b200.SageSparseLinearAttention(w.D, w.topk, w.feature).to(dev)
     else:
         m = sla_b200.SparseLinearAttention(w.D, w.topk, w.feature, w.BLKQ, w.BLKK).to(dev)
+    if args.single_stream:
+        m.overlap_linear_state = m.overlap_prepare = False   # default None: fork when the tensors are large enough
     with torch.no_grad():
         m.proj_l.weight.copy_(W)
         m.proj_l.bias.copy_(b)

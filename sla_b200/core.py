@@ -15,6 +15,17 @@ from . import ops
 
 _FEATURES = ("elu", "relu", "softmax")
 
+# Forking to a second stream costs two cross-stream waits per forward (some tens of microseconds when the step is
+# launch-bound) and gains the smaller of the two overlapped parts: measured on B200 it loses at 8 MB per tensor
+# (0.150 vs 0.116 ms forward) and wins at 100 MB (0.624 vs 0.660 ms).
+_OVERLAP_MIN_BYTES = 32 << 20
+
+
+def _want_overlap(setting, k):
+    if setting is None:
+        return k.numel() * 2 >= _OVERLAP_MIN_BYTES
+    return bool(setting)
+
 
 class SparseLinearAttention(nn.Module):
     def __init__(self, head_dim, topk, feature_map="softmax", BLKQ=64, BLKK=64, use_bf16=True,
@@ -48,7 +59,8 @@ class SparseLinearAttention(nn.Module):
             raise NotImplementedError(f"Not supported linear scope {linear_scope}.")
         self.linear_scope = linear_scope
         self.impl_flags = ops.FLAG_LINEAR_UNSELECTED if linear_scope == "unselected" else 0
-        self.overlap_linear_state = True   # run the linear-branch state next to the block-mask prediction
+        # run the linear-branch state next to the block-mask prediction: True, False, or None = when it pays
+        self.overlap_linear_state = None
         self.init_weights_()
 
     def init_weights_(self):
@@ -72,7 +84,7 @@ class SparseLinearAttention(nn.Module):
         # a second stream and run next to the (latency-bound) mask prediction; both join before the attention kernel.
         kc, vc = k.to(self.dtype), v.to(self.dtype)
         prep = None
-        if self.overlap_linear_state and self.linear_scope == "all":
+        if _want_overlap(self.overlap_linear_state, k) and self.linear_scope == "all":
             nb = (k.shape[2] + self.BLKK - 1) // self.BLKK
             side = ops.side_stream(q.device)
             prep = ops.prepare_linear(kc, vc, self.proj_l.weight, self.proj_l.bias, ops.topk_count(nb, self.topk),
@@ -103,7 +115,7 @@ class SageSparseLinearAttention(nn.Module):
         if feature_map not in _FEATURES:
             raise NotImplementedError(f"Not supported feature map {feature_map}.")
         self.feature_map = feature_map
-        self.overlap_prepare = True
+        self.overlap_prepare = None        # True, False, or None = when it pays
         self.init_weights_()
 
     def init_weights_(self):
@@ -118,7 +130,7 @@ class SageSparseLinearAttention(nn.Module):
         # quantization pre-passes and linear-branch state on a second stream next to the block-mask prediction
         qc, kc, vc = q.to(self.dtype), k.to(self.dtype), v.to(self.dtype)
         prep = None
-        if self.overlap_prepare:
+        if _want_overlap(self.overlap_prepare, k):
             side = ops.side_stream(q.device)
             with torch.no_grad():
                 prep = ops.sage_prepare(qc, kc, vc, self.proj_l.weight, self.proj_l.bias,

@@ -154,14 +154,17 @@ def test_unselected_scope_vs_oracle(feat, D, BLKQ, L, ratio):
         m(q.cuda().requires_grad_(True), k.cuda(), v.cuda())
 
 
-def test_forward_is_cuda_graph_capturable():
-    """The whole forward (block map, linear state, fused tcgen05 kernel) enqueues on the caller's stream only and
-    never synchronises (the top-k count comes from shapes, utils.py:61-62), so it can be captured into a CUDA
-    graph; the replay must reproduce the eager result bit for bit."""
+@pytest.mark.parametrize("fork", [False, True])
+def test_forward_is_cuda_graph_capturable(fork):
+    """The whole forward (block map, linear state, fused tcgen05 kernel) enqueues on the caller's stream, or on a
+    second stream that forks from it and joins it again (fork=True), and never synchronises (the top-k count comes
+    from shapes, utils.py:61-62), so it can be captured into a CUDA graph; the replay must reproduce the eager
+    result bit for bit."""
     import sla_b200
     g = torch.Generator().manual_seed(11)
     q, k, v = (torch.randn(1, 2, 2048, 128, generator=g).bfloat16().cuda() for _ in range(3))
     m = sla_b200.SparseLinearAttention(128, 0.1).cuda()
+    m.overlap_linear_state = fork
     with torch.no_grad():
         m.proj_l.weight.copy_(torch.randn(128, 128, generator=g) * 0.05)
         eager = m(q, k, v)
@@ -189,6 +192,7 @@ def test_graphed_forward_backward_matches_eager():
     w = torch.randn(128, 128, generator=g) * 0.05
     m_graph = sla_b200.SparseLinearAttention(128, 0.2).cuda()
     m_eager = sla_b200.SparseLinearAttention(128, 0.2).cuda()
+    m_graph.overlap_linear_state = True     # the fork to the second stream is captured too
     with torch.no_grad():
         m_graph.proj_l.weight.copy_(w)
         m_eager.proj_l.weight.copy_(w)
