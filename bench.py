@@ -492,9 +492,11 @@ def main():
     if bwd:
         kernels["sparse_bwd_dq_dkdv"] = {"ms": kb_ms, "tflops": bwd_flops / kb_ms / 1e9}
     # DRAM bytes per launch from the committed ncu captures (profiles/tcgen05_sparse_kernels_c3.md,
-    # profiles/sage_fwd_tc_c4.md): dram__bytes_read.sum + dram__bytes_write.sum; null where not captured
-    traffic_table = {("c3", "sparse_fwd"): 386.1e6, ("c3", "sparse_bwd_dq_dkdv"): 494.8e6 + 588.1e6,
-                     ("c4", "sparse_fwd"): 1.925e9}
+    # profiles/sage_fwd_tc_c4s.md): dram__bytes_read.sum + dram__bytes_write.sum; null where not captured.
+    # The captures are the launches of a whole module step: the forward there also writes o (100 MB at c3) and
+    # the dK/dV kernel also reads dH; the c4 figure is the 8-head capture times 5 (traffic grows with the heads).
+    traffic_table = {("c3", "sparse_fwd"): 471.8e6, ("c3", "sparse_bwd_dq_dkdv"): 592.7e6 + 585.9e6,
+                     ("c4", "sparse_fwd"): 5 * 525.5e6, ("c4s", "sparse_fwd"): 525.5e6}
     if w.quantized:
         # no driver-measured 8-bit peak exists: measure an e4m3 GEMM here with the protocol of the bf16 one
         # (8192^3, best of 10, CUDA events) and quote it beside the bf16 peak
