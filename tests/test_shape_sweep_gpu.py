@@ -21,6 +21,8 @@ CASES = [
     (2, 2, 1025, 128, 128, 0.2,  "elu",     False),   # 9 query tiles, 17 KV blocks, last of each ragged
     (1, 3, 1536, 128, 64,  0.13, "softmax", False),   # topk 3 of 24, three heads
     (1, 1, 2049, 64,  128, 0.08, "softmax", False),   # topk 2 of 33
+    (1, 2, 900,  128, 64,  0.25, "softmax", True),    # fp16 at head dim 128 (tcgen05 linear backward in fp16)
+    (1, 1, 1300, 128, 128, 0.3,  "relu",    True),    # same, relu feature map, three row chunks in the linear passes
 ]
 
 
