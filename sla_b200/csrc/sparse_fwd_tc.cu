@@ -76,6 +76,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __shared__ __align__(8) uint64_t bars[18];
   __shared__ uint32_t s_zp[D / 2];   // z of the linear state, pairs of T
   __shared__ float s_bias[D];
+  __shared__ float s_rden[128];      // 1 / den of the linear branch per tile row
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_n_entries;
   __shared__ int s_abort;
@@ -418,85 +419,85 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tma_store_wait_read();
         }
       } else {
-        // ---- phi(q) of this thread's row, written over the row in the Q tile (core.py:90) ----
-        float dsum = 0.f;        // sum_d round(phi_d * z_d), core.py:95
-        auto emit_phi = [&](int ch, const float (&f)[8]) {
-          uint32_t w[4];
+        // ---- phi(q) over the Q tile in place (core.py:90) and 1 / den per row (core.py:95) ----
+        // Eight threads per row (thread = 16-byte chunk `pc` of every 64-column slab), sixteen rows per pass, eight
+        // passes: the rows of a thread are independent, which hides the latency a one-thread-per-row loop exposes.
+        {
+          const int pc = tid & 7, rg = tid >> 3;
+          uint32_t zz[SLABS][4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            w[i] = Elem<T>::pack2(f[2 * i], f[2 * i + 1]);
-            const float2 pz = Elem<T>::unpack2(Elem<T>::mul2(w[i], s_zp[ch * 4 + i]));   // each product rounded to T
-            dsum += pz.x + pz.y;
-          }
-          st_shared_v4(chunk_addr(sQ, ch), w[0], w[1], w[2], w[3]);
-        };
-        auto load_x = [&](int ch, float (&f)[8]) {
-          uint32_t w0, w1, w2, w3;
-          ld_shared_v4(chunk_addr(sQ, ch), w0, w1, w2, w3);
-          float2 a = Elem<T>::unpack2(w0), b2 = Elem<T>::unpack2(w1), c = Elem<T>::unpack2(w2), d = Elem<T>::unpack2(w3);
-          f[0] = a.x; f[1] = a.y; f[2] = b2.x; f[3] = b2.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
-        };
-        if (p.feature == SLA_PHI_SOFTMAX) {
-          float mx0 = -INFINITY, mx1 = -INFINITY;
+          for (int sl = 0; sl < SLABS; ++sl)
 #pragma unroll
-          for (int ch = 0; ch < D / 8; ++ch) {
-            float f[8];
-            load_x(ch, f);
-            mx0 = fmaxf(mx0, fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])));
-            mx1 = fmaxf(mx1, fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])));
-          }
-          const float mx = fmaxf(mx0, mx1);
-          const float neg_mx = -mx * kLog2e;
-          // exp(x - max) in fp32 is parked in the idle S columns of this thread's TMEM lane
-          float e0 = 0.f, e1 = 0.f;
+            for (int i = 0; i < 4; ++i) zz[sl][i] = s_zp[(sl * 8 + pc) * 4 + i];
+#pragma unroll 4
+          for (int it = 0; it < 8; ++it) {
+            const int r = rg + 16 * it;
+            const uint32_t a0 = sQ + r * 128 + ((pc ^ (r & 7)) << 4);
+            float f[SLABS][8];
 #pragma unroll
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t ev[32];
+            for (int sl = 0; sl < SLABS; ++sl) {
+              uint32_t w0, w1, w2, w3;
+              ld_shared_v4(a0 + sl * Q_SLAB, w0, w1, w2, w3);
+              const float2 a = Elem<T>::unpack2(w0), b2 = Elem<T>::unpack2(w1), c = Elem<T>::unpack2(w2), d = Elem<T>::unpack2(w3);
+              f[sl][0] = a.x; f[sl][1] = a.y; f[sl][2] = b2.x; f[sl][3] = b2.y;
+              f[sl][4] = c.x; f[sl][5] = c.y; f[sl][6] = d.x; f[sl][7] = d.y;
+            }
+            if (p.feature == SLA_PHI_SOFTMAX) {
+              float mx = -INFINITY;
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              float f[8];
-              load_x((c0 >> 3) + q4, f);
+              for (int sl = 0; sl < SLABS; ++sl)
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float e = ex2(fmaf(f[i], kLog2e, neg_mx));
-                if (i & 1) e1 += e; else e0 += e;
-                ev[q4 * 8 + i] = __float_as_uint(e);
+                for (int i = 0; i < 8; ++i) mx = fmaxf(mx, f[sl][i]);
+#pragma unroll
+              for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+              const float neg_mx = -mx * kLog2e;
+              float es = 0.f;
+#pragma unroll
+              for (int sl = 0; sl < SLABS; ++sl)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  f[sl][i] = ex2(fmaf(f[sl][i], kLog2e, neg_mx));
+                  es += f[sl][i];
+                }
+#pragma unroll
+              for (int o = 1; o < 8; o <<= 1) es += __shfl_xor_sync(0xffffffffu, es, o);
+              const float inv_s = 1.f / es;
+#pragma unroll
+              for (int sl = 0; sl < SLABS; ++sl)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[sl][i] *= inv_s;
+            } else {
+#pragma unroll
+              for (int sl = 0; sl < SLABS; ++sl)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float x = f[sl][i];
+                  if (p.feature == SLA_PHI_RELU) f[sl][i] = fmaxf(x, 0.f);
+                  else f[sl][i] = x > 0.f ? x + 1.f : __expf(x);      // elu(x) + 1
+                }
+            }
+            float dsum = 0.f;        // sum_d round(phi_d * z_d), core.py:95
+#pragma unroll
+            for (int sl = 0; sl < SLABS; ++sl) {
+              uint32_t w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                w[i] = Elem<T>::pack2(f[sl][2 * i], f[sl][2 * i + 1]);
+                const float2 pz = Elem<T>::unpack2(Elem<T>::mul2(w[i], zz[sl][i]));   // each product rounded to T
+                dsum += pz.x + pz.y;
               }
+              st_shared_v4(a0 + sl * Q_SLAB, w[0], w[1], w[2], w[3]);
             }
-            tmem_st_x32(tmem + lane_addr + COL_S + c0, ev);
-          }
-          tmem_wait_st();
-          const float inv_s = 1.f / (e0 + e1);
 #pragma unroll
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t ev[32];
-            tmem_ld_x32(tmem + lane_addr + COL_S + c0, ev);
-            tmem_wait_ld();
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              float f[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(ev[q4 * 8 + i]) * inv_s;
-              emit_phi((c0 >> 3) + q4, f);
-            }
-          }
-        } else {
-#pragma unroll
-          for (int ch = 0; ch < D / 8; ++ch) {
-            float f[8];
-            load_x(ch, f);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              if (p.feature == SLA_PHI_RELU) f[i] = fmaxf(f[i], 0.f);
-              else f[i] = f[i] > 0.f ? f[i] + 1.f : __expf(f[i]);      // elu(x) + 1
-            }
-            emit_phi(ch, f);
+            for (int o = 1; o < 8; o <<= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, o);
+            if (pc == 0) s_rden[r] = 1.f / round_to<T>(1e-5f + round_to<T>(dsum));
           }
         }
-        const float rden = 1.f / round_to<T>(1e-5f + round_to<T>(dsum));
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(BAR(B_PHI));
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");     // s_rden of this thread's row was written by another thread
+        const float rden = s_rden[row];
         // ---- while the read-out GEMM runs: the sparse branch's own output, staged in the idle V stages ----
         if (p.store_os) {
 #pragma unroll
