@@ -1,9 +1,8 @@
 """Generate the golden fixtures in this directory from the reference implementation itself.
 
-Run once, in a container that has the reference checkout (default path below, override with
-SLA_REFERENCE_DIR):
+Run once, in a container that has a checkout of the reference (thu-ml/SLA); SLA_REFERENCE_DIR names it:
 
-    python tests/golden/make_golden.py
+    SLA_REFERENCE_DIR=<path to the reference checkout> python tests/golden/make_golden.py
 
 The reference (thu-ml/SLA) only has Triton GPU kernels. They are executed here, unmodified, on
 the CPU through Triton's interpreter (TRITON_INTERPRET=1). Two things outside the reference are
@@ -22,7 +21,9 @@ import os
 import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
-REF = os.environ.get("SLA_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("SLA_REFERENCE_DIR")
+if not REF or not os.path.isdir(REF):
+    sys.exit("set SLA_REFERENCE_DIR to a checkout of the reference (thu-ml/SLA)")
 sys.path.insert(0, REF)
 
 import numpy as np
