@@ -9,12 +9,17 @@ printed by rank 0. `value` is the dense-attention-equivalent TFLOP/s of the refe
 formula (evaluate/bench_kernel.py:93-99: 4*B*H*L^2*D per forward, x3.5 for forward+backward), summed
 over all ranks; ms per step, the sparse-actual TFLOP/s and the forward-only figures are extra keys.
 
-N > 1: launched under torchrun, one rank per GPU. Rank r owns batch element r of a global batch of N
-(each batch element = the workload's H heads): (batch x head) sharding with no collective on the
-attention path, so per-GPU work is fixed ("scaling": "weak").
+N > 1: launched under torchrun, one rank per GPU, no collective on the attention path. Two splits are timed:
+* `value` ("scaling": "weak"): rank r owns batch element r of a global batch of N, each batch element being the
+  workload's B*H (batch, head) units, so per-GPU work is fixed;
+* `strong`: the workload's own B*H units are sharded over the ranks (`sharding.unit_range`: c3 12 -> 6/3/{2,1},
+  c5 16 -> 8/4/2, c4 40 -> 20/10/5), the total work is fixed. Per-unit checksums of o, dq, dk, dv of the sharded
+  run are compared on rank 0 with those of the same units in its unsharded run: every unit must give the same
+  bits however the units are split. `--gather` also times the optional NCCL all-gather of o.
 
 --impl reference times the CPU restatement of the reference's algorithm (oracle/) on the host cores,
-rank 0 only, each step a bounded sample (one head) of the same workload.
+rank 0 only, each step a bounded sample (one head) of the same workload. That arm never imports the product
+package or loads its shared library.
 """
 from __future__ import annotations
 
@@ -133,8 +138,31 @@ def cpu_reference_step(w, sample, backward=True):
     return time.perf_counter() - t0
 
 
+def load_synthetic():
+    """The workload generator, loaded by file path: the CPU arm must not import the product package (whose
+    __init__ loads libsla_b200.so)."""
+    import importlib.util
+    name = "sla_b200_synthetic_standalone"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "sla_b200", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def bench_config(w, world, impl="default"):
+    """The `config` object both arms print (same keys, same values for the same command line)."""
+    tensor_mb = w.B * w.H * w.L * w.D * 2 / 1e6
+    return {"workload": w.name, "B_per_gpu": w.B, "H": w.H, "L": w.L, "D": w.D, "BLKQ": w.BLKQ, "BLKK": w.BLKK,
+            "topk": w.topk, "topk_blocks": w.topk_blocks, "feature_map": w.feature,
+            "global_units": world * w.units, "parallelism": f"bh-shard x{world}",
+            "l2": "inputs larger than L2 (q,k,v,dO,o,dq,dk,dv = %.0f MB)" % (8 * tensor_mb), "impl": impl}
+
+
 def cpu_sample(w):
-    from sla_b200 import synthetic
+    synthetic = load_synthetic()
     q, k, v, do = synthetic.make_inputs(w, "cpu", units=[0])
     W, b = synthetic.make_proj(w, "cpu")
     return q, k, v, do, W, b
@@ -155,20 +183,22 @@ def run_reference_arm(args, w, rank):
         return
     cores = _use_all_host_threads()
     sample = cpu_sample(w)
-    for _ in range(min(args.warmup, 1)):
-        cpu_reference_step(w, sample)
-    ts = [cpu_reference_step(w, sample) for _ in range(args.steps)]
+    bwd = w.backward and not w.quantized
+    for _ in range(args.warmup):
+        cpu_reference_step(w, sample, bwd)
+    ts = [cpu_reference_step(w, sample, bwd) for _ in range(args.steps)]
     sec = sum(ts) / len(ts)
-    flops_unit = w.dense_equiv_flops(True) / w.units
+    flops_unit = w.dense_equiv_flops(bwd) / w.units
     val = flops_unit / sec / 1e12
+    what = "forward+backward" if bwd else "forward"
     line = {
-        "impl": "reference", "metric": "sla_fwd_bwd_dense_equiv_tflops", "value": val, "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3,
+        "impl": "reference", "metric": "sla_fwd_bwd_dense_equiv_tflops" if bwd else "sla_fwd_dense_equiv_tflops",
+        "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "B": w.B, "H": w.H, "L": w.L, "D": w.D, "BLKQ": w.BLKQ, "BLKK": w.BLKK,
-                   "topk": w.topk, "feature_map": w.feature},
+        "config": bench_config(w, int(os.environ.get("WORLD_SIZE", "1"))),
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                         "sample": f"1 of {w.units} (batch,head) units, forward+backward incl. block map, per step"},
+                         "sample": f"1 of {w.units} (batch,head) units, {what} incl. block map, per step"},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -268,6 +298,9 @@ def main():
     ap.add_argument("--single-stream", action="store_true",
                     help="keep every launch on one stream (the modules otherwise run the linear-branch state and "
                          "the quantization pre-passes on a second stream next to the block map)")
+    ap.add_argument("--gather", action="store_true",
+                    help="N > 1: also time the optional NCCL all-gather of the sharded run's output")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the 2 s sustained-clock loop (N = 1)")
     ap.add_argument("--topk", type=float, default=None, help="override the workload's top-k ratio (c5 sweeps 0.05/0.1/0.2)")
     args = ap.parse_args()
 
@@ -275,18 +308,20 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
-    from sla_b200 import synthetic
-    w = synthetic.WORKLOADS[args.workload]
-    if args.topk is not None:
-        w = dataclasses.replace(w, topk=args.topk)
-
     if args.impl == "reference":
+        synthetic = load_synthetic()
+        w = synthetic.WORKLOADS[args.workload]
+        if args.topk is not None:
+            w = dataclasses.replace(w, topk=args.topk)
         run_reference_arm(args, w, rank)
         return
 
     import torch.distributed as dist
     import sla_b200
-    from sla_b200 import _lib, ops
+    from sla_b200 import _lib, ops, sharding, synthetic
+    w = synthetic.WORKLOADS[args.workload]
+    if args.topk is not None:
+        w = dataclasses.replace(w, topk=args.topk)
 
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path for the product)"
     torch.cuda.set_device(local_rank)
@@ -377,6 +412,85 @@ def main():
         t = torch.tensor([fwd_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         fwd_ms = float(t.item())
+
+    # ---- sustained: the same step for at least 2 s, with the SM clock sampled over that loop (N = 1) ----
+    sustained = None
+    if world == 1 and not args.no_sustained:
+        n_sus = max(args.steps, int(2200.0 / ms) + 1)
+        s2 = ClockSampler(local_rank)
+        s2.start()
+        torch.cuda.synchronize()
+        s2.mark_begin()
+        sus_ms = timed(step_fwdbwd, n_sus, 0, torch.cuda.synchronize)
+        s2.mark_end()
+        c2 = s2.stop()
+        check_device("the sustained loop")
+        sustained = {"ms_per_step": sus_ms, "steps": n_sus, "seconds": sus_ms * n_sus / 1e3,
+                     "value": w.dense_equiv_flops(bwd) / sus_ms / 1e9, "unit": "TFLOP/s", "clocks": c2}
+
+    # ---- strong scaling: the workload's own B*H units sharded over the ranks ----
+    def unit_checksums(ts):
+        """Exact per-unit checksums (two int64 sums over the raw 16-bit patterns) of tensors shaped (1, U, L, D)."""
+        out = []
+        for t in ts:
+            x = t.detach().reshape(t.shape[0] * t.shape[1], -1).view(torch.int16).to(torch.int64)
+            wgt = (torch.arange(x.shape[1], device=x.device, dtype=torch.int64) % 8191) + 1
+            out.append(torch.stack([x.sum(dim=1), (x * wgt).sum(dim=1)], dim=1))
+        return torch.stack(out, dim=1)          # (U, n_tensors, 2)
+
+    def run_units(mq, mk, mv, mdo):
+        """One forward(+backward) step over the given units; returns the tensors whose bits are compared."""
+        if not bwd:
+            with torch.no_grad():
+                return (m(mq, mk, mv),)
+        a, b_, c = (t.detach().requires_grad_(True) for t in (mq, mk, mv))
+        o = m(a, b_, c)
+        o.backward(mdo)
+        m.proj_l.weight.grad = m.proj_l.bias.grad = None
+        return (o.detach(), a.grad, b_.grad, c.grad)
+
+    strong = {"ms_per_step": ms, "units_per_rank": [w.units], "speedup": 1.0, "efficiency": 1.0,
+              "granularity_bound": 1.0, "checksums_equal": None}
+    if world > 1:
+        counts = sharding.unit_counts(w.units, world)
+        lo, hi = sharding.unit_range(w.units, rank, world)
+        flat = lambda t: t.reshape(1, w.units, w.L, w.D)
+        ref_sums = unit_checksums(run_units(*(flat(t) for t in (q, k, v, do)))) if rank == 0 else None
+        if hi > lo:
+            sq, sk, sv, sdo = synthetic.make_inputs(w, dev, units=list(range(lo, hi)))
+            mine = run_units(sq, sk, sv, sdo)
+            my_sums = unit_checksums(mine)
+            strong_ms = timed(lambda: run_units(sq, sk, sv, sdo), args.steps, max(3, args.warmup), sync)
+        else:                                   # more ranks than units: this rank idles through the same barriers
+            mine, my_sums = None, torch.zeros((0, 4 if bwd else 1, 2), dtype=torch.int64, device=dev)
+            strong_ms = timed(lambda: None, args.steps, max(3, args.warmup), sync)
+        check_device("the sharded run")
+        t = torch.tensor([strong_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        strong_ms = float(t.item())
+        gathered = [None] * world
+        dist.all_gather_object(gathered, my_sums.cpu())
+        equal = None
+        if rank == 0:
+            equal = bool(torch.equal(torch.cat(gathered, dim=0), ref_sums.cpu()))
+        bound = w.units / max(counts)
+        strong = {"ms_per_step": strong_ms, "units_per_rank": counts, "speedup": ms / strong_ms,
+                  "efficiency": ms / strong_ms / world, "granularity_bound": bound,
+                  "efficiency_vs_granularity_bound": ms / strong_ms / bound,
+                  "value": w.dense_equiv_flops(bwd) / strong_ms / 1e9, "unit": "TFLOP/s",
+                  "checksums_equal": equal,
+                  "checksums": "per-unit int64 sums over the bits of " + ("o, dq, dk, dv" if bwd else "o") +
+                               ", sharded run vs rank 0's unsharded run of the same units",
+                  "baseline": "speedup = this run's replica ms_per_step (all units on every GPU) / sharded ms_per_step"}
+        if args.gather:
+            o_local = mine[0][0] if mine is not None else torch.zeros((0, w.L, w.D), dtype=q.dtype, device=dev)
+            sharding.all_gather_units(o_local, w.units)
+            g_ms = timed(lambda: sharding.all_gather_units(o_local, w.units), args.steps, 3, sync)
+            t = torch.tensor([g_ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            strong["gather_ms"] = float(t.item())
+            strong["gather_bytes_per_rank"] = w.units * w.L * w.D * 2
+        del mine
 
     # ---- end to end through the module API with HOST buffers ----
     hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, do))
@@ -512,6 +626,17 @@ def main():
         except Exception as e:  # noqa: BLE001
             peaks["e4m3_tflops"] = None
             print(f"# e4m3 peak not measured: {type(e).__name__}: {e}"[:200], file=sys.stderr)
+        try:        # the INT8 half of the kernel's GEMM work: s8 x s8 -> s32, same size and protocol
+            n = 8192
+            ai = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8)
+            bi = torch.randint(-127, 128, (n, n), device=dev, dtype=torch.int8).t()
+            mmi = lambda: torch._int_mm(ai, bi)
+            best = min(timed(mmi, 1, 1, sync) for _ in range(10))
+            peaks["int8_tops"] = 2.0 * n ** 3 / best / 1e9
+            del ai, bi
+        except Exception as e:  # noqa: BLE001
+            peaks["int8_tops"] = None
+            print(f"# int8 peak not measured: {type(e).__name__}: {e}"[:200], file=sys.stderr)
     dom = "sparse_bwd_dq_dkdv" if kb_ms >= kf_ms else "sparse_fwd"
     achieved = kernels[dom]["tflops"]
     roofline = {"kernel": dom, "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
@@ -520,23 +645,28 @@ def main():
                 "peak_source": peaks["source"] + " burst (kernel timed alone)",
                 "algorithmic_flops_per_launch": bwd_flops if dom != "sparse_fwd" else fwd_flops}
     if w.quantized:
-        roofline["peak_8bit_tflops_measured_here"] = peaks.get("e4m3_tflops")
-        roofline["note"] = ("frac is quoted against the bf16 peak; half of this kernel's GEMM work runs as INT8, half as "
-                            "e4m3, and the kernel is bound by the SFU (ex2) rate, not by the tensor pipe")
+        # half of the kernel's GEMM work is INT8 (S = Q K^T), half e4m3 (P V): the denominator is the rate at which a
+        # kernel doing both halves at their library-GEMM peaks would run (harmonic mean of the two measured peaks)
+        e4, i8 = peaks.get("e4m3_tflops"), peaks.get("int8_tops")
+        roofline["peak_e4m3_tflops_measured_here"] = e4
+        roofline["peak_int8_tops_measured_here"] = i8
+        roofline["frac_of_bf16_peak"] = roofline["frac"]
+        if e4 and i8:
+            p8 = 2.0 / (1.0 / e4 + 1.0 / i8)
+            roofline.update({"peak": p8, "frac": achieved / p8,
+                             "peak_source": "harmonic mean of the e4m3 and INT8 GEMM peaks measured in this run "
+                                            "(torch._scaled_mm / torch._int_mm, 8192^3, best of 10)"})
+        roofline["note"] = ("half of this kernel's GEMM work runs as INT8, half as e4m3; the kernel is bound by the "
+                            "SFU (ex2) rate, not by the tensor pipe")
 
     dense_fb = w.dense_equiv_flops(bwd)
-    n_units_total = world * w.units
     value = world * dense_fb / ms / 1e9
     line = {
         "metric": "sla_fwd_bwd_dense_equiv_tflops" if bwd else "sla_fwd_dense_equiv_tflops", "value": value,
         "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8/e4m3" if w.quantized else "bf16", "data": "synthetic",
-        "config": {"workload": w.name, "B_per_gpu": w.B, "H": w.H, "L": w.L, "D": w.D, "BLKQ": w.BLKQ,
-                   "BLKK": w.BLKK, "topk": w.topk, "topk_blocks": w.topk_blocks, "feature_map": w.feature,
-                   "global_units": n_units_total, "parallelism": f"bh-shard x{world}",
-                   "l2": "inputs larger than L2 (q,k,v,dO,o,dq,dk,dv = %.0f MB)" % (8 * tensor_bytes / 1e6),
-                   "impl": "mma.sync" if args.legacy_mma else "default"},
+        "config": bench_config(w, world, "mma.sync" if args.legacy_mma else "default"),
         "fwd_ms": fwd_ms, "fwd_bwd_ms": ms,
         "fwd_dense_equiv_tflops": world * w.dense_equiv_flops(False) / fwd_ms / 1e9,
         "sparse_actual_tflops": world * (w.sparse_flops(bwd) + w.linear_flops(bwd)) / ms / 1e9,
@@ -548,6 +678,7 @@ def main():
                 "h2d_bytes_per_step": (4 if bwd else 3) * tensor_bytes,
                 "d2h_bytes_per_step": (4 if bwd else 1) * tensor_bytes},
         "gpu_launches": int(launches), "clocks": clocks, "kernels": kernels, "roofline": roofline,
+        "strong": strong, "sustained": sustained,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         _use_all_host_threads()

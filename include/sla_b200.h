@@ -64,6 +64,10 @@ enum sla_flags {
                                     that block did NOT select (the scope drawn in assets/overview_of_SLA.png)
                                     instead of over all tokens (core.py:92-96). Forward only: sla_bwd returns
                                     SLA_ERR_UNSUPPORTED with this flag. */
+  SLA_FLAG_LINEAR_ONLY = 16,     /* sla_bwd only: differentiate the linear branch and proj_l alone, the sparse branch
+                                    being a constant of the graph (the quantized forward of SageSLA/core.py:114-146
+                                    has no backward; core.py:148-158 after it is ordinary autograd). o_s, lse, lut and
+                                    the column lists are not read and may be NULL. */
   SLA_FLAG_STATE_READY = 8       /* sla_fwd / sage_sla_fwd only: sla_fwd_prepare / sage_sla_prepare has already run
                                     for this shape on the same inputs, lin_state and workspace (and has completed,
                                     or is ordered before this call on the stream) */
@@ -84,14 +88,30 @@ SLA_API const char* sla_status_string(int status);
 /* Text of the last CUDA runtime error seen by the calling thread inside this library. */
 SLA_API const char* sla_last_cuda_error(void);
 /* The tcgen05 kernels bound every device-side wait; when one runs out the kernel records a code in
- * a device word and stops working. This call synchronises the device, returns the code (0 = none) in
- * *code and optionally clears it. */
+ * a device word and stops working: that launch and every later tcgen05 launch on the device leave their
+ * outputs unwritten until the word is cleared. This call synchronises the device, stores the code
+ * (0 = none) in *code, optionally clears it, and returns SLA_ERR_TIMEOUT when the code is non-zero.
+ * Poll it where the host synchronises anyway (once per step). */
 SLA_API int sla_poll_device_error(int* code, int clear);
+/* Diagnostic: the limit of every device-side wait on the current device, in nanoseconds (default 2 s;
+ * 0 restores the default). A synchronous copy to the device. */
+SLA_API int sla_debug_set_wait_limit_ns(unsigned long long ns);
+/* Test hook for the time-out path: while set, the first CTA of the tcgen05 forward never requests its first
+ * K tile, so its waits run out, it records a code and leaves through the same teardown as a real time-out
+ * (shared-memory copies drained, tensor memory freed). Nothing faults; clear it and the error word afterwards. */
+SLA_API int sla_debug_drop_first_k_tile(int on);
 /* Diagnostic: give the backward tcgen05 kernels a device buffer of 2 x 1024 int64 into which the
  * first CTA of each kernel records SM-clock timestamps of its pipeline events; NULL switches it off. */
 SLA_API int sla_debug_set_trace(void* device_buffer);
 /* Diagnostic: number of kernels this library has launched in the process so far. */
 SLA_API long long sla_launch_count(void);
+
+/* Which kernels serve `op` (SLA_OP_FWD, SLA_OP_BWD, SLA_OP_SPARSE_BWD, SLA_OP_SAGE_FWD) for `shape`: 0 = the
+ * tcgen05 kernels, 1 = the mma.sync kernels (asked for with SLA_FLAG_LEGACY_MMA, or taken automatically when a
+ * tile's block list does not fit the tcgen05 kernels' shared memory: forward top-k above about 8,000 at D = 128;
+ * backward M_BLOCKS above 1,536 or top-k above 2,100 at D = 128, M_BLOCKS above 5,500 at D = 64), or a negative
+ * sla_status. No counterpart in the reference, which has one set of kernels. */
+SLA_API int sla_kernel_path(const sla_shape* shape, int op);
 
 /* Replaces sparse_linear_attention/utils.py:61-62: min(n_blocks, int(topk_ratio * n_blocks)). */
 SLA_API int sla_topk_count(int n_blocks, double topk_ratio);

@@ -14,11 +14,11 @@ LIB_PATH = os.path.join(_HERE, "libsla_b200.so")
 SLA_BF16, SLA_FP16, SLA_FP32 = 0, 1, 2
 PHI = {"softmax": 0, "relu": 1, "elu": 2}
 OP_BLOCK_MAP, OP_FWD, OP_BWD, OP_LINEAR_STATE, OP_SAGE_FWD, OP_SPARSE_BWD = 0, 1, 2, 3, 4, 5
-FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA, FLAG_LINEAR_UNSELECTED, FLAG_STATE_READY = 1, 2, 4, 8
+FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA, FLAG_LINEAR_UNSELECTED, FLAG_STATE_READY, FLAG_LINEAR_ONLY = 1, 2, 4, 8, 16
 
 # every symbol include/sla_b200.h declares
 EXPORTS = (
-    "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_debug_set_trace", "sla_topk_count", "sla_workspace_bytes",
+    "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_debug_set_trace", "sla_debug_set_wait_limit_ns", "sla_debug_drop_first_k_tile", "sla_topk_count", "sla_workspace_bytes", "sla_kernel_path",
     "sla_block_map", "sla_column_lists", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_linear_state_static", "sla_fwd", "sla_fwd_prepare", "sla_bwd",
     "sage_sla_fwd", "sage_sla_prepare",
 )
@@ -53,10 +53,16 @@ def _load() -> C.CDLL:
     lib.sla_launch_count.restype = C.c_longlong
     lib.sla_debug_set_trace.restype = C.c_int
     lib.sla_debug_set_trace.argtypes = [C.c_void_p]
+    lib.sla_debug_set_wait_limit_ns.restype = C.c_int
+    lib.sla_debug_set_wait_limit_ns.argtypes = [C.c_ulonglong]
+    lib.sla_debug_drop_first_k_tile.restype = C.c_int
+    lib.sla_debug_drop_first_k_tile.argtypes = [C.c_int]
     lib.sla_poll_device_error.restype = C.c_int
     lib.sla_poll_device_error.argtypes = [C.POINTER(C.c_int), C.c_int]
     lib.sla_topk_count.restype = C.c_int
     lib.sla_topk_count.argtypes = [C.c_int, C.c_double]
+    lib.sla_kernel_path.restype = C.c_int
+    lib.sla_kernel_path.argtypes = [sp, C.c_int]
     lib.sla_workspace_bytes.restype = C.c_size_t
     lib.sla_workspace_bytes.argtypes = [sp, C.c_int]
     lib.sla_block_map.restype = C.c_int
@@ -102,8 +108,18 @@ def check(status: int) -> None:
 def poll_device_error(clear: bool = True) -> int:
     """Synchronise and return the device error code of the tcgen05 kernels (0 = none)."""
     code = C.c_int(0)
-    check(lib.sla_poll_device_error(C.byref(code), 1 if clear else 0))
+    rc = lib.sla_poll_device_error(C.byref(code), 1 if clear else 0)
+    if rc not in (0, -8):          # -8 = SLA_ERR_TIMEOUT: the code says which wait
+        check(rc)
     return code.value
+
+
+def raise_on_device_error() -> None:
+    """Synchronise, and raise if a bounded device-side wait ran out since the last poll (the word is cleared)."""
+    code = poll_device_error(clear=True)
+    if code != 0:
+        raise SlaError(-8, f"a device-side wait of a tcgen05 kernel ran out (code {code}); the outputs of that "
+                           "launch and of every tcgen05 launch after it are not valid")
 
 
 def topk_count(n_blocks: int, ratio: float) -> int:

@@ -139,9 +139,8 @@ class SageSparseLinearAttention(nn.Module):
         bm = ops.block_map(q, k, self.topk, 128, 64)
         if prep is not None:
             torch.cuda.current_stream(q.device).wait_stream(side)
-        q, k, v = qc, kc, vc
-        with torch.no_grad():
-            o = ops.sage_sla_attention(q, k, v, self.proj_l.weight, self.proj_l.bias, bm, self.feature_map, prep=prep)
+        # differentiable through the linear branch and proj_l only (SageSLA/core.py:148-158), like the reference
+        o = ops.sage_sla_attention(qc, kc, vc, self.proj_l.weight, self.proj_l.bias, bm, self.feature_map, prep=prep)
         o = o.to(dtype)
         if return_sparsity:
             return o, bm.topk / bm.n_blocks

@@ -204,8 +204,10 @@ __global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
   uint32_t kreg[kKeyRegs];
 #pragma unroll
   for (int i = 0; i < kKeyRegs; ++i) kreg[i] = lane + 32 * i < nb ? kr[lane + 32 * i] : 0u;
-  // Scores were rounded to TIn: their keys have kLowZero low bits clear, and no candidate with one of those bits
-  // set can be the k-th largest key.
+  // Scores were rounded to TIn, so the kLowZero low bits of a score's fp32 pattern are clear. order_key() keeps
+  // them clear for a non-negative score and turns them all into ones for a negative one (it complements the
+  // pattern). Keys that agree above bit kLowZero have the same sign, hence the same low bits: the search only
+  // has to decide the high bits, and the low bits follow from the sign of what it found.
   constexpr int kLowZero = std::is_same<TIn, __nv_bfloat16>::value ? 16 : (std::is_same<TIn, __half>::value ? 13 : 0);
   uint32_t prefix = 0;
   for (int bit = 31; bit >= kLowZero; --bit) {
@@ -219,6 +221,7 @@ __global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
     for (int j = lane + 32 * kKeyRegs; j < nb; j += 32) c0 += kr[j] >= cand ? 1 : 0;
     if (__reduce_add_sync(0xffffffffu, c0 + c1) >= topk) prefix = cand;
   }
+  if (kLowZero > 0 && !(prefix & 0x80000000u)) prefix |= (1u << kLowZero) - 1u;   // k-th score is negative
   int above = 0;
 #pragma unroll
   for (int i = 0; i < kKeyRegs; ++i) above += kreg[i] > prefix ? 1 : 0;
@@ -239,6 +242,10 @@ __global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
     int eq_rank = eq_seen + __popc(be & lt_mask);
     bool sel = gt || (eq && eq_rank < need);
     uint32_t bs = __ballot_sync(0xffffffffu, sel);
+    // a row never emits more than topk entries, whatever the scores are (NaNs included): the LUT row, the 0/1
+    // map and the column counts are sized for exactly topk
+    sel = sel && n_out + __popc(bs & lt_mask) < topk;
+    bs = __ballot_sync(0xffffffffu, sel);
     if (sel) {
       out[n_out + __popc(bs & lt_mask)] = j;
       if (cols) atomicAdd(&cols[j + 1], 1);

@@ -3,6 +3,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tc_common.cuh"
 #include "workspace.h"
 
 using namespace sla;
@@ -32,6 +33,16 @@ FwdParams make_fwd(const sla_shape* s, const void* q, const void* k, const void*
   return p;
 }
 
+// Sparse forward (with the fused linear read-out when `lin`): the tcgen05 kernel, or the mma.sync kernel when the
+// caller asks for it or when the entry list of a query tile does not fit the tcgen05 kernel's shared memory.
+int run_sparse_fwd(const sla_shape* s, const FwdParams& p, bool lin, cudaStream_t st) {
+  if (!(s->flags & SLA_FLAG_LEGACY_MMA)) {
+    int rc = run_sparse_fwd_tc(s, p, st);
+    if (rc != SLA_ERR_BAD_SHAPE) return rc;
+  }
+  return run_sparse_fwd_mma(s, p, lin, st);
+}
+
 }  // namespace
 
 extern "C" {
@@ -43,8 +54,20 @@ int sla_sparse_fwd(const sla_shape* s, const void* q, const void* k, const void*
   if (rc != SLA_OK) return rc;
   if (!all_aligned({q, k, v, o_s})) return SLA_ERR_BAD_ALIGN;
   FwdParams p = make_fwd(s, q, k, v, lut, o_s, nullptr, lse, nullptr, nullptr);
-  if (s->flags & SLA_FLAG_LEGACY_MMA) return run_sparse_fwd_mma(s, p, false, static_cast<cudaStream_t>(stream));
-  return run_sparse_fwd_tc(s, p, static_cast<cudaStream_t>(stream));
+  return run_sparse_fwd(s, p, false, static_cast<cudaStream_t>(stream));
+}
+
+int sla_kernel_path(const sla_shape* s, int op) {
+  int rc = validate_shape(s);
+  if (rc != SLA_OK) return rc;
+  const bool legacy = (s->flags & SLA_FLAG_LEGACY_MMA) != 0;
+  switch (op) {
+    case SLA_OP_FWD: return (legacy || !sparse_fwd_tc_fits(s)) ? 1 : 0;
+    case SLA_OP_BWD:
+    case SLA_OP_SPARSE_BWD: return (legacy || !sparse_bwd_tc_fits(s)) ? 1 : 0;
+    case SLA_OP_SAGE_FWD: return 0;
+    default: return SLA_ERR_UNSUPPORTED;
+  }
 }
 
 int sla_debug_set_trace(void* device_buffer) {
@@ -54,7 +77,21 @@ int sla_debug_set_trace(void* device_buffer) {
 
 int sla_poll_device_error(int* code, int clear) {
   if (!code) return SLA_ERR_NULL;
-  return read_tc_error(code, clear != 0);
+  int rc = read_tc_error(code, clear != 0);
+  if (rc != SLA_OK) return rc;
+  return *code != 0 ? SLA_ERR_TIMEOUT : SLA_OK;
+}
+
+int sla_debug_set_wait_limit_ns(unsigned long long ns) {
+  int rc = check_device_arch();
+  if (rc != SLA_OK) return rc;
+  return set_tc_wait_limit(ns == 0 ? tc::kDefaultWaitLimitNs : ns);
+}
+
+int sla_debug_drop_first_k_tile(int on) {
+  int rc = check_device_arch();
+  if (rc != SLA_OK) return rc;
+  return set_tc_drop_first_k_tile(on != 0 ? 1 : 0);
 }
 
 int sla_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, void* ws,
@@ -108,7 +145,7 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   const bool legacy = (s->flags & SLA_FLAG_LEGACY_MMA) != 0;
   if (s->flags & SLA_FLAG_SPARSE_ONLY) {
     FwdParams p = make_fwd(s, q, k, v, lut, o, nullptr, lse, nullptr, nullptr);
-    return legacy ? run_sparse_fwd_mma(s, p, false, st) : run_sparse_fwd_tc(s, p, st);
+    return run_sparse_fwd(s, p, false, st);
   }
   if (!w || !lin_state || !ws) return SLA_ERR_NULL;
   WsLinearState wl = ws_linear_state(s);
@@ -134,6 +171,7 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
     void* os_buf = o_s ? o_s : o;
     FwdParams ps = make_fwd(s, q, k, v, lut, os_buf, nullptr, lse, nullptr, nullptr);
     rc = run_sparse_fwd_tc(s, ps, st);
+    if (rc == SLA_ERR_BAD_SHAPE) return SLA_ERR_UNSUPPORTED;   // this scope has no mma.sync path
     if (rc != SLA_OK) return rc;
     rc = run_feature_map(s, q, ub + wu.phiq, st);
     if (rc != SLA_OK) return rc;
@@ -147,9 +185,8 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
     FwdParams pr = make_fwd(s, ub + wu.phiq, k, v, lut, o, os_buf, lse, lin_state, wbits);
     return run_linear_readout_unselected(s, pr, ub + wu.cnum, reinterpret_cast<const float*>(ub + wu.cden), st);
   }
-  if (legacy) return run_sparse_fwd_mma(s, p, true, st);
-  // tcgen05 sparse branch with the linear read-out, proj_l and the final sum fused into its epilogue
-  return run_sparse_fwd_tc(s, p, st);
+  // sparse branch with the linear read-out, proj_l and the final sum fused into its epilogue
+  return run_sparse_fwd(s, p, true, st);
 }
 
 static int sparse_bwd_impl(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s,
@@ -190,11 +227,13 @@ int sla_bwd(const sla_shape* s, const void* q, const void* k, const void* v, con
             const void* d_o, const int32_t* lut, const int32_t* col_offsets, const int32_t* col_index,
             const float* w, const void* lin_state, void* dq, void* dk, void* dv, float* dw, float* dbias,
             void* ws, size_t ws_bytes, sla_stream_t stream) {
-  if (!q || !k || !v || !o_s || !lse || !d_o || !lut || !col_offsets || !col_index || !dq || !dk || !dv || !ws)
-    return SLA_ERR_NULL;
+  const bool linear_only = s && (s->flags & SLA_FLAG_LINEAR_ONLY) != 0;
+  if (!q || !k || !v || !d_o || !dq || !dk || !dv || !ws) return SLA_ERR_NULL;
+  if (!linear_only && (!o_s || !lse || !lut || !col_offsets || !col_index)) return SLA_ERR_NULL;
   int rc = check_common(s);
   if (rc != SLA_OK) return rc;
   if (!all_aligned({q, k, v, o_s, d_o, dq, dk, dv, lin_state, ws})) return SLA_ERR_BAD_ALIGN;
+  if (linear_only && (s->flags & SLA_FLAG_SPARSE_ONLY)) return SLA_ERR_UNSUPPORTED;
   WsBwd wb = ws_bwd(s);
   if (ws_bytes < wb.total + ws_sparse_bwd(s).total) return SLA_ERR_WS_TOO_SMALL;
   unsigned char* base = static_cast<unsigned char*>(ws);
@@ -219,12 +258,12 @@ int sla_bwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   // Linear branch first (plain stores), then the sparse kernels add their part: the tcgen05 dQ kernel through TMA
   // reduce-add stores, the mma.sync kernels by reading the tile back. With the tcgen05 kernels the linear
   // branch's dk, dv are not a pass of their own: the dK/dV kernel computes them in its epilogue from dH and dz.
-  const bool fuse_kv = !legacy && sparse_bwd_tc_fits(s);
+  const bool fuse_kv = !linear_only && !legacy && sparse_bwd_tc_fits(s);
   lp.accumulate = 0;
   lp.skip_kv = fuse_kv ? 1 : 0;
   lp.tc_pass_a = legacy ? 0 : 1;
   rc = run_linear_bwd(s, lp, st);
-  if (rc != SLA_OK) return rc;
+  if (rc != SLA_OK || linear_only) return rc;
   return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 1, st,
                          fuse_kv ? lp.dh : nullptr, fuse_kv ? lp.dz : nullptr);
 }

@@ -67,6 +67,8 @@ void set_trace_buffer(long long* p);
 long long* trace_buffer();
 int run_sparse_bwd_tc(const sla_shape* s, const BwdParams& p, void* stats, cudaStream_t st);
 bool sparse_bwd_tc_fits(const sla_shape* s);
+bool sparse_bwd_dq_pair_fits(const sla_shape* s);
+bool sparse_fwd_tc_fits(const sla_shape* s);
 int run_sparse_bwd_dq_pair(const sla_shape* s, const BwdParams& p, const void* stats, int Lpad, cudaStream_t st);
 int run_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, float* partial,
                      int nch, int rows, cudaStream_t st);

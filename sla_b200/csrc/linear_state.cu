@@ -5,6 +5,8 @@
 //
 // Stage 1: a CTA reduces a chunk of rows into an fp32 partial (scratch memory, one slot per chunk).
 // Stage 2: partials are summed in a fixed order -> deterministic results.
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -215,19 +217,19 @@ static __device__ __align__(256) float g_state_scratch[kStaticScratchFloats];
 // In host code `g_state_scratch` is only a handle, not an address a kernel could use: the device
 // address is looked up once per device (with that device current) and cached.
 static float* static_scratch_for_current_device(int* status) {
-  static float* ptrs[64] = {nullptr};
+  static std::atomic<float*> ptrs[64];     // several host threads may make the first call on a device
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) { set_last_cuda_error(e); *status = SLA_ERR_CUDA; return nullptr; }
   if (dev < 0 || dev >= 64) { *status = SLA_ERR_UNSUPPORTED; return nullptr; }
-  if (ptrs[dev] == nullptr) {
-    float* ptr = nullptr;
+  float* ptr = ptrs[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_state_scratch);
     if (e != cudaSuccess) { set_last_cuda_error(e); *status = SLA_ERR_CUDA; return nullptr; }
-    ptrs[dev] = ptr;
+    ptrs[dev].store(ptr, std::memory_order_release);
   }
   *status = SLA_OK;
-  return ptrs[dev];
+  return ptr;
 }
 
 int run_linear_state_static(const sla_shape* s, const void* k, const void* v, void* lin_state, cudaStream_t st) {

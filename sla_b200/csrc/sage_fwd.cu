@@ -193,16 +193,16 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int r = 0; r < NSLAB; ++r)
               for (int c = 0; c < NSLAB; ++c)
                 tma_load_3d(sHW + r * HW_STAGE + c * HW_SLAB, &tmHW, BAR(B_HW), c * 64, r * 64, bh);
-            if (*abortp) mbar_wait(BAR(B_HW), 0, kSErrDrain, p.err);
+            if (*abortp) mbar_wait_drain(BAR(B_HW), 0, p.err);
           }
-          if (!ring_free || *abortp) mbar_wait(BAR(B_Q16), 0, kSErrDrain, p.err);
+          if (!ring_free || *abortp) mbar_wait_drain(BAR(B_Q16), 0, p.err);
         }
         if (!ring_free) *abortp = 1;
       }
       if (*abortp) {
-        mbar_wait(BAR(B_Q), 0, kSErrDrain, p.err);
-        for (int j = max(0, issued_k - NS); j < issued_k; ++j) mbar_wait(BAR(B_K + j % NS), (j / NS) & 1, kSErrDrain, p.err);
-        for (int j = max(0, issued_v - NS); j < issued_v; ++j) mbar_wait(BAR(B_V + j % NS), (j / NS) & 1, kSErrDrain, p.err);
+        mbar_wait_drain(BAR(B_Q), 0, p.err);
+        for (int j = max(0, issued_k - NS); j < issued_k; ++j) mbar_wait_drain(BAR(B_K + j % NS), (j / NS) & 1, p.err);
+        for (int j = max(0, issued_v - NS); j < issued_v; ++j) mbar_wait_drain(BAR(B_V + j % NS), (j / NS) & 1, p.err);
       }
     }
   } else if (warp == 5) {
@@ -690,7 +690,8 @@ static int run_sage_main_typed(const sla_shape* s, const void* q, const int32_t*
   p.scale_log2 = softmax_scale(s) * kLog2e;
   auto kern = tc::sage_fwd_tc_kernel<T, D>;
   const int smem = 1024 + 2 * 128 * 128 + 2 * 4 * 64 * 128 + s->topk * 8 + 16;
-  if (smem > 113 * 1024) return SLA_ERR_BAD_TOPK;
+  // up to 113 KB two CTAs share an SM, a longer list takes the SM alone; beyond 227 KB there is no quantized path
+  if (smem + 2048 > 227 * 1024) return SLA_ERR_UNSUPPORTED;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   kern<<<dim3(mb, bh), 192, smem, st>>>(tq, tk, tv, to, tq16, thw, p);
   SLA_LAUNCH_OK();

@@ -206,9 +206,9 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         issued = pi + 1;
       }
       if (*abortp) {
-        mbar_wait(BAR(B_X), 0, kQErrDrain, p.err);
-        for (int j = max(0, issued - NK); j < issued; ++j) mbar_wait(BAR(B_KF + j % NK), (j / NK) & 1, kQErrDrain, p.err);
-        for (int j = max(0, issued - NV); j < issued; ++j) mbar_wait(BAR(B_VF + j % NV), (j / NV) & 1, kQErrDrain, p.err);
+        mbar_wait_drain(BAR(B_X), 0, p.err);
+        for (int j = max(0, issued - NK); j < issued; ++j) mbar_wait_drain(BAR(B_KF + j % NK), (j / NK) & 1, p.err);
+        for (int j = max(0, issued - NV); j < issued; ++j) mbar_wait_drain(BAR(B_VF + j % NV), (j / NV) & 1, p.err);
       }
     }
   } else if (warp == 17) {
@@ -405,11 +405,16 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
 
 }  // namespace tc
 
+static int dq_pair_smem_bytes(int D, int topk) { return 1024 + 6 * 128 * D * 2 + (4 * topk + 4) * 4 + 16; }
+constexpr int kDqStaticSmem = 1024;   // statically allocated shared memory of the kernel (barriers)
+
+bool sparse_bwd_dq_pair_fits(const sla_shape* s) { return dq_pair_smem_bytes(s->D, s->topk) + kDqStaticSmem <= 227 * 1024; }
+
 template <typename T, int D, int BM>
 static int launch_dq_pair(const sla_shape* s, const BwdParams& bp, const float2* stats, int Lpad, cudaStream_t st) {
   const int bh = s->B * s->H;
-  const int smem = 1024 + 6 * 128 * D * 2 + (4 * bp.topk + 4) * 4 + 16;
-  if (smem > 227 * 1024) return SLA_ERR_BAD_SHAPE;
+  const int smem = dq_pair_smem_bytes(D, bp.topk);
+  if (!sparse_bwd_dq_pair_fits(s)) return SLA_ERR_BAD_SHAPE;
   CUtensorMap tq, tdo, tk, tv, tdq;
   int rc;
   if ((rc = make_tmap_3d(&tq, bp.q, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;

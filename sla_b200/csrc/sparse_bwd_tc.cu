@@ -1,17 +1,13 @@
-// Backward of the block-sparse branch on tcgen05 / TMEM / TMA (mathematics:
-// sparse_linear_attention/kernel.py:85-237).
+// dK and dV of the block-sparse branch on tcgen05 / TMEM / TMA (mathematics:
+// sparse_linear_attention/kernel.py:167-237), the row statistics both backward kernels read
+// (kernel.py:85-105), and the host entry of the tcgen05 backward. dQ is sparse_bwd_dq_tc.cu.
 //
-// One kernel template, two instantiations:
-//   KVS = false  "dQ":    a CTA owns a 128-row query tile (Q, dO stationary in shared memory) and
-//                         streams the selected K_j, V_j blocks.   T1 = Q K_j^T, T2 = dO V_j^T,
-//                         dS = P * (T2 - delta),  dQ += dS K_j.
-//   KVS = true   "dK/dV": a CTA owns a 128-key tile (two adjacent KV blocks; K, V stationary) and
-//                         streams 64-row slices Q_i, dO_i of the query blocks that selected either
-//                         block.                 T1 = K Q_i^T, T2 = V dO_i^T (transposed scores),
-//                         dV += P^T dO_i,  dK += dS^T Q_i.
-// As in the forward, a 128-row tile that spans two 64-row blocks walks the UNION of the two blocks'
-// (ascending) lists; two mask bits per entry say which half selected it and the other half
-// contributes zeros, so all MMAs run at M = 128 while the mask stays 64 x 64.
+// A CTA owns a 128-key tile (two adjacent KV blocks; K, V stationary in shared memory) and streams
+// 64-row slices Q_i, dO_i of the query blocks that selected either block:
+//   T1 = K Q_i^T,  T2 = V dO_i^T (transposed scores),  dV += P^T dO_i,  dK += dS^T Q_i.
+// As in the forward, the tile walks the UNION of the two blocks' (ascending) column lists; two mask
+// bits per entry say which half selected it and the other half contributes zeros, so all MMAs run at
+// M = 128 while the mask stays 64 x 64.
 //
 // Roles (576 threads, one CTA per SM):
 //   warps 0-15  four compute groups of 128 threads (thread = tile row = TMEM lane). Group g works on
@@ -20,7 +16,7 @@
 //               cross-column state) and writes them back as 16-bit A operands over its own columns.
 //   warp 16     TMA producer (stationary tiles once, then a ring of streamed tiles + row stats)
 //   warp 17     MMA issuer.
-// TMEM: acc1 [0,D) (dQ or dK), acc2 [D,2D) (dV, KVS only), then per buffer T1 (64 cols), T2 (64 cols).
+// TMEM: acc1 [0,D) (dK), acc2 [D,2D) (dV), then per buffer T1 (64 cols), T2 (64 cols).
 // Row statistics (lse, delta) come from a padded (B*H, Lpad, 2) fp32 array written by a small
 // preprocessing kernel (delta = rowsum(o_s * dO), kernel.py:102-105; padding rows hold lse = +inf).
 // All waits are bounded; see tc_common.cuh.
@@ -34,15 +30,15 @@ namespace sla {
 namespace tc {
 
 struct TcBwdParams {
-  const int32_t* list;       // dQ: lut (B*H, mb, topk)          KVS: col_index (B*H, mb*topk)
-  const int32_t* offsets;    // dQ: unused                        KVS: col_offsets (B*H, nb+1)
+  const int32_t* list;       // col_index (B*H, mb*topk)
+  const int32_t* offsets;    // col_offsets (B*H, nb+1)
   const float2* stats;       // (B*H, Lpad) {lse, delta}
   int* err;
   long long* trace;          // optional timeline of CTA (0,0): [role 0..3][entry < 64][4 events], SM clock cycles
   int L, Lpad, mb, nb, topk, max_entries;
-  int accumulate;            // add the result to what dq / dk / dv already hold (the linear branch's part)
+  int accumulate;            // add the result to what dk / dv already hold (the linear branch's part)
   float scale, scale_log2;
-  // dK/dV variant only: the linear branch's dk, dv computed in the epilogue (feature < 0: not fused)
+  // the linear branch's dk, dv computed in the epilogue (feature < 0: not fused)
   int lin_feature;           // sla_feature or -1
   const float* dz;           // [BH][D] fp32 gradient of z = sum phi(k)
 };
@@ -65,9 +61,9 @@ __device__ __forceinline__ void trace_ev(long long* tr, int role, int j, int ev)
 enum : int { kBErrX = 201, kBErrYFull = 202, kBErrYEmpty = 203, kBErrTFull = 204, kBErrCFull = 205,
              kBErrAcc = 206, kBErrDrain = 207, kBErrDh = 208, kBErrPhi = 209, kBErrLin = 210 };
 
-template <typename T, int D, int BM, bool KVS>
+template <typename T, int D, int BM>
 __global__ void __launch_bounds__(576, 1)
-sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
+sparse_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                      const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
                      const __grid_constant__ CUtensorMap tmO1, const __grid_constant__ CUtensorMap tmO2,
                      const __grid_constant__ CUtensorMap tmDH, TcBwdParams p) {
@@ -76,20 +72,17 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   constexpr int X_BYTES = SLABS * X_SLAB, Y_BYTES = SLABS * Y_SLAB;
   constexpr int NS = D == 128 ? 4 : 6;                       // ring stages
   constexpr int STAT_BYTES = 64 * 8;
-  constexpr int SL = KVS ? BM / 64 : 1;                      // 64-row slices per list entry
+  constexpr int SL = BM / 64;                                // 64-row slices per list entry (a query block)
   constexpr int FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   constexpr uint32_t IDESC_T = idesc_f16(FMT, 128, 64, 0, 0);
   constexpr uint32_t IDESC_ACC = idesc_f16(FMT, 128, D, 0, 1);
   constexpr uint32_t TMEM_COLS = 512;
-  // dQ variant: the stationary Q and dO tiles are also copied into TMEM (16-bit, D/2 columns each) so
-  // that the score GEMMs read their A operand from tensor memory instead of re-reading 4 KB of shared
-  // memory per k-step.
-  constexpr int COL_ACC1 = 0, COL_ACC2 = D, COL_X1 = D, COL_X2 = D + D / 2, COL_T = 2 * D;
+  constexpr int COL_ACC1 = 0, COL_ACC2 = D, COL_T = 2 * D;
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * NS + 10];
-  __shared__ float s_dz[KVS ? D : 1];              // fused linear backward: gradient of z
-  __shared__ float s_e[KVS ? 3 : 1][4][128];       // row-wide maxima / sums handed between the four compute groups
+  __shared__ float s_dz[D];                        // fused linear backward: gradient of z
+  __shared__ float s_e[3][4][128];                 // row-wide maxima / sums handed between the four compute groups
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_n_entries;
   __shared__ int s_abort;
@@ -110,10 +103,10 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
   // 0 x_full | 1..NS y_full | NS+1..2NS y_empty | then t_full[2], c_full[2], acc_done
-  constexpr int B_X = 0, B_YF = 1, B_YE = 1 + NS, B_T = 1 + 2 * NS, B_C = 3 + 2 * NS, B_ACC = 5 + 2 * NS, B_XT = 6 + 2 * NS;
-  // fused linear dk, dv (dK/dV variant): dH landed in stage 0 | phi(k) written over the K tile | the two GEMMs done
+  constexpr int B_X = 0, B_YF = 1, B_YE = 1 + NS, B_T = 1 + 2 * NS, B_C = 3 + 2 * NS, B_ACC = 5 + 2 * NS;
+  // fused linear dk, dv: dH landed in stage 0 | phi(k) written over the K tile | the two GEMMs done
   constexpr int B_DH = 7 + 2 * NS, B_PHIK = 8 + 2 * NS, B_LIN = 9 + 2 * NS;
-  const bool lin = KVS && p.lin_feature >= 0;
+  const bool lin = p.lin_feature >= 0;
 
   if (warp == 16 && lane == 0) {
     // the producer lane sets the barriers up itself and requests the stationary tiles before it merges the lists
@@ -128,7 +121,6 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       mbar_init(BAR(B_C + b), 8);      // one arrival per warp of the buffer's two compute groups
     }
     mbar_init(BAR(B_ACC), 1);
-    mbar_init(BAR(B_XT), 16);
     mbar_init(BAR(B_DH), 1);
     mbar_init(BAR(B_PHIK), 16);
     mbar_init(BAR(B_LIN), 1);
@@ -151,14 +143,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     // source lists are copied to shared memory with coalesced loads before the serial merge.
     const int32_t *ga, *gb;
     int na, nb2;
-    if (!KVS) {
-      if (BM == 128) {
-        ga = p.list + (static_cast<size_t>(bh) * p.mb + tile) * p.topk; na = p.topk; gb = ga; nb2 = 0;
-      } else {
-        ga = p.list + (static_cast<size_t>(bh) * p.mb + 2 * tile) * p.topk; na = p.topk;
-        gb = ga + p.topk; nb2 = 2 * tile + 1 < p.mb ? p.topk : 0;
-      }
-    } else {
+    {
       const int32_t* off = p.offsets + static_cast<size_t>(bh) * (p.nb + 1);
       const int32_t* ci = p.list + static_cast<size_t>(bh) * p.mb * p.topk;
       const int j0 = 2 * tile;
@@ -171,21 +156,14 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     for (int i = lane; i < na; i += 32) ra[i] = ga[i];
     for (int i = lane; i < nb2; i += 32) rb[i] = gb[i];
     __syncwarp();
-    int n;
-    if (!KVS && BM == 128) {
-      for (int i = lane; i < na; i += 32) ulist[i] = ra[i] | (3 << 28);
-      n = na;
-      __syncwarp();
-    } else {
-      n = warp_union_lists(ra, na, rb, nb2, ulist, 1 << 28, 2 << 28, lane);
-    }
+    const int n = warp_union_lists(ra, na, rb, nb2, ulist, 1 << 28, 2 << 28, lane);
     if (lane == 0) s_n_entries = n;
   }
   if (warp == 17) {
     tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
-  if (KVS && p.lin_feature >= 0 && tid < D) s_dz[tid] = p.dz[static_cast<size_t>(bh) * D + tid];
+  if (lin && tid < D) s_dz[tid] = p.dz[static_cast<size_t>(bh) * D + tid];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -197,7 +175,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
   // global row of the streamed tile j
   auto y_row0 = [&](int j) {
     const int e = ulist[j / SL] & 0x0fffffff;
-    return KVS ? e * BM + (j % SL) * 64 : e * 64;
+    return e * BM + (j % SL) * 64;
   };
 
   if (warp == 16) {
@@ -211,14 +189,13 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         trace_ev(tr, 0, j, 0);
         const int row0 = y_row0(j);
         const uint32_t y1 = sY0 + s * 2 * Y_BYTES, y2 = y1 + Y_BYTES;
-        mbar_expect_tx(BAR(B_YF + s), 2 * Y_BYTES + (KVS ? STAT_BYTES : 0));
+        mbar_expect_tx(BAR(B_YF + s), 2 * Y_BYTES + STAT_BYTES);
         for (int c = 0; c < SLABS; ++c) {
           tma_load_3d(y1 + c * Y_SLAB, &tmY1, BAR(B_YF + s), c * 64, row0, bh);
           tma_load_3d(y2 + c * Y_SLAB, &tmY2, BAR(B_YF + s), c * 64, row0, bh);
         }
-        if (KVS)
-          bulk_load_1d(sStat0 + s * STAT_BYTES, p.stats + static_cast<size_t>(bh) * p.Lpad + row0, STAT_BYTES,
-                       BAR(B_YF + s));
+        bulk_load_1d(sStat0 + s * STAT_BYTES, p.stats + static_cast<size_t>(bh) * p.Lpad + row0, STAT_BYTES,
+                     BAR(B_YF + s));
         issued = j + 1;
       }
       if (lin && !*abortp) {
@@ -231,12 +208,12 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
           for (int r = 0; r < D / 64; ++r)
             for (int c = 0; c < SLABS; ++c)
               tma_load_3d(sY0 + c * (D * 128) + r * (64 * 128), &tmDH, BAR(B_DH), c * 64, r * 64, bh);
-          if (*abortp) mbar_wait(BAR(B_DH), 0, kBErrDrain, p.err);
+          if (*abortp) mbar_wait_drain(BAR(B_DH), 0, p.err);
         }
       }
       if (*abortp) {
-        mbar_wait(BAR(B_X), 0, kBErrDrain, p.err);
-        for (int j = max(0, issued - NS); j < issued; ++j) mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrDrain, p.err);
+        mbar_wait_drain(BAR(B_X), 0, p.err);
+        for (int j = max(0, issued - NS); j < issued; ++j) mbar_wait_drain(BAR(B_YF + j % NS), (j / NS) & 1, p.err);
       }
     }
   } else if (warp == 17) {
@@ -253,24 +230,18 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t yo = ((kk >> 2) * Y_SLAB + (kk & 3) * 32) >> 4;
-            if (KVS) mma_ss(t1, x1_lo + (((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4), y1_lo + yo, IDESC_T, kk > 0 ? 1u : 0u);
-            else mma_ts(t1, tmem + COL_X1 + kk * 8, y1_lo + yo, IDESC_T, kk > 0 ? 1u : 0u);
+            mma_ss(t1, x1_lo + (((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4), y1_lo + yo, IDESC_T, kk > 0 ? 1u : 0u);
           }
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t yo = ((kk >> 2) * Y_SLAB + (kk & 3) * 32) >> 4;
-            if (KVS) mma_ss(t2, x2_lo + (((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4), y2_lo + yo, IDESC_T, kk > 0 ? 1u : 0u);
-            else mma_ts(t2, tmem + COL_X2 + kk * 8, y2_lo + yo, IDESC_T, kk > 0 ? 1u : 0u);
+            mma_ss(t2, x2_lo + (((kk >> 2) * X_SLAB + (kk & 3) * 32) >> 4), y2_lo + yo, IDESC_T, kk > 0 ? 1u : 0u);
           }
           tc_commit(BAR(B_T + b));
         }
         __syncwarp();
       };
       bool ok = warp_all(mbar_wait(BAR(B_X), 0, kBErrX, p.err));
-      if (ok && !KVS) {
-        ok = warp_all(mbar_wait(BAR(B_XT), 0, kBErrX, p.err));   // Q, dO copied to tensor memory by the compute groups
-        tc_fence_after();
-      }
       for (int j = 0; ok && j < 2 && j < n_ent; ++j) {
         ok = warp_all(mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrYFull, p.err));
         if (!ok) break;
@@ -294,12 +265,8 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
             // 16-bit operand columns: elements [0,32) packed at +0..15, elements [32,64) at +32..47
             const uint32_t ao = (kk >> 1) * 32 + (kk & 1) * 8;
             const uint32_t ko = (kk * 2048) >> 4;
-            if (KVS) {
-              mma_ts(tmem + COL_ACC2, a1 + ao, y2_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dV += P^T dO_i  (kernel.py:220)
-              mma_ts(tmem + COL_ACC1, a2 + ao, y1_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dK += dS^T Q_i (kernel.py:225)
-            } else {
-              mma_ts(tmem + COL_ACC1, a2 + ao, y1_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dQ += dS K_j   (kernel.py:163)
-            }
+            mma_ts(tmem + COL_ACC2, a1 + ao, y2_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dV += P^T dO_i  (kernel.py:220)
+            mma_ts(tmem + COL_ACC1, a2 + ao, y1_lo + ko, IDESC_ACC, kk > 0 ? 1u : acc_on);   // dK += dS^T Q_i (kernel.py:225)
           }
           tc_commit(BAR(B_YE + s));
         }
@@ -354,47 +321,20 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int half = row >> 6;
     const float sc = p.scale_log2;
-    const int grow = tile * 128 + row;                      // global query row (dQ) or key row (KVS)
-    float my_lse = INFINITY, my_delta = 0.f;
-    if (!KVS) {
-      float2 st = p.stats[static_cast<size_t>(bh) * p.Lpad + min(grow, p.Lpad - 1)];
-      if (grow < L) { my_lse = st.x; my_delta = st.y; }
-    }
-    const bool key_ok = grow < L;                           // KVS: keys past the end give P = 0 (kernel.py:216)
+    const int grow = tile * 128 + row;                      // global key row
+    const bool key_ok = grow < L;                           // keys past the end give P = 0 (kernel.py:216)
     bool ok = !*abortp;
-    if (!KVS && ok) {
-      // stationary tiles -> TMEM: groups 0,1 copy the two column halves of Q, groups 2,3 those of dO
-      ok = mbar_wait(BAR(B_X), 0, kBErrX, p.err);
-      if (ok) {
-        constexpr int NCH = D / 16;                           // 16-byte chunks per thread (D/2 elements)
-        const uint32_t src = ((wg >> 1) ? sX2 : sX1) + (((wg & 1) * (D / 2)) >> 6) * X_SLAB + row * 128;
-        const int chunk0 = (((wg & 1) * (D / 2)) & 63) >> 3;
-        uint32_t xr[NCH * 4];
-#pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          const uint32_t addr = src + (((chunk0 + c) ^ (row & 7)) << 4);
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n"
-                       : "=r"(xr[4 * c]), "=r"(xr[4 * c + 1]), "=r"(xr[4 * c + 2]), "=r"(xr[4 * c + 3]) : "r"(addr));
-        }
-        const uint32_t dst = tmem + lane_addr + ((wg >> 1) ? COL_X2 : COL_X1) + (wg & 1) * (D / 4);
-        if constexpr (NCH * 4 == 32) tmem_st_x32(dst, xr); else tmem_st_x16(dst, xr);
-        tmem_wait_st();
-        tc_fence_before();
-      }
-      mbar_arrive_warp(BAR(B_XT), lane);
-    }
     for (int j = buf; ok && j < n_ent; j += 2) {
       long long* trc = ((warp & 3) == 0 && lane == 0) ? tr : nullptr;
       trace_ev(trc, 2 + ch, j, 0);
       if (!mbar_wait(BAR(B_T + buf), (j >> 1) & 1, kBErrTFull, p.err)) { ok = false; break; }
       if (*abortp) { ok = false; break; }
       trace_ev(trc, 2 + ch, j, 1);
-      if (KVS && !mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrYFull, p.err)) { ok = false; break; }  // row stats landed
+      if (!mbar_wait(BAR(B_YF + j % NS), (j / NS) & 1, kBErrYFull, p.err)) { ok = false; break; }  // row stats landed
       tc_fence_after();
       const int entry = ulist[j / SL];
-      const bool active = (!KVS && BM == 128) || ((entry >> (28 + half)) & 1);
+      const bool active = (entry >> (28 + half)) & 1;
       const uint32_t t1 = tmem + lane_addr + COL_T + buf * 128 + ch * 32, t2 = t1 + 64;
-      const int valid = KVS ? 64 : L - (entry & 0x0fffffff) * 64;   // dQ: keys of this block that exist
       const float4* stc = reinterpret_cast<const float4*>(stat_p + (j % NS) * 64 + ch * 32);
       uint32_t pp[16], ds[16];
       if (active) {
@@ -405,16 +345,11 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
         trace_ev(trc, 2 + ch, j, 2);
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float lse0, del0, lse1, del1;
-          if (KVS) { float4 st = stc[c >> 1]; lse0 = st.x; del0 = st.y; lse1 = st.z; del1 = st.w; }
-          else { lse0 = lse1 = my_lse; del0 = del1 = my_delta; }
+          const float4 st = stc[c >> 1];                                    // {lse, delta} of two query rows
+          const float lse0 = st.x, del0 = st.y, lse1 = st.z, del1 = st.w;
           float p0 = ex2b(__uint_as_float(sv[c]) * sc - lse0);
           float p1 = ex2b(__uint_as_float(sv[c + 1]) * sc - lse1);
-          if (KVS) { if (!key_ok) p0 = p1 = 0.f; }                         // kernel.py:216
-          else if (valid < 64) {                                            // kernel.py:157
-            if (ch * 32 + c >= valid) p0 = 0.f;
-            if (ch * 32 + c + 1 >= valid) p1 = 0.f;
-          }
+          if (!key_ok) p0 = p1 = 0.f;                                       // kernel.py:216
           pp[c >> 1] = Elem<T>::pack2(p0, p1);
           ds[c >> 1] = Elem<T>::pack2(p0 * (__uint_as_float(dv[c]) - del0),
                                       p1 * (__uint_as_float(dv[c + 1]) - del1));   // kernel.py:161 / :224
@@ -423,7 +358,7 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
 #pragma unroll
         for (int c = 0; c < 16; ++c) pp[c] = ds[c] = 0u;
       }
-      if (KVS) tmem_st_x16(t1, pp);
+      tmem_st_x16(t1, pp);
       tmem_st_x16(t2, ds);
       tmem_wait_st();
       tc_fence_before();
@@ -563,13 +498,13 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       } else {
       // accumulators -> T, staged over the (idle) stationary tiles in the swizzled slab layout, then
       // TMA stores; rows past the end of the sequence are clipped by the copy engine.
-      // dQ: group g converts columns [g D/4, +D/4) of acc1. KVS: groups 0,1 halves of acc1 (dK), 2,3 of acc2 (dV).
-      const bool second = KVS && wg >= 2;
-      const int span = KVS ? D / 2 : D / 4;
-      const int c_lo = (KVS ? (wg & 1) : wg) * span, c_hi = c_lo + span;
+      // groups 0,1 convert the two column halves of acc1 (dK), groups 2,3 those of acc2 (dV)
+      const bool second = wg >= 2;
+      const int span = D / 2;
+      const int c_lo = (wg & 1) * span, c_hi = c_lo + span;
       const uint32_t acc = tmem + lane_addr + (second ? COL_ACC2 : COL_ACC1);
       const uint32_t stage = second ? sX2 : sX1;
-      const float mul = second ? 1.0f : p.scale;   // dQ, dK carry the softmax scale (kernel.py:164,236)
+      const float mul = second ? 1.0f : p.scale;   // dK carries the softmax scale (kernel.py:236)
       for (int c0 = c_lo; c0 < c_hi; c0 += 16) {
         uint32_t ov[16];
         if (n_ent > 0) {
@@ -597,12 +532,10 @@ sparse_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_cons
       if (tid == 0) {
         if (p.accumulate) {   // read-modify-write done by the copy engine in L2: no load stalls this CTA
           for (int c = 0; c < SLABS; ++c) tma_reduce_add_3d(&tmO1, sX1 + c * X_SLAB, c * 64, tile * 128, bh);
-          if (KVS)
-            for (int c = 0; c < SLABS; ++c) tma_reduce_add_3d(&tmO2, sX2 + c * X_SLAB, c * 64, tile * 128, bh);
+          for (int c = 0; c < SLABS; ++c) tma_reduce_add_3d(&tmO2, sX2 + c * X_SLAB, c * 64, tile * 128, bh);
         } else {
           for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO1, sX1 + c * X_SLAB, c * 64, tile * 128, bh);
-          if (KVS)
-            for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO2, sX2 + c * X_SLAB, c * 64, tile * 128, bh);
+          for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO2, sX2 + c * X_SLAB, c * 64, tile * 128, bh);
         }
         tma_store_commit();
         tma_store_wait_read();
@@ -680,41 +613,37 @@ static int bwd_tc_smem_bytes(int D, int max_entries) {
 }
 constexpr int kBwdStaticSmem = 8 * 1024;   // statically allocated shared memory of the kernels (barriers, exchange slots)
 
-template <typename T, int D, int BM, bool KVS>
-static int launch_bwd_tc(const sla_shape* s, const BwdParams& bp, const float2* stats, int Lpad, cudaStream_t st) {
+template <typename T, int D, int BM>
+static int launch_dkdv(const sla_shape* s, const BwdParams& bp, const float2* stats, int Lpad, cudaStream_t st) {
   const int bh = s->B * s->H;
   CUtensorMap x1, x2, y1, y2, o1, o2, dh;
   int rc;
-  const void *X1 = KVS ? bp.k : bp.q, *X2 = KVS ? bp.v : bp.d_o, *Y1 = KVS ? bp.q : bp.k, *Y2 = KVS ? bp.d_o : bp.v;
-  void *O1 = KVS ? bp.dk : bp.dq, *O2 = KVS ? bp.dv : bp.dq;
-  if ((rc = make_tmap_3d(&x1, X1, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
-  if ((rc = make_tmap_3d(&x2, X2, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
-  if ((rc = make_tmap_3d(&y1, Y1, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
-  if ((rc = make_tmap_3d(&y2, Y2, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
-  if ((rc = make_tmap_3d(&o1, O1, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
-  if ((rc = make_tmap_3d(&o2, O2, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
-  const bool lin = KVS && bp.lin_dh != nullptr;
+  if ((rc = make_tmap_3d(&x1, bp.k, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&x2, bp.v, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&y1, bp.q, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&y2, bp.d_o, s->dtype, D, s->L, bh, 64)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&o1, bp.dk, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  if ((rc = make_tmap_3d(&o2, bp.dv, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
+  const bool lin = bp.lin_dh != nullptr;
   dh = o1;
   if (lin && (rc = make_tmap_rows(&dh, bp.lin_dh, s->dtype, D, D, bh, size_t(D) * D * 2, 64)) != SLA_OK) return rc;
   tc::TcBwdParams p;
-  p.list = KVS ? bp.col_index : bp.lut;
+  p.list = bp.col_index;
   p.offsets = bp.col_offsets;
   p.stats = stats;
   p.err = tc_error_word();
   if (p.err == nullptr) return SLA_ERR_CUDA;
-  p.trace = g_trace_buffer ? g_trace_buffer + (KVS ? 1024 : 0) : nullptr;
+  p.trace = g_trace_buffer ? g_trace_buffer + 1024 : nullptr;
   p.L = s->L; p.Lpad = Lpad; p.mb = bp.mb; p.nb = bp.nb; p.topk = bp.topk;
   p.scale = bp.scale; p.scale_log2 = bp.scale_log2; p.accumulate = bp.accumulate;
   p.lin_feature = lin ? s->feature_map : -1;
   p.dz = bp.lin_dz;
-  const int max_entries = KVS ? 2 * bp.mb : 2 * bp.topk;
-  p.max_entries = max_entries;
-  const int smem = bwd_tc_smem_bytes(D, max_entries);
+  p.max_entries = 2 * bp.mb;            // a KV block may have been selected by every query block
+  const int smem = bwd_tc_smem_bytes(D, p.max_entries);
   if (smem + kBwdStaticSmem > 227 * 1024) return SLA_ERR_BAD_SHAPE;
-  auto kern = tc::sparse_bwd_tc_kernel<T, D, BM, KVS>;
+  auto kern = tc::sparse_bwd_dkdv_kernel<T, D, BM>;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  const int tiles = KVS ? ceil_div(bp.nb, 2) : ceil_div(s->L, 128);
-  kern<<<dim3(tiles, bh), 576, smem, st>>>(x1, x2, y1, y2, o1, o2, dh, p);
+  kern<<<dim3(ceil_div(bp.nb, 2), bh), 576, smem, st>>>(x1, x2, y1, y2, o1, o2, dh, p);
   SLA_LAUNCH_OK();
   return SLA_OK;
 }
@@ -727,20 +656,17 @@ static int run_bwd_tc_typed(const sla_shape* s, const BwdParams& bp, float2* sta
   bwd_prep_kernel<T, D><<<dim3(ceil_div(Lpad, 64), bh), 256, 0, st>>>(
       static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L, Lpad);
   SLA_LAUNCH_OK();
-  // dQ: the kernel that takes list entries in pairs (sparse_bwd_dq_tc.cu); this file's dQ variant only when
-  // that one's shared-memory need does not fit
   int rc = run_sparse_bwd_dq_pair(s, bp, stats, Lpad, st);
-  if (rc == SLA_ERR_BAD_SHAPE) rc = launch_bwd_tc<T, D, BM, false>(s, bp, stats, Lpad, st);
   if (rc != SLA_OK) return rc;
-  return launch_bwd_tc<T, D, BM, true>(s, bp, stats, Lpad, st);
+  return launch_dkdv<T, D, BM>(s, bp, stats, Lpad, st);
 }
 
 // Whether the tcgen05 backward kernels fit this shape (so that a caller can decide what to fuse into them before
-// it launches anything).
+// it launches anything): the dK/dV kernel keeps a column-list union of up to 2 * M_BLOCKS entries in shared
+// memory, the dQ kernel one of up to 2 * topk.
 bool sparse_bwd_tc_fits(const sla_shape* s) {
   const int mb = ceil_div(s->L, s->BLKQ);
-  return bwd_tc_smem_bytes(s->D, 2 * mb) + kBwdStaticSmem <= 227 * 1024 &&
-         bwd_tc_smem_bytes(s->D, 2 * s->topk) + kBwdStaticSmem <= 227 * 1024;
+  return bwd_tc_smem_bytes(s->D, 2 * mb) + kBwdStaticSmem <= 227 * 1024 && sparse_bwd_dq_pair_fits(s);
 }
 
 // `stats` must hold B*H*Lpad float2 with Lpad = ceil(L/128)*128.

@@ -20,6 +20,8 @@
 //
 // Every wait on an mbarrier is bounded; on expiry the CTA records a code in a device error word,
 // stops issuing work, and leaves through the common teardown (TMEM is freed).
+#include <atomic>
+#include <cstddef>
 #include <type_traits>
 
 #include "common.cuh"
@@ -174,8 +176,11 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // K tiles run one entry ahead of V tiles: a K stage is free as soon as S_j has been computed,
       // a V stage only after P_j V_j.
       int issued_k = 0, issued_v = 0;
+      // test hook: with the control block's drop_first_k_tile set, CTA (0,0) never requests its first K tile, so the
+      // waits behind it run out and the CTA leaves through the abort path
+      const bool drop_k0 = tile == 0 && bh == 0 && reinterpret_cast<volatile TcControl*>(p.err)->drop_first_k_tile != 0;
       for (int t = 0; t <= n_ent; ++t) {
-        if (t < n_ent) {
+        if (t < n_ent && !(drop_k0 && t == 0)) {
           const int s = t & 1;
           if (t >= 2 && !mbar_wait(BAR(B_KE + s), ((t >> 1) - 1) & 1, kErrEmpty, p.err)) { *abortp = 1; break; }
           if (*abortp) break;
@@ -205,14 +210,15 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int r = 0; r < D / 64; ++r)
             for (int c = 0; c < SLABS; ++c)
               tma_load_3d(sK0 + r * KV_BYTES + c * KV_SLAB, &tmHW, BAR(B_HW), c * 64, r * 64, bh);
-          if (*abortp) mbar_wait(BAR(B_HW), 0, kErrDrain, p.err);
+          if (*abortp) mbar_wait_drain(BAR(B_HW), 0, p.err);
         }
       }
       if (*abortp) {
         // let the copies already in flight land before the CTA's shared memory goes away
-        mbar_wait(BAR(B_Q), 0, kErrDrain, p.err);
-        for (int j = max(0, issued_k - 2); j < issued_k; ++j) mbar_wait(BAR(B_K + (j & 1)), (j >> 1) & 1, kErrDrain, p.err);
-        for (int j = max(0, issued_v - 2); j < issued_v; ++j) mbar_wait(BAR(B_V + (j & 1)), (j >> 1) & 1, kErrDrain, p.err);
+        mbar_wait_drain(BAR(B_Q), 0, p.err);
+        for (int j = max(0, issued_k - 2); j < issued_k; ++j)
+          if (!(drop_k0 && j == 0)) mbar_wait_drain(BAR(B_K + (j & 1)), (j >> 1) & 1, p.err);
+        for (int j = max(0, issued_v - 2); j < issued_v; ++j) mbar_wait_drain(BAR(B_V + (j & 1)), (j >> 1) & 1, p.err);
       }
     }
   } else if (warp == 5) {
@@ -554,23 +560,34 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
 }  // namespace tc
 
-// The error word lives in this translation unit; other tcgen05 kernels receive its address.
-__device__ int g_tc_error_word = 0;
+// The control block lives in this translation unit; other tcgen05 kernels receive its address.
+__device__ tc::TcControl g_tc_control = {0, 0, tc::kDefaultWaitLimitNs};
 
 int* tc_error_word() {
-  static int* ptrs[64] = {nullptr};
+  static std::atomic<int*> ptrs[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (ptrs[dev] == nullptr) {
+  int* known = ptrs[dev].load(std::memory_order_acquire);
+  if (known == nullptr) {
     void* p = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&p, g_tc_error_word);
+    cudaError_t e = cudaGetSymbolAddress(&p, g_tc_control);
     if (e != cudaSuccess) {
       set_last_cuda_error(e);
       return nullptr;
     }
-    ptrs[dev] = static_cast<int*>(p);
+    known = static_cast<int*>(p);
+    ptrs[dev].store(known, std::memory_order_release);
   }
-  return ptrs[dev];
+  return known;
+}
+
+int set_tc_wait_limit(unsigned long long ns) {
+  SLA_CUDA_OK(cudaMemcpyToSymbol(g_tc_control, &ns, sizeof(ns), offsetof(tc::TcControl, wait_limit_ns)));
+  return SLA_OK;
+}
+int set_tc_drop_first_k_tile(int on) {
+  SLA_CUDA_OK(cudaMemcpyToSymbol(g_tc_control, &on, sizeof(on), offsetof(tc::TcControl, drop_first_k_tile)));
+  return SLA_OK;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -635,6 +652,10 @@ int make_tmap_3d_u8(CUtensorMap* out, const void* base, int row_bytes, int L, in
   return SLA_OK;
 }
 
+constexpr int kFwdStaticSmem = 2 * 1024;   // statically allocated shared memory of the kernel (barriers, z, bias, 1/den)
+static int fwd_tc_smem_bytes(int D, int topk) { return 1024 + 128 * D * 2 + 4 * 64 * D * 2 + 4 * topk * 4 + 16; }
+bool sparse_fwd_tc_fits(const sla_shape* s) { return fwd_tc_smem_bytes(s->D, s->topk) + kFwdStaticSmem <= 227 * 1024; }
+
 template <typename T, int D, int BM>
 static int launch_tc(const sla_shape* s, const FwdParams& fp, cudaStream_t st) {
   const int bh = s->B * s->H;
@@ -663,9 +684,10 @@ static int launch_tc(const sla_shape* s, const FwdParams& fp, cudaStream_t st) {
   p.n_tiles = ceil_div(s->L, 128);
   p.scale_log2 = fp.scale_log2;
   auto kern = tc::sparse_fwd_tc_kernel<T, D, BM>;
-  const int tiles_bytes = 128 * D * 2 + 4 * 64 * D * 2;
-  const int smem = 1024 + tiles_bytes + 4 * fp.topk * 4 + 16;
-  if (smem > 113 * 1024) return SLA_ERR_BAD_TOPK;
+  // Up to 113 KB two CTAs share an SM; a longer entry list (top-k above about 1000 at D = 128) takes the SM alone.
+  // SLA_ERR_BAD_SHAPE (nothing launched) when the list does not fit at all: the caller picks another path.
+  const int smem = fwd_tc_smem_bytes(D, fp.topk);
+  if (!sparse_fwd_tc_fits(s)) return SLA_ERR_BAD_SHAPE;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   kern<<<dim3(p.n_tiles, bh), 192, smem, st>>>(tq, tk, tv, to, tos, thw, p);
   SLA_LAUNCH_OK();
@@ -683,10 +705,10 @@ int run_sparse_fwd_tc(const sla_shape* s, const FwdParams& p, cudaStream_t st) {
 
 int read_tc_error(int* out, bool clear) {
   int v = 0;
-  SLA_CUDA_OK(cudaMemcpyFromSymbol(&v, g_tc_error_word, sizeof(int)));
+  SLA_CUDA_OK(cudaMemcpyFromSymbol(&v, g_tc_control, sizeof(int)));
   if (clear && v != 0) {
     int z = 0;
-    SLA_CUDA_OK(cudaMemcpyToSymbol(g_tc_error_word, &z, sizeof(int)));
+    SLA_CUDA_OK(cudaMemcpyToSymbol(g_tc_control, &z, sizeof(int)));
   }
   *out = v;
   return SLA_OK;

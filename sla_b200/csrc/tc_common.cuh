@@ -10,11 +10,16 @@
 namespace sla {
 namespace tc {
 
-// Every kernel gets a pointer to a device-wide error word: 0 = fine, otherwise the code of the first
-// bounded wait that ran out. Once it is non-zero every CTA of the tcgen05 kernels leaves as soon as it
-// notices.
-
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s: far above any legitimate wait (microseconds)
+// Every kernel gets a pointer to a device-wide control block (TcControl): word 0 is the error word, 0 = fine,
+// otherwise the code of the first bounded wait that ran out. Once it is non-zero every CTA of the tcgen05
+// kernels leaves as soon as it notices. Word 1 is a test hook (see sparse_fwd_tc.cu), the 64-bit word behind
+// them the limit of every wait in nanoseconds.
+struct TcControl {
+  int error;
+  int drop_first_k_tile;             // test hook: CTA (0,0) of the forward never requests its first K tile
+  unsigned long long wait_limit_ns;
+};
+constexpr unsigned long long kDefaultWaitLimitNs = 2000000000ull;   // 2 s: far above any legitimate wait (microseconds)
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
@@ -54,8 +59,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
-// Bounded wait. Returns false (after recording `code`) if the phase did not complete within kWaitLimitNs of
-// wall-clock time or another CTA has already reported a failure. The bound is on elapsed time, not on the
+// Bounded wait. Returns false (after recording `code`) if the phase did not complete within the control block's
+// wait limit of wall-clock time or another CTA has already reported a failure. The bound is on elapsed time, not on the
 // number of polls: a try_wait on a pending phase may itself suspend the thread for a while.
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
@@ -67,11 +72,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t it = 0;; ++it) {
     if (mbar_try(bar, parity)) return true;
-    if ((it & 63u) == 63u && *reinterpret_cast<volatile int*>(err) != 0) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    if ((it & 15u) == 15u) {       // the control block is only looked at while the wait is already long
+      if (*reinterpret_cast<volatile int*>(err) != 0) return false;
+      if (global_timer_ns() - t0 > reinterpret_cast<volatile TcControl*>(err)->wait_limit_ns) break;
+    }
   }
   atomicCAS(err, 0, code);
   return false;
+}
+
+// Wait of the abort path: a copy this CTA requested earlier must land before its shared memory goes away. The
+// error word is already set at that point, so it is not consulted; the time limit still holds.
+__device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity, int* err) {
+  if (mbar_test(bar, parity)) return;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try(bar, parity)) return;
+    if ((it & 15u) == 15u &&
+        global_timer_ns() - t0 > reinterpret_cast<volatile TcControl*>(err)->wait_limit_ns) return;
+  }
 }
 
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
@@ -324,7 +343,11 @@ int make_tmap_rows(CUtensorMap* out, const void* base, int dtype, int D, int L, 
                    int box_rows);
 // host: same for 8-bit elements, rows of `row_bytes` (<= 128) bytes, box = (row_bytes, box_rows, 1).
 int make_tmap_3d_u8(CUtensorMap* out, const void* base, int row_bytes, int L, int BH, int box_rows);
-// host: address of the current device's error word (looked up once per device), or nullptr.
+// host: address of the current device's control block, i.e. of its error word (looked up once per device), or
+// nullptr.
 int* tc_error_word();
+// host: set the wait limit / the test hook of the current device's control block (synchronous copies).
+int set_tc_wait_limit(unsigned long long ns);
+int set_tc_drop_first_k_tile(int on);
 
 }  // namespace sla

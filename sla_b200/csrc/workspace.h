@@ -45,10 +45,12 @@ struct WsLinearState {
 inline WsLinearState ws_linear_state(const sla_shape* s) {
   WsLinearState w;
   size_t bh = size_t(s->B) * s->H;
-  // about 4 waves of 148 CTAs, at least 512 rows per CTA
-  long long want = (static_cast<long long>(s->L) * static_cast<long long>(bh) + 591) / 592;
-  int rows = static_cast<int>(want < 512 ? 512 : want);
-  rows = (rows + 63) / 64 * 64;
+  // The split of a head's rows into chunks fixes the order of the fp32 sums. It depends on L alone, never on
+  // B or H, so a (batch, head) unit gives the same bits whatever else is in the batch and however the units are
+  // sharded over GPUs: at most 64 chunks per head, at least 512 rows per chunk.
+  int nch = ws_ceil_div(s->L, 512);
+  if (nch > 64) nch = 64;
+  int rows = (ws_ceil_div(s->L, nch) + 63) / 64 * 64;
   w.rows = rows;
   w.nch = ws_ceil_div(s->L, rows);
   w.partial = 0;
@@ -94,9 +96,10 @@ struct WsBwd {
 inline WsBwd ws_bwd(const sla_shape* s) {
   WsBwd w;
   size_t bh = size_t(s->B) * s->H;
-  long long want = (static_cast<long long>(s->L) * static_cast<long long>(bh) + 295) / 296;
-  int rows = static_cast<int>(want < 512 ? 512 : want);
-  rows = (rows + s->D - 1) / s->D * s->D;
+  // chunks of the linear backward's row passes: a function of L alone, like ws_linear_state
+  int nch = ws_ceil_div(s->L, 512);
+  if (nch > 64) nch = 64;
+  int rows = (ws_ceil_div(s->L, nch) + 127) / 128 * 128;
   w.rows = rows;
   w.nch = ws_ceil_div(s->L, rows);
   size_t dd = size_t(s->D) * s->D;

@@ -13,6 +13,7 @@ libsla_b200.so. Nothing here falls back to PyTorch math.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -20,6 +21,16 @@ import torch
 
 from . import _lib
 from ._lib import SlaShape, check, lib
+
+# SLA_B200_CHECK=1: after every fused forward / backward call synchronise the device and raise if a bounded
+# device-side wait of a tcgen05 kernel ran out (otherwise poll with `_lib.raise_on_device_error()` once per step).
+_CHECK_EVERY_CALL = os.environ.get("SLA_B200_CHECK", "0") == "1"
+
+
+def _check_device():
+    if _CHECK_EVERY_CALL and not torch.cuda.is_current_stream_capturing():
+        _lib.raise_on_device_error()
+
 
 _DT = {torch.bfloat16: _lib.SLA_BF16, torch.float16: _lib.SLA_FP16, torch.float32: _lib.SLA_FP32}
 
@@ -107,7 +118,12 @@ def get_block_map(q, k, topk_ratio, BLKQ=64, BLKK=64):
 
 
 class _attention(torch.autograd.Function):
-    """Drop-in for sparse_linear_attention.kernel._attention (kernel.py:240-320)."""
+    """Drop-in for sparse_linear_attention.kernel._attention (kernel.py:240-320).
+
+    ``_attention.impl_flags`` (class attribute, default 0) is OR-ed into the shape's flags: set it to
+    ``_lib.FLAG_LEGACY_MMA`` to force the mma.sync kernels."""
+
+    impl_flags = 0
 
     @staticmethod
     def forward(ctx, q, k, v, k_block_id, lut, topk, BLOCK_M, BLOCK_N, qk_scale=None):
@@ -119,8 +135,8 @@ class _attention(torch.autograd.Function):
         B, H, L, D = q.shape
         bm = getattr(lut, "_sla_block_map", None)
         lut32 = bm.lut if bm is not None else lut.to(torch.int32)
-        shape = make_shape(B, H, L, D, BLOCK_M, BLOCK_N, topk, q.dtype, flags=_lib.FLAG_SPARSE_ONLY,
-                           qk_scale=qk_scale)
+        shape = make_shape(B, H, L, D, BLOCK_M, BLOCK_N, topk, q.dtype,
+                           flags=_lib.FLAG_SPARSE_ONLY | _attention.impl_flags, qk_scale=qk_scale)
         o_s = torch.empty_like(v)
         lse = torch.empty(q.shape[:-1], device=q.device, dtype=torch.float32)
         check(lib.sla_sparse_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(lut32), _p(o_s), _p(lse), _stream(q)))
@@ -217,6 +233,7 @@ class _SLAFused(torch.autograd.Function):
             fwd_shape = shape
         check(lib.sla_fwd(C.byref(fwd_shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o), _p(o_s),
                           _p(lse), _p(lin_state), _p(ws), ws.numel(), _stream(q)))
+        _check_device()
         if need_grad:
             ctx.save_for_backward(q, k, v, o_s, lse, lin_state, weight, bm.lut, bm.col_offsets, bm.col_index)
             ctx.sla_shape = shape
@@ -236,6 +253,7 @@ class _SLAFused(torch.autograd.Function):
         check(lib.sla_bwd(C.byref(shape), _p(q), _p(k), _p(v), _p(o_s), _p(lse), _p(d_o), _p(lut), _p(co), _p(ci),
                           _p(weight), _p(lin_state), _p(dq), _p(dk), _p(dv), _p(dw), _p(db), _p(ws), ws.numel(),
                           _stream(q)))
+        _check_device()
         return dq, dk, dv, dw, (db if ctx.has_bias else None), None, None, None, None, None, None, None
 
 
@@ -274,11 +292,50 @@ def sage_prepare(q, k, v, weight, bias, topk: int, feature="softmax", sparse_onl
     return LinearPrep(lin_state, ws, (B, H, L, D, 128, 64, topk, q.dtype, feature, flags))
 
 
+class _SageFused(torch.autograd.Function):
+    """SageSLA/core.py:100-158 as one operator. As in the reference the quantized sparse branch has no backward
+    (SageSLA/core.py:114-146 calls a forward-only kernel), while the linear branch and proj_l after it
+    (SageSLA/core.py:148-158) are differentiable: the backward returns their gradients for q, k, v, W and b."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, weight, bias, bm, feature, prep):
+        o, lin_state = _sage_forward(q, k, v, weight, bias, bm, feature, False, prep)
+        B, H, L, D = q.shape
+        ctx.save_for_backward(q, k, v, lin_state, weight)
+        ctx.sla_shape = make_shape(B, H, L, D, 128, 64, bm.topk, q.dtype, feature, flags=_lib.FLAG_LINEAR_ONLY)
+        ctx.has_bias = bias is not None
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, lin_state, weight = ctx.saved_tensors
+        shape = ctx.sla_shape
+        d_o = d_o.contiguous()
+        D = shape.D
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dw = torch.empty((D, D), dtype=torch.float32, device=q.device)
+        db = torch.empty((D,), dtype=torch.float32, device=q.device)
+        ws = _workspace(shape, _lib.OP_BWD, q.device)
+        check(lib.sla_bwd(C.byref(shape), _p(q), _p(k), _p(v), None, None, _p(d_o), None, None, None, _p(weight),
+                          _p(lin_state), _p(dq), _p(dk), _p(dv), _p(dw), _p(db), _p(ws), ws.numel(), _stream(q)))
+        _check_device()
+        return dq, dk, dv, dw, (db if ctx.has_bias else None), None, None, None
+
+
 def sage_sla_attention(q, k, v, weight, bias, bm: BlockMap, feature="softmax", sparse_only: bool = False,
                        prep: Optional[LinearPrep] = None):
-    """SageSLA/core.py:100-158: quantized sparse branch + linear branch + proj_l. Forward only.
-    ``sparse_only`` returns the quantized sparse branch alone (the o_s of SageSLA/core.py:114)."""
+    """SageSLA/core.py:100-158: quantized sparse branch + linear branch + proj_l.
+    ``sparse_only`` returns the quantized sparse branch alone (the o_s of SageSLA/core.py:114). When a gradient is
+    required it flows through the linear branch and proj_l only, as in the reference."""
     _require_cuda(q, k, v, weight)
+    need_grad = not sparse_only and torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (q, k, v, weight, bias))
+    if need_grad:
+        return _SageFused.apply(q, k, v, weight, bias, bm, feature, prep)
+    return _sage_forward(q, k, v, weight, bias, bm, feature, sparse_only, prep)[0]
+
+
+def _sage_forward(q, k, v, weight, bias, bm, feature, sparse_only, prep):
     B, H, L, D = q.shape
     flags = _lib.FLAG_SPARSE_ONLY if sparse_only else 0
     o = torch.empty_like(q)
@@ -293,4 +350,5 @@ def sage_sla_attention(q, k, v, weight, bias, bm: BlockMap, feature="softmax", s
         ws = _workspace(shape, _lib.OP_SAGE_FWD, q.device)
     check(lib.sage_sla_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o),
                            _p(lin_state), _p(ws), ws.numel(), _stream(q)))
-    return o
+    _check_device()
+    return o, lin_state

@@ -73,6 +73,39 @@ def test_block_map_vs_oracle(dtype, B, H, L, D, BLKQ, BLKK, ratio):
     _check_against(score, bm.lut, lut, strict=False)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("ratio", [0.6, 0.75, 0.95])
+def test_negative_tied_kth_score(dtype, ratio):
+    """The k-th largest pooled score is negative and tied: every KV block appears four times, so each score
+    value occurs at least four times in a row, and with K-mean smoothing (utils.py:56) most of a row's scores at
+    these ratios lie below zero. Every row must still select exactly topk blocks (utils.py:63), the 0/1 map and
+    the column lists must describe the same sets, and the sets must equal the oracle's up to ties."""
+    from oracle import sla_oracle as O
+    from sla_b200 import ops
+    g = torch.Generator().manual_seed(11)
+    B, H, D, BLK, nuniq, rep = 1, 2, 64, 64, 9, 4
+    q = torch.randn(B, H, nuniq * rep * BLK, D, generator=g).to(dtype)
+    kb = torch.randn(B, H, nuniq, BLK, D, generator=g)
+    k = kb.repeat(1, 1, rep, 1, 1).reshape(B, H, nuniq * rep * BLK, D).to(dtype)
+    bm = ops.block_map(q.cuda(), k.cuda(), ratio, BLK, BLK, want_map=True, want_cols=True)
+    nb = mb = nuniq * rep
+    topk = O.topk_count(nb, ratio)
+    assert bm.topk == topk
+    lut = bm.lut.cpu()
+    assert bool((lut[..., 1:] > lut[..., :-1]).all()) and int(lut.min()) >= 0 and int(lut.max()) < nb
+    smap = bm.sparse_map.cpu()
+    assert bool((smap.sum(-1) == topk).all()), "a row selected more or fewer than topk blocks"
+    assert torch.equal(smap, torch.zeros_like(smap).scatter_(-1, lut.long(), 1))
+    co = bm.col_offsets.cpu()
+    assert bool((co[..., 0] == 0).all()) and bool((co[..., nb] == mb * topk).all())
+    assert torch.equal(smap.sum(dim=-2).int(), co[..., 1:] - co[..., :-1])
+    score = O.pooled_scores(q, k, BLK, BLK)
+    kth = torch.sort(score.float(), dim=-1, descending=True).values[..., topk - 1]
+    assert float((kth < 0).float().mean()) > 0.5, "the case must exercise negative k-th scores"
+    _, lut_ref, _ = O.get_block_map(q, k, ratio, BLK, BLK)
+    _check_against(score, lut, lut_ref, strict=False)
+
+
 def test_smooth_k_invariance():
     """Adding a constant vector to every key leaves the selected set unchanged (utils.py:56)."""
     from sla_b200 import ops

@@ -1,14 +1,25 @@
 """On-GPU parity against the UNMODIFIED reference package (its Triton kernels), installed under
-baseline/_ref. Same inputs, same parameters: LUT equal as per-row sets up to score ties, outputs and
-gradients within cosine >= 0.999 / relative L1 <= 1e-2. Skipped when baseline/_ref is absent."""
+baseline/_ref. Same inputs, same parameters.
+
+Block LUT: equal as per-row sets. Rows that differ are classified with the REFERENCE's own pooled scores,
+computed on the GPU with the reference's own operators (utils.py:56-59): `tie` = every member the two sets
+disagree on has exactly the row's k-th largest score (torch.topk leaves ties unspecified, utils.py:63);
+`ulp` = every such member is within one unit in the last place of the score dtype of the k-th score (the
+scores are rounded to the input dtype, utils.py:59, after an fp32 sum whose order differs between a library
+GEMM and this library's kernel, so a sum on a rounding boundary can land on either side); `bad` = anything
+else. bad must be 0; the counts are printed and reported as a warning so that they show in the test log.
+
+Outputs and gradients: cosine >= 0.999 and relative L1 <= 1e-2 (3e-2 for dW, db); the quantized module
+cosine >= 0.995 against the reference's 16-bit module. Skipped when baseline/_ref is absent."""
 import importlib.util
 import os
 import sys
+import warnings
 
 import pytest
 import torch
 
-from helpers import assert_close_parity
+from helpers import assert_close_parity, cos_sim
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -28,39 +39,105 @@ def _reference():
     return mod
 
 
-@pytest.mark.parametrize("wl,units", [("c2", None), ("c3", [0])])
-def test_module_matches_reference_triton(wl, units):
+def _lut_parity(tag, q, k, ratio, BLKQ, BLKK):
+    """(ident, tie, ulp, bad) row counts of this library's LUT against the reference's, see the file header."""
+    from sla_b200 import ops
+    _reference()
+    from sla_reference.utils import get_block_map as ref_block_map, mean_pool as ref_mean_pool
+    _, lut_ref, topk_ref = ref_block_map(q, k, ratio, BLKQ, BLKK)
+    bm = ops.block_map(q, k, ratio, BLKQ, BLKK)
+    assert bm.topk == topk_ref
+    # the reference's own pooled scores (utils.py:56-59), with its own operators, on the GPU
+    arg_k = k - torch.mean(k, dim=-2, keepdim=True)
+    score = (ref_mean_pool(q, BLKQ) @ ref_mean_pool(arg_k, BLKK).transpose(-1, -2)).float()
+    kth = torch.topk(score, topk_ref, dim=-1).values[..., -1:]
+    mine = torch.zeros_like(score, dtype=torch.bool).scatter_(-1, bm.lut.long(), True)
+    theirs = torch.zeros_like(score, dtype=torch.bool).scatter_(-1, lut_ref.long(), True)
+    assert bool((mine.sum(-1) == topk_ref).all()) and bool((theirs.sum(-1) == topk_ref).all())
+    diff = mine ^ theirs
+    rows_diff = diff.any(-1)
+    dist = (score - kth).abs()
+    mant = {torch.bfloat16: 7, torch.float16: 10}.get(q.dtype, 23)
+    ulp = torch.exp2(torch.floor(torch.log2(kth.abs().clamp_min(1e-30))) - mant)
+    tie_rows = rows_diff & ((dist == 0) | ~diff).all(-1)
+    ulp_rows = rows_diff & ~tie_rows & ((dist <= ulp) | ~diff).all(-1)
+    bad_rows = rows_diff & ~tie_rows & ~ulp_rows
+    counts = tuple(int(x) for x in ((~rows_diff).sum(), tie_rows.sum(), ulp_rows.sum(), bad_rows.sum()))
+    msg = "LUT parity vs reference [%s]: identical=%d tie=%d ulp=%d bad=%d of %d rows" % ((tag,) + counts + (rows_diff.numel(),))
+    print(msg)
+    warnings.warn(msg)
+    assert counts[3] == 0, msg
+    return bm, lut_ref
+
+
+def _modules(w, BLKQ, BLKK, W, b):
     import sla_b200
-    from oracle import sla_oracle as O
-    from sla_b200 import ops, synthetic
     ref = _reference()
-    from sla_reference.utils import get_block_map as ref_block_map
-    w = synthetic.WORKLOADS[wl]
-    q, k, v, do = synthetic.make_inputs(w, "cuda", units=units)
-    W, b = synthetic.make_proj(w, "cuda", std=0.05)
-    b = b + 0.01
-    mine = sla_b200.SparseLinearAttention(w.D, w.topk, w.feature, w.BLKQ, w.BLKK).cuda()
-    theirs = ref.SparseLinearAttention(w.D, w.topk, w.feature, w.BLKQ, w.BLKK).cuda()
+    mine = sla_b200.SparseLinearAttention(w.D, w.topk, w.feature, BLKQ, BLKK).cuda()
+    theirs = ref.SparseLinearAttention(w.D, w.topk, w.feature, BLKQ, BLKK).cuda()
     for m in (mine, theirs):
         with torch.no_grad():
             m.proj_l.weight.copy_(W)
             m.proj_l.bias.copy_(b)
-    # block map: sets per row, ties excepted
-    _, lut_ref, topk_ref = ref_block_map(q, k, w.topk, w.BLKQ, w.BLKK)
-    bm = ops.block_map(q, k, w.topk, w.BLKQ, w.BLKK)
-    assert bm.topk == topk_ref
-    score = O.pooled_scores(q.cpu(), k.cpu(), w.BLKQ, w.BLKK)
-    ident, tie, bad = O.lut_rows_equal_up_to_ties(score, bm.lut.cpu().long(), lut_ref.cpu().long(), ulps=2)
-    total = ident + tie + bad
-    assert bad <= 0.002 * total, f"LUT rows differing beyond ties: {bad}/{total} (tie-only {tie})"
-    res = []
-    for m in (mine, theirs):
-        qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
-        o = m(qg, kg, vg)
-        o.backward(do)
-        res.append((o.detach().float().cpu(), qg.grad.float().cpu(), kg.grad.float().cpu(), vg.grad.float().cpu(),
-                    m.proj_l.weight.grad.cpu(), m.proj_l.bias.grad.cpu()))
-    names = ("o", "dq", "dk", "dv", "dW", "db")
-    for n, a, r in zip(names, *res):
+    return mine, theirs
+
+
+def _fwd_bwd(m, q, k, v, do):
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    o = m(qg, kg, vg)
+    o.backward(do)
+    return (o.detach().float().cpu(), qg.grad.float().cpu(), kg.grad.float().cpu(), vg.grad.float().cpu(),
+            m.proj_l.weight.grad.cpu(), m.proj_l.bias.grad.cpu())
+
+
+@pytest.mark.parametrize("wl,units,topk", [
+    ("c2", None, None),          # README shape, all 8 units
+    ("c3", [0], None),           # one head of the headline configuration (L = 32760, 25 of 512 blocks)
+    ("c5", [3], 0.05),           # one head of the long-sequence sweep: D = 64, BLKQ = 128, relu, L = 131072
+    ("c5", [3], 0.2),            # same at 409 of 2048 blocks (keys of a score row spill past the registers)
+])
+def test_module_matches_reference_triton(wl, units, topk):
+    import dataclasses
+    from sla_b200 import synthetic
+    w = synthetic.WORKLOADS[wl]
+    if topk is not None:
+        w = dataclasses.replace(w, topk=topk)
+    q, k, v, do = synthetic.make_inputs(w, "cuda", units=units)
+    W, b = synthetic.make_proj(w, "cuda", std=0.05)
+    b = b + 0.01
+    _lut_parity(f"{wl} topk={w.topk}", q, k, w.topk, w.BLKQ, w.BLKK)
+    mine, theirs = _modules(w, w.BLKQ, w.BLKK, W, b)
+    res = [_fwd_bwd(m, q, k, v, do) for m in (mine, theirs)]
+    for n, a, r in zip(("o", "dq", "dk", "dv", "dW", "db"), *res):
         l1 = 3e-2 if n in ("dW", "db") else 1e-2
         assert_close_parity(a, r, cos_min=0.999, l1_max=l1, what=f"{wl}.{n}")
+
+
+def test_c4_shape_quantized_and_16bit_match_reference_16bit():
+    """One head of the quantized configuration's shape (L = 75600: query tail 80 rows, key tail 16 rows, 59 of
+    1182 blocks, BLKQ/BLKK = 128/64). The reference's quantized module cannot run here (its kernel package is not
+    installed), so its 16-bit module at the same block sizes is the yardstick, as the quantized path's bar is
+    defined against the un-quantized result: quantized forward cosine >= 0.995, this library's 16-bit module
+    forward and gradients cosine >= 0.999 / relative L1 <= 1e-2."""
+    import sla_b200
+    from sla_b200 import synthetic
+    w = synthetic.WORKLOADS["c4"]
+    q, k, v, do = synthetic.make_inputs(w, "cuda", units=[7])
+    W, b = synthetic.make_proj(w, "cuda", std=0.05)
+    b = b + 0.01
+    _lut_parity("c4 shape", q, k, w.topk, 128, 64)
+    mine, theirs = _modules(w, 128, 64, W, b)
+    res = [_fwd_bwd(m, q, k, v, do) for m in (mine, theirs)]
+    for n, a, r in zip(("o", "dq", "dk", "dv", "dW", "db"), *res):
+        l1 = 3e-2 if n in ("dW", "db") else 1e-2
+        assert_close_parity(a, r, cos_min=0.999, l1_max=l1, what=f"c4shape.{n}")
+    sage = sla_b200.SageSparseLinearAttention(w.D, w.topk, w.feature).cuda()
+    with torch.no_grad():
+        sage.proj_l.weight.copy_(W)
+        sage.proj_l.bias.copy_(b)
+        o8 = sage(q, k, v).float().cpu()
+    c = cos_sim(o8, res[1][0])
+    msg = "quantized forward vs reference 16-bit module at the c4 shape: cosine %.6f" % c
+    print(msg)
+    warnings.warn(msg)
+    assert c >= 0.995, msg

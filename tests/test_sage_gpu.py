@@ -90,3 +90,36 @@ def test_sage_prepare_on_side_stream_changes_nothing():
             outs.append(m(q.cuda(), k.cuda(), v.cuda()))
         torch.cuda.synchronize()
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("D,feature,L", [(128, "softmax", 1500), (64, "relu", 1100), (128, "elu", 777)])
+def test_sage_module_backward_is_the_linear_branch(D, feature, L):
+    """In the reference only the quantized o_s is a constant of the graph (SageSLA/core.py:114-146); the linear
+    branch and proj_l after it (SageSLA/core.py:148-158) are ordinary autograd ops. The module's gradients must
+    equal the oracle autograd (fp64) of  proj_l(calc_linear(phi(q), phi(k), v))  alone."""
+    import sla_b200
+    from oracle import sla_oracle as O
+    B, H = 1, 2
+    q, k, v = _inputs(B, H, L, D, L + 1, 0.5)
+    g = torch.Generator().manual_seed(L)
+    do = torch.randn(B, H, L, D, generator=g).bfloat16()
+    w, b = torch.randn(D, D, generator=g) * 0.05, torch.randn(D, generator=g) * 0.05
+    m = sla_b200.SageSparseLinearAttention(D, 0.2, feature).cuda()
+    with torch.no_grad():
+        m.proj_l.weight.copy_(w)
+        m.proj_l.bias.copy_(b)
+    qg, kg, vg = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o = m(qg, kg, vg)
+    with torch.no_grad():
+        o_nograd = m(q.cuda(), k.cuda(), v.cuda())
+    assert torch.equal(o.detach(), o_nograd)
+    o.backward(do.cuda())
+    qd, kd, vd = (t.double().requires_grad_(True) for t in (q, k, v))
+    wd, bd = w.double().requires_grad_(True), b.double().requires_grad_(True)
+    o_l = O.calc_linear(O.feature_map(qd, feature), O.feature_map(kd, feature), vd)
+    (o_l @ wd.t() + bd).backward(do.double())
+    assert_close_parity(qg.grad.float().cpu(), qd.grad, what="dq")
+    assert_close_parity(kg.grad.float().cpu(), kd.grad, what="dk")
+    assert_close_parity(vg.grad.float().cpu(), vd.grad, what="dv")
+    assert_close_parity(m.proj_l.weight.grad.cpu(), wd.grad, l1_max=2e-2, what="dw")
+    assert_close_parity(m.proj_l.bias.grad.cpu(), bd.grad, l1_max=2e-2, what="db")
