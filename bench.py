@@ -470,15 +470,20 @@ def main():
         strong_ms = float(t.item())
         gathered = [None] * world
         dist.all_gather_object(gathered, my_sums.cpu())
-        equal = None
+        equal, mismatches = None, None
         if rank == 0:
-            equal = bool(torch.equal(torch.cat(gathered, dim=0), ref_sums.cpu()))
+            got = torch.cat(gathered, dim=0)
+            equal = bool(torch.equal(got, ref_sums.cpu()))
+            if not equal:       # which (unit, tensor) pairs differ
+                names = ("o", "dq", "dk", "dv")
+                bad = (got != ref_sums.cpu()).any(dim=-1).nonzero().tolist()
+                mismatches = [f"unit {u}: {names[t]}" for u, t in bad][:16]
         bound = w.units / max(counts)
         strong = {"ms_per_step": strong_ms, "units_per_rank": counts, "speedup": ms / strong_ms,
                   "efficiency": ms / strong_ms / world, "granularity_bound": bound,
                   "efficiency_vs_granularity_bound": ms / strong_ms / bound,
                   "value": w.dense_equiv_flops(bwd) / strong_ms / 1e9, "unit": "TFLOP/s",
-                  "checksums_equal": equal,
+                  "checksums_equal": equal, "checksum_mismatches": mismatches,
                   "checksums": "per-unit int64 sums over the bits of " + ("o, dq, dk, dv" if bwd else "o") +
                                ", sharded run vs rank 0's unsharded run of the same units",
                   "baseline": "speedup = this run's replica ms_per_step (all units on every GPU) / sharded ms_per_step"}

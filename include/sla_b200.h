@@ -136,6 +136,14 @@ SLA_API int sla_block_map(const sla_shape* shape, int in_dtype, const void* q, c
 SLA_API int sla_column_lists(const sla_shape* shape, const int8_t* sparse_map, int32_t* col_offsets,
                              int32_t* col_index, sla_stream_t stream);
 
+/* Converts `count` block indices between the 32-bit form every entry point here reads and writes (lut,
+ * col_index) and an unsigned 16-bit form, for callers that keep block maps across calls (the reference's own
+ * benchmark predicts the map once, evaluate/bench_kernel.py:79, and a diffusion sampler may reuse it over several
+ * steps): (src_bits, dst_bits) = (32, 16) packs, (16, 32) unpacks. Indices must be below 65,536 (L < 4 Mi tokens).
+ * The reference keeps its LUT as int64 (utils.py:64); no counterpart there. */
+SLA_API int sla_index_convert(const void* src, int src_bits, void* dst, int dst_bits, size_t count,
+                              sla_stream_t stream);
+
 /* Replaces sparse_linear_attention/kernel.py:242-274 _attention.forward (+ _attn_fwd :21-82). */
 SLA_API int sla_sparse_fwd(const sla_shape* shape, const void* q, const void* k, const void* v,
                    const int32_t* lut, void* o_s, float* lse, sla_stream_t stream);

@@ -19,7 +19,7 @@ FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA, FLAG_LINEAR_UNSELECTED, FLAG_STATE_READY, FLA
 # every symbol include/sla_b200.h declares
 EXPORTS = (
     "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_debug_set_trace", "sla_debug_set_wait_limit_ns", "sla_debug_drop_first_k_tile", "sla_topk_count", "sla_workspace_bytes", "sla_kernel_path",
-    "sla_block_map", "sla_column_lists", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_linear_state_static", "sla_fwd", "sla_fwd_prepare", "sla_bwd",
+    "sla_block_map", "sla_column_lists", "sla_index_convert", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_linear_state_static", "sla_fwd", "sla_fwd_prepare", "sla_bwd",
     "sage_sla_fwd", "sage_sla_prepare",
 )
 
@@ -67,6 +67,8 @@ def _load() -> C.CDLL:
     lib.sla_workspace_bytes.argtypes = [sp, C.c_int]
     lib.sla_block_map.restype = C.c_int
     lib.sla_block_map.argtypes = [sp, C.c_int, vp, vp, i32p, i8p, i32p, i32p, vp, C.c_size_t, vp]
+    lib.sla_index_convert.restype = C.c_int
+    lib.sla_index_convert.argtypes = [vp, C.c_int, vp, C.c_int, C.c_size_t, vp]
     lib.sla_column_lists.restype = C.c_int
     lib.sla_column_lists.argtypes = [sp, i8p, i32p, i32p, vp]
     lib.sla_sparse_fwd.restype = C.c_int

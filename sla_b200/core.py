@@ -68,11 +68,21 @@ class SparseLinearAttention(nn.Module):
             nn.init.zeros_(self.proj_l.weight)
             nn.init.zeros_(self.proj_l.bias)
 
-    def forward(self, q, k, v, return_sparsity=False):
+    def predict_block_map(self, q, k, with_column_lists=True):
+        R"""Block-mask prediction alone (utils.py:55-67), on q and k as given (core.py:83). The result can be
+        handed to `forward(..., block_map=...)` any number of times, e.g. over several steps of a diffusion sampler,
+        or computed once outside a timed loop as the reference's benchmark does (evaluate/bench_kernel.py:79).
+        `with_column_lists`: also build the per-KV-block lists a backward needs. `.pack16()` halves its size."""
+        return ops.block_map(q.contiguous(), k.contiguous(), self.topk, self.BLKQ, self.BLKK,
+                             want_cols=with_column_lists)
+
+    def forward(self, q, k, v, return_sparsity=False, block_map=None):
         R"""
         Args:
             q, k, v: (B, H, L, D) CUDA tensors (any float dtype; output has q's dtype).
             return_sparsity: also return topk / N_BLOCKS, the kept fraction of KV blocks.
+            block_map: not in the reference. A map from `predict_block_map` (or its packed form) to use instead of
+                predicting one from this call's q and k.
         """
         dtype = q.dtype
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
@@ -80,16 +90,23 @@ class SparseLinearAttention(nn.Module):
             q.requires_grad or k.requires_grad or v.requires_grad or self.proj_l.weight.requires_grad)
         if need_grad and self.linear_scope == "unselected":
             raise NotImplementedError("linear_scope='unselected' has no backward: call it under torch.no_grad()")
+        bm = None
+        if block_map is not None:
+            bm = block_map.unpack() if isinstance(block_map, ops.PackedBlockMap) else block_map
+            mb = (q.shape[2] + self.BLKQ - 1) // self.BLKQ
+            if tuple(bm.lut.shape) != (q.shape[0], q.shape[1], mb, bm.topk) or bm.lut.device != q.device:
+                raise ValueError("block_map was predicted for another shape, block size or device")
         # The linear-branch state needs k, v and proj_l only and the block map q and k only: the state kernels go to
         # a second stream and run next to the (latency-bound) mask prediction; both join before the attention kernel.
         kc, vc = k.to(self.dtype), v.to(self.dtype)
         prep = None
-        if _want_overlap(self.overlap_linear_state, k) and self.linear_scope == "all":
+        if bm is None and _want_overlap(self.overlap_linear_state, k) and self.linear_scope == "all":
             nb = (k.shape[2] + self.BLKK - 1) // self.BLKK
             side = ops.side_stream(q.device)
             prep = ops.prepare_linear(kc, vc, self.proj_l.weight, self.proj_l.bias, ops.topk_count(nb, self.topk),
                                       self.BLKQ, self.BLKK, self.feature_map, self.impl_flags, stream=side)
-        bm = ops.block_map(q, k, self.topk, self.BLKQ, self.BLKK, want_cols=need_grad)  # on the given dtype
+        if bm is None:
+            bm = ops.block_map(q, k, self.topk, self.BLKQ, self.BLKK, want_cols=need_grad)  # on the given dtype
         if prep is not None:
             torch.cuda.current_stream(q.device).wait_stream(side)
         q, k, v = q.to(self.dtype), kc, vc

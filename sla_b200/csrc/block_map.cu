@@ -387,6 +387,38 @@ int run_k_mean(const sla_shape* s, const void* k, float* partial, float* kmean, 
 
 }  // namespace sla
 
+namespace sla {
+// ---- 7. packed block lists: block indices fit 16 bits while N_BLOCKS, M_BLOCKS <= 65536 ----
+template <typename TSrc, typename TDst>
+__global__ void __launch_bounds__(256) index_convert_kernel(const TSrc* __restrict__ src, TDst* __restrict__ dst,
+                                                            size_t n) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    dst[i] = static_cast<TDst>(src[i]);
+}
+}  // namespace sla
+
+extern "C" int sla_index_convert(const void* src, int src_bits, void* dst, int dst_bits, size_t count,
+                                 sla_stream_t stream) {
+  using namespace sla;
+  if (!src || !dst) return SLA_ERR_NULL;
+  if (count == 0) return SLA_OK;
+  int rc = check_device_arch();
+  if (rc != SLA_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(count / 1024 + 1 < 148u * 8u ? count / 1024 + 1 : 148u * 8u);
+  if (src_bits == 32 && dst_bits == 16)
+    index_convert_kernel<int32_t, uint16_t><<<grid, 256, 0, st>>>(static_cast<const int32_t*>(src),
+                                                                  static_cast<uint16_t*>(dst), count);
+  else if (src_bits == 16 && dst_bits == 32)
+    index_convert_kernel<uint16_t, int32_t><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(src),
+                                                                  static_cast<int32_t*>(dst), count);
+  else
+    return SLA_ERR_UNSUPPORTED;
+  SLA_LAUNCH_OK();
+  return SLA_OK;
+}
+
 extern "C" int sla_column_lists(const sla_shape* s, const int8_t* sparse_map, int32_t* col_offsets,
                                 int32_t* col_index, sla_stream_t stream) {
   using namespace sla;

@@ -73,6 +73,38 @@ class BlockMap:
     col_index: Optional[torch.Tensor]     # (B,H,M_BLOCKS*topk) int32
 
 
+    def pack16(self) -> "PackedBlockMap":
+        """A copy with 16-bit block indices, for keeping the map across calls at half the bytes."""
+        if max(self.n_blocks, self.lut.shape[-2]) > 65536:
+            raise ValueError("block indices do not fit 16 bits")
+        return PackedBlockMap(_convert_index(self.lut, 16), self.topk, self.n_blocks,
+                              self.col_offsets, None if self.col_index is None else _convert_index(self.col_index, 16))
+
+
+@dataclass
+class PackedBlockMap:
+    """`BlockMap` with unsigned 16-bit indices (stored in int16 tensors); `unpack()` gives the form the operators
+    read. The 0/1 map is not kept: the LUT and the column lists describe the same set."""
+    lut16: torch.Tensor
+    topk: int
+    n_blocks: int
+    col_offsets: Optional[torch.Tensor]
+    col_index16: Optional[torch.Tensor]
+
+    def unpack(self) -> BlockMap:
+        return BlockMap(_convert_index(self.lut16, 32), self.topk, self.n_blocks, None, self.col_offsets,
+                        None if self.col_index16 is None else _convert_index(self.col_index16, 32))
+
+
+def _convert_index(t: torch.Tensor, dst_bits: int) -> torch.Tensor:
+    _require_cuda(t)
+    t = t.contiguous()
+    src_bits = 32 if t.dtype == torch.int32 else 16
+    out = torch.empty(t.shape, dtype=torch.int16 if dst_bits == 16 else torch.int32, device=t.device)
+    check(lib.sla_index_convert(_p(t), src_bits, _p(out), dst_bits, t.numel(), _stream(t)))
+    return out
+
+
 def block_map(q: torch.Tensor, k: torch.Tensor, topk_ratio: float, BLKQ: int = 64, BLKK: int = 64,
               want_map: bool = False, want_cols: bool = False) -> BlockMap:
     _require_cuda(q, k)

@@ -234,3 +234,37 @@ def test_linear_state_on_side_stream_changes_nothing(D, BLKQ, L, feat):
         res[overlap] = (o.detach(), qg.grad, kg.grad, vg.grad, m2.proj_l.weight.grad.clone(), m2.proj_l.bias.grad.clone())
     for a, b in zip(res[True], res[False]):
         assert torch.equal(a, b)
+
+
+def test_block_map_reuse_and_packed_form():
+    """A map predicted once (`predict_block_map`) and handed back to `forward` gives the bits of a forward that
+    predicts it itself, forward and backward, also after a round trip through the 16-bit packed form; a map for
+    another shape is refused."""
+    import sla_b200
+    g = torch.Generator().manual_seed(17)
+    B, H, L, D = 1, 2, 2100, 128
+    q, k, v, do = (torch.randn(B, H, L, D, generator=g).bfloat16().cuda() for _ in range(4))
+    m = _module(D, 0.15, "softmax", 64, 64, True, torch.randn(D, D, generator=g) * 0.05,
+                torch.randn(D, generator=g) * 0.05)
+
+    def run(**kw):
+        a, b, c = (t.clone().requires_grad_(True) for t in (q, k, v))
+        o = m(a, b, c, **kw)
+        o.backward(do)
+        out = (o.detach(), a.grad, b.grad, c.grad, m.proj_l.weight.grad.clone())
+        m.proj_l.weight.grad = m.proj_l.bias.grad = None
+        return out
+
+    ref = run()
+    bm = m.predict_block_map(q, k)
+    packed = bm.pack16()
+    assert packed.lut16.dtype == torch.int16 and packed.lut16.numel() == bm.lut.numel()
+    assert torch.equal(packed.unpack().lut, bm.lut) and torch.equal(packed.unpack().col_index, bm.col_index)
+    for kw in (dict(block_map=bm), dict(block_map=packed)):
+        for a, r in zip(run(**kw), ref):
+            assert torch.equal(a, r)
+    with torch.no_grad():
+        o2, sp = m(q, k, v, return_sparsity=True, block_map=m.predict_block_map(q, k, with_column_lists=False))
+    assert torch.equal(o2, ref[0]) and sp == bm.topk / bm.n_blocks
+    with pytest.raises(ValueError):
+        m(q[:, :1], k[:, :1], v[:, :1], block_map=bm)
