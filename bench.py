@@ -152,13 +152,14 @@ def load_synthetic():
     return mod
 
 
-def bench_config(w, world, impl="default"):
+def bench_config(w, world, impl="default", linear_scope="all"):
     """The `config` object both arms print (same keys, same values for the same command line)."""
     tensor_mb = w.B * w.H * w.L * w.D * 2 / 1e6
     return {"workload": w.name, "B_per_gpu": w.B, "H": w.H, "L": w.L, "D": w.D, "BLKQ": w.BLKQ, "BLKK": w.BLKK,
             "topk": w.topk, "topk_blocks": w.topk_blocks, "feature_map": w.feature,
             "global_units": world * w.units, "parallelism": f"bh-shard x{world}",
-            "l2": "inputs larger than L2 (q,k,v,dO,o,dq,dk,dv = %.0f MB)" % (8 * tensor_mb), "impl": impl}
+            "l2": "inputs larger than L2 (q,k,v,dO,o,dq,dk,dv = %.0f MB)" % (8 * tensor_mb), "impl": impl,
+            "linear_scope": linear_scope}
 
 
 def cpu_sample(w):
@@ -298,6 +299,9 @@ def main():
     ap.add_argument("--single-stream", action="store_true",
                     help="keep every launch on one stream (the modules otherwise run the linear-branch state and "
                          "the quantization pre-passes on a second stream next to the block map)")
+    ap.add_argument("--linear-scope", default="all", choices=["all", "unselected"],
+                    help="scope of the linear branch: every token (the reference's code) or, per query block, the KV "
+                         "blocks it did not select")
     ap.add_argument("--gather", action="store_true",
                     help="N > 1: also time the optional NCCL all-gather of the sharded run's output")
     ap.add_argument("--no-sustained", action="store_true", help="skip the 2 s sustained-clock loop (N = 1)")
@@ -344,7 +348,8 @@ def main():
     if w.quantized:
         m = sla_b200.SageSparseLinearAttention(w.D, w.topk, w.feature).to(dev)
     else:
-        m = sla_b200.SparseLinearAttention(w.D, w.topk, w.feature, w.BLKQ, w.BLKK).to(dev)
+        m = sla_b200.SparseLinearAttention(w.D, w.topk, w.feature, w.BLKQ, w.BLKK,
+                                           linear_scope=args.linear_scope).to(dev)
     if args.single_stream:
         m.overlap_linear_state = m.overlap_prepare = False   # default None: fork when the tensors are large enough
     with torch.no_grad():
@@ -671,7 +676,7 @@ def main():
         "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8/e4m3" if w.quantized else "bf16", "data": "synthetic",
-        "config": bench_config(w, world, "mma.sync" if args.legacy_mma else "default"),
+        "config": bench_config(w, world, "mma.sync" if args.legacy_mma else "default", args.linear_scope),
         "fwd_ms": fwd_ms, "fwd_bwd_ms": ms,
         "fwd_dense_equiv_tflops": world * w.dense_equiv_flops(False) / fwd_ms / 1e9,
         "sparse_actual_tflops": world * (w.sparse_flops(bwd) + w.linear_flops(bwd)) / ms / 1e9,

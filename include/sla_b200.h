@@ -60,10 +60,9 @@ enum sla_op { SLA_OP_BLOCK_MAP = 0, SLA_OP_FWD = 1, SLA_OP_BWD = 2, SLA_OP_LINEA
 enum sla_flags {
   SLA_FLAG_SPARSE_ONLY = 1, /* skip the linear branch and proj_l (the `_attention` operator) */
   SLA_FLAG_LEGACY_MMA = 2,  /* use the mma.sync kernels instead of the tcgen05 ones */
-  SLA_FLAG_LINEAR_UNSELECTED = 4, /* sla_fwd only: the linear branch of query block i sums over the KV blocks
+  SLA_FLAG_LINEAR_UNSELECTED = 4, /* sla_fwd, sla_bwd: the linear branch of query block i sums over the KV blocks
                                     that block did NOT select (the scope drawn in assets/overview_of_SLA.png)
-                                    instead of over all tokens (core.py:92-96). Forward only: sla_bwd returns
-                                    SLA_ERR_UNSUPPORTED with this flag. */
+                                    instead of over all tokens (core.py:92-96). tcgen05 kernels only. */
   SLA_FLAG_LINEAR_ONLY = 16,     /* sla_bwd only: differentiate the linear branch and proj_l alone, the sparse branch
                                     being a constant of the graph (the quantized forward of SageSLA/core.py:114-146
                                     has no backward; core.py:148-158 after it is ordinary autograd). o_s, lse, lut and

@@ -232,11 +232,13 @@ def calc_linear(cq, ck, v):
 
 def calc_linear_unselected(cq, ck, v, sparse_map, BLKQ, BLKK):
     """The paper's scope (assets/overview_of_SLA.png, right panel): for query block i the state is
-    summed over the KV blocks NOT selected for i. fp32 evaluation."""
+    summed over the KV blocks NOT selected for i. Evaluated in fp32, or in fp64 when the inputs are fp64;
+    differentiable (the block map is a constant), and defined as 0 when every block is selected."""
     B, H, L, D = cq.shape
     mb, nb = sparse_map.shape[-2:]
+    dt = torch.float64 if cq.dtype == torch.float64 else torch.float32
     padk = nb * BLKK - L
-    ckf, vf = ck.float(), v.float()
+    ckf, vf = ck.to(dt), v.to(dt)
     if padk:
         ckf = F.pad(ckf, (0, 0, 0, padk))
         vf = F.pad(vf, (0, 0, 0, padk))
@@ -244,17 +246,19 @@ def calc_linear_unselected(cq, ck, v, sparse_map, BLKQ, BLKK):
     vb = vf.view(B, H, nb, BLKK, D)
     h = ckb.transpose(-1, -2) @ vb                    # (B,H,nb,D,D)
     z = ckb.sum(dim=3)                                # (B,H,nb,D)
-    unsel = (1 - sparse_map.float())                  # (B,H,mb,nb)
+    unsel = (1 - sparse_map.to(dt))                   # (B,H,mb,nb)
     Hi = torch.einsum("bhmn,bhnde->bhmde", unsel, h)
     zi = torch.einsum("bhmn,bhnd->bhmd", unsel, z)
-    out = torch.zeros(B, H, L, D)
-    cqf = cq.float()
+    cqf = cq.to(dt)
+    if bool((unsel.sum(-1) == 0).all()):
+        return torch.zeros(B, H, L, D, dtype=dt) + 0.0 * cqf
+    rows = []
     for i in range(mb):
         r0, r1 = i * BLKQ, min(L, (i + 1) * BLKQ)
         num = cqf[:, :, r0:r1] @ Hi[:, :, i]
         den = 1e-5 + (cqf[:, :, r0:r1] * zi[:, :, i].unsqueeze(2)).sum(-1, keepdim=True)
-        out[:, :, r0:r1] = num / den
-    return out
+        rows.append(num / den)
+    return torch.cat(rows, dim=2)
 
 
 def sla_forward(q, k, v, weight, bias, topk_ratio, feature="softmax", BLKQ=64, BLKK=64,
@@ -296,7 +300,7 @@ def sla_forward_fp(q, k, v, weight, bias, sparse_map, feature="softmax", BLKQ=64
     if linear_scope == "all":
         o_l = calc_linear(cq, ck, v)
     else:
-        raise NotImplementedError
+        o_l = calc_linear_unselected(cq, ck, v, sparse_map, BLKQ, BLKK)
     return o_s + o_l @ weight.t() + bias
 
 

@@ -42,8 +42,7 @@ class SparseLinearAttention(nn.Module):
                 (in the reference both choices select the same function, core.py:43-60).
             linear_scope: not in the reference. "all" (default) is the reference's behaviour: the linear
                 branch sums over every token (core.py:92-96). "unselected" sums, for each query block, over
-                the KV blocks that block did not select (the scope drawn in assets/overview_of_SLA.png);
-                forward only.
+                the KV blocks that block did not select (the scope drawn in assets/overview_of_SLA.png).
         """
         super().__init__()
         self.dtype = torch.bfloat16 if use_bf16 else torch.float16
@@ -88,8 +87,6 @@ class SparseLinearAttention(nn.Module):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         need_grad = torch.is_grad_enabled() and (
             q.requires_grad or k.requires_grad or v.requires_grad or self.proj_l.weight.requires_grad)
-        if need_grad and self.linear_scope == "unselected":
-            raise NotImplementedError("linear_scope='unselected' has no backward: call it under torch.no_grad()")
         bm = None
         if block_map is not None:
             bm = block_map.unpack() if isinstance(block_map, ops.PackedBlockMap) else block_map

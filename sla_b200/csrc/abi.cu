@@ -79,7 +79,7 @@ size_t sla_workspace_bytes(const sla_shape* s, int op) {
     case SLA_OP_BLOCK_MAP: return sla::ws_block_map(s).total;
     case SLA_OP_LINEAR_STATE: return sla::ws_linear_state(s).total;
     case SLA_OP_FWD: return sla::ws_fwd_total(s);
-    case SLA_OP_BWD: return sla::ws_bwd(s).total + sla::ws_sparse_bwd(s).total;
+    case SLA_OP_BWD: return sla::ws_bwd_total(s);
     case SLA_OP_SPARSE_BWD: return sla::ws_sparse_bwd(s).total;
     case SLA_OP_SAGE_FWD: return sla::ws_sage(s).total;
     default: return 0;

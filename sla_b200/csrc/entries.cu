@@ -209,6 +209,63 @@ static int sparse_bwd_impl(const sla_shape* s, const void* q, const void* k, con
   return run_sparse_bwd_mma(s, p, st);
 }
 
+// Backward of sla_fwd with SLA_FLAG_LINEAR_UNSELECTED (algebra: linear_bwd_unselected.cu). `base` is the workspace of
+// sla_bwd: the all-token regions, the sparse backward's, then ws_bwd_unselected; its 16-bit W has been written.
+static int bwd_unselected(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s,
+                          const float* lse, const void* d_o, const int32_t* lut, const int32_t* col_offsets,
+                          const int32_t* col_index, const float* w, const void* lin_state, void* dq, void* dk,
+                          void* dv, float* dw, float* dbias, unsigned char* base, cudaStream_t st) {
+  const WsBwd wb = ws_bwd(s);
+  unsigned char* sparse_ws = base + wb.total;
+  unsigned char* ub = sparse_ws + ws_sparse_bwd(s).total;
+  const WsBwdUnselected wu = ws_bwd_unselected(s);
+  const int nb = ceil_div(s->L, s->BLKK), Lpad = ceil_div(s->L, 128) * 128;
+  const size_t bh = size_t(s->B) * s->H;
+  int rc;
+  // the forward's intermediates again: phi(q), phi(k), and the selected blocks' share C_num, C_den
+  if ((rc = run_feature_map(s, q, ub + wu.phiq, st)) != SLA_OK) return rc;
+  if ((rc = run_feature_map(s, k, ub + wu.phik, st)) != SLA_OK) return rc;
+  FwdParams pc = make_fwd(s, ub + wu.phiq, ub + wu.phik, v, lut, ub + wu.cnum, nullptr,
+                          reinterpret_cast<float*>(ub + wu.cden), nullptr, nullptr);
+  pc.plain = 1;
+  if ((rc = run_sparse_fwd_tc(s, pc, st)) != SLA_OK) return rc;
+  // row pass: -dN, dden, the all-token part of dphi_q (into dq), and the partials of G, dz, db, G2
+  SLA_CUDA_OK(cudaMemsetAsync(ub + wu.stats, 0, bh * Lpad * sizeof(float2), st));
+  UnselBwdParams up;
+  up.phiq = ub + wu.phiq; up.d_o = d_o; up.cnum = ub + wu.cnum;
+  up.cden = reinterpret_cast<const float*>(ub + wu.cden);
+  up.lin_state = lin_state; up.wbits = base + wb.wbits;
+  up.dn_neg = ub + wu.dn_neg; up.dphi = dq;
+  up.stats = reinterpret_cast<float2*>(ub + wu.stats);
+  up.g_partial = reinterpret_cast<float*>(ub + wu.g_partial);
+  up.L = s->L; up.Lpad = Lpad; up.nch = wb.nch; up.rows = wb.rows; up.all_selected = s->topk >= nb ? 1 : 0;
+  if ((rc = run_linear_bwd_unselected_rows(s, up, st)) != SLA_OK) return rc;
+  LinBwdParams lp;
+  lp.q = q; lp.k = k; lp.v = v; lp.d_o = d_o; lp.lin_state = lin_state; lp.wbits = base + wb.wbits; lp.w = w;
+  lp.dq = dq; lp.dk = dk; lp.dv = dv;
+  lp.g_partial = up.g_partial;
+  lp.g_sum = reinterpret_cast<float*>(ub + wu.g_sum);
+  lp.dh = base + wb.dh;
+  lp.dz = reinterpret_cast<float*>(base + wb.dz);
+  lp.dw_part = reinterpret_cast<float*>(base + wb.dw_part);
+  lp.dw = dw; lp.dbias = dbias; lp.L = s->L; lp.nch = wb.nch; lp.rows = wb.rows;
+  lp.g_stride = 2 * s->D * s->D + 2 * s->D; lp.has_g2 = 1;
+  if ((rc = run_linear_bwd_reductions(s, lp, st)) != SLA_OK) return rc;
+  // the product without softmax over the selected blocks, on (phi(q), phi(k), v) with dO = -dN, delta = dden:
+  // dq += dS phi(k) (still a gradient of phi(q)); dk = phi'(k)(v dH^T + dz + dS^T phi(q)); dv = phi(k) dH + P^T dO
+  BwdParams bp;
+  bp.q = ub + wu.phiq; bp.k = ub + wu.phik; bp.v = v; bp.o_s = nullptr; bp.d_o = ub + wu.dn_neg; bp.lse = nullptr;
+  bp.delta = nullptr; bp.lut = lut; bp.col_offsets = col_offsets; bp.col_index = col_index;
+  bp.dq = dq; bp.dk = dk; bp.dv = dv;
+  bp.L = s->L; bp.mb = ceil_div(s->L, s->BLKQ); bp.nb = nb; bp.topk = s->topk;
+  bp.scale = 1.0f; bp.scale_log2 = 1.0f; bp.accumulate = 1;
+  bp.lin_dh = lp.dh; bp.lin_dz = lp.dz; bp.plain = 1;
+  if ((rc = run_sparse_bwd_tc(s, bp, ub + wu.stats, st)) != SLA_OK) return rc;
+  if ((rc = run_feature_map_bwd(s, ub + wu.phiq, dq, st)) != SLA_OK) return rc;   // dq = phi'(q) dphi_q
+  // the softmax branch adds its dq, dk, dv
+  return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 1, st);
+}
+
 int sla_sparse_bwd(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s,
                    const float* lse, const void* do_s, const int32_t* lut, const int32_t* col_offsets,
                    const int32_t* col_index, void* dq, void* dk, void* dv, void* ws, size_t ws_bytes,
@@ -235,17 +292,21 @@ int sla_bwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   if (!all_aligned({q, k, v, o_s, d_o, dq, dk, dv, lin_state, ws})) return SLA_ERR_BAD_ALIGN;
   if (linear_only && (s->flags & SLA_FLAG_SPARSE_ONLY)) return SLA_ERR_UNSUPPORTED;
   WsBwd wb = ws_bwd(s);
-  if (ws_bytes < wb.total + ws_sparse_bwd(s).total) return SLA_ERR_WS_TOO_SMALL;
+  if (ws_bytes < ws_bwd_total(s)) return SLA_ERR_WS_TOO_SMALL;
   unsigned char* base = static_cast<unsigned char*>(ws);
   unsigned char* sparse_ws = base + wb.total;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (s->flags & SLA_FLAG_SPARSE_ONLY)
     return sparse_bwd_impl(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, dq, dk, dv, sparse_ws, 0, st);
   if (!w || !lin_state || !dw || !dbias) return SLA_ERR_NULL;
-  if (s->flags & SLA_FLAG_LINEAR_UNSELECTED) return SLA_ERR_UNSUPPORTED;   // forward-only scope
   const bool legacy = (s->flags & SLA_FLAG_LEGACY_MMA) != 0;
   rc = convert_proj(s, w, nullptr, base + wb.wbits, st);
   if (rc != SLA_OK) return rc;
+  if (s->flags & SLA_FLAG_LINEAR_UNSELECTED) {
+    if (legacy || linear_only || !sparse_bwd_tc_fits(s) || !sparse_fwd_tc_fits(s)) return SLA_ERR_UNSUPPORTED;
+    return bwd_unselected(s, q, k, v, o_s, lse, d_o, lut, col_offsets, col_index, w, lin_state, dq, dk, dv, dw,
+                          dbias, base, st);
+  }
   LinBwdParams lp;
   lp.q = q; lp.k = k; lp.v = v; lp.d_o = d_o; lp.lin_state = lin_state; lp.wbits = base + wb.wbits; lp.w = w;
   lp.dq = dq; lp.dk = dk; lp.dv = dv;

@@ -35,6 +35,11 @@ struct BwdParams {
   // plainly stored, whatever `accumulate` says). lin_dh: [BH][D*D] 16-bit dH, lin_dz: [BH][D] fp32.
   const void* lin_dh = nullptr;
   const float* lin_dz = nullptr;
+  // tcgen05 path only: differentiate the block-sparse product WITHOUT softmax, sum_{j in sel(i)} (q_i k_j^T) v_j and
+  // its row sums (the selected blocks' share of the linear state in the "unselected" scope): P = S, dS = T2 - delta
+  // with `delta` given by the caller in the row statistics (no pre-pass), no softmax scale. With lin_dh set, q and k
+  // are feature maps already and dk = phi'(k) (v dH^T + dz + dK), dv = phi(k) dH + dV.
+  int plain = 0;
 };
 
 struct LinBwdParams {
@@ -53,7 +58,27 @@ struct LinBwdParams {
   int accumulate;         // add to what dq/dk/dv already hold instead of overwriting
   int skip_kv = 0;        // stop after dq and the per-head reductions (dk, dv are produced elsewhere)
   int tc_pass_a = 0;      // run pass A (dq, G, dz, db) as the tcgen05 kernel where it applies
+  // "unselected" linear scope (linear_bwd_unselected.cu): per-chunk partials and per-head sums are records of
+  // g_stride floats {G, dz, db, G2}, and the head's dW is G H - G2
+  int g_stride = 0;       // 0: the default record D*D + 2*D
+  int has_g2 = 0;
 };
+
+// Row pass of the backward of the "unselected" linear scope.
+struct UnselBwdParams {
+  const void *phiq, *d_o, *cnum;   // (BH, L, D) 16-bit: phi(q), dY, C_num
+  const float* cden;               // (BH, L)
+  const void* lin_state;           // H, z, H W^T
+  const void* wbits;               // W 16-bit [n][k]
+  void* dn_neg;                    // out (BH, L, D) 16-bit: -dY W / den
+  void* dphi;                      // out (BH, L, D) 16-bit: the all-token part of dphi_q
+  float2* stats;                   // out (BH, Lpad): {unused, dden}
+  float* g_partial;                // out [BH][NCH][2*D*D + 2*D]
+  int L, Lpad, nch, rows, all_selected;
+};
+int run_linear_bwd_unselected_rows(const sla_shape* s, const UnselBwdParams& p, cudaStream_t st);
+int run_feature_map_bwd(const sla_shape* s, const void* phi, void* dphi_to_dx, cudaStream_t st);
+int run_linear_bwd_reductions(const sla_shape* s, const LinBwdParams& p, cudaStream_t st);
 
 int convert_proj(const sla_shape* s, const float* w, const float* bias, void* out, cudaStream_t st);
 int run_sparse_fwd_mma(const sla_shape* s, const FwdParams& p, bool lin, cudaStream_t st);

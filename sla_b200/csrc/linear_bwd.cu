@@ -193,7 +193,8 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_reduce_kernel(LinBwdPa
   unsigned char* sH = sW + dd * 2;       // [i][k] T
   const int bh = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const float* G = p.g_sum + static_cast<size_t>(bh) * n;
+  const int stride = p.g_stride ? p.g_stride : n;     // floats per head record: {G, dz, db} or {G, dz, db, G2}
+  const float* G = p.g_sum + static_cast<size_t>(bh) * stride;
   const T* hs = static_cast<const T*>(p.lin_state) + static_cast<size_t>(bh) * (2 * dd + D);
   T* dh = static_cast<T*>(p.dh) + static_cast<size_t>(bh) * dd;
   float* dwp = p.dw_part + static_cast<size_t>(bh) * (dd + D);
@@ -228,6 +229,16 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_reduce_kernel(LinBwdPa
     uint32_t a[KS][4];
     load_a_frags<D, KS>(a, sG_a, m0, 0, lane);
     gemm_b_kn<T, D, D / 8, KS>(acc2, a, sH_a, 0, 0, lane);         // rows n of dW_head
+  }
+  if (p.has_g2) {   // "unselected" scope: dW_head = G H - G2
+    const float* G2 = G + dd + 2 * D;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      const int r0 = m0 + g, c = 8 * j + 2 * t;
+      const float2 a = *reinterpret_cast<const float2*>(G2 + r0 * D + c);
+      const float2 b = *reinterpret_cast<const float2*>(G2 + (r0 + 8) * D + c);
+      acc2[j][0] -= a.x; acc2[j][1] -= a.y; acc2[j][2] -= b.x; acc2[j][3] -= b.y;
+    }
   }
 #pragma unroll
   for (int j = 0; j < D / 8; ++j) {
@@ -318,6 +329,29 @@ __global__ void __launch_bounds__(128) linear_bwd_kv_kernel(LinBwdParams p) {
   cp_async_wait<0>();
 }
 
+// Per-head reductions after a row pass: chunk partials -> head sums -> dH (16-bit), dz, the head's dW and db ->
+// dW, db summed over the heads.
+template <typename T, int D>
+static int reductions_typed(const sla_shape* s, const LinBwdParams& p, cudaStream_t st) {
+  const int bh = s->B * s->H, dd = D * D;
+  const int n = p.g_stride ? p.g_stride : dd + 2 * D;
+  linear_bwd_gsum_kernel<<<dim3(ceil_div(n, 256), bh), 256, 0, st>>>(p.g_partial, p.g_sum, p.nch, n);
+  SLA_LAUNCH_OK();
+  auto rk = linear_bwd_reduce_kernel<T, D>;
+  SLA_CUDA_OK(cudaFuncSetAttribute(rk, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * dd * 2));
+  rk<<<bh, D / 16 * 32, 3 * dd * 2, st>>>(p);
+  SLA_LAUNCH_OK();
+  dw_final_kernel<<<ceil_div(dd + D, 256), 256, 0, st>>>(p.dw_part, p.dw, p.dbias, bh, dd, D);
+  SLA_LAUNCH_OK();
+  return SLA_OK;
+}
+
+int run_linear_bwd_reductions(const sla_shape* s, const LinBwdParams& p, cudaStream_t st) {
+  if (s->dtype == SLA_BF16)
+    return s->D == 64 ? reductions_typed<__nv_bfloat16, 64>(s, p, st) : reductions_typed<__nv_bfloat16, 128>(s, p, st);
+  return s->D == 64 ? reductions_typed<__half, 64>(s, p, st) : reductions_typed<__half, 128>(s, p, st);
+}
+
 template <typename T, int D, int FEAT>
 static int launch_lin_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_t st) {
   const int bh = s->B * s->H, dd = D * D;
@@ -331,15 +365,8 @@ static int launch_lin_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_
     SLA_LAUNCH_OK();
   }
   {
-    const int n = dd + 2 * D;
-    linear_bwd_gsum_kernel<<<dim3(ceil_div(n, 256), bh), 256, 0, st>>>(p.g_partial, p.g_sum, p.nch, n);
-    SLA_LAUNCH_OK();
-    auto rk = linear_bwd_reduce_kernel<T, D>;
-    SLA_CUDA_OK(cudaFuncSetAttribute(rk, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * dd * 2));
-    rk<<<bh, D / 16 * 32, 3 * dd * 2, st>>>(p);
-    SLA_LAUNCH_OK();
-    dw_final_kernel<<<ceil_div(dd + D, 256), 256, 0, st>>>(p.dw_part, p.dw, p.dbias, bh, dd, D);
-    SLA_LAUNCH_OK();
+    int rc = reductions_typed<T, D>(s, p, st);
+    if (rc != SLA_OK) return rc;
   }
   if (!p.skip_kv) {
     auto kern = linear_bwd_kv_kernel<T, D, FEAT>;

@@ -46,7 +46,7 @@ __device__ __forceinline__ float ex2q(float x) {
 enum : int { kQErrX = 401, kQErrYFull = 402, kQErrYEmpty = 403, kQErrT1 = 404, kQErrT2 = 405, kQErrT1C = 406,
              kQErrC = 407, kQErrAcc = 408, kQErrDrain = 409 };
 
-template <typename T, int D, int BM>
+template <typename T, int D, int BM, bool PLAIN>
 __global__ void __launch_bounds__(576, 1)
 sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                           const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -330,7 +330,8 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       float pf[32];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        float pv = ex2q(fmaf(__uint_as_float(sv[c]), sc, -my_lse));
+        // PLAIN (BwdParams::plain): no softmax, dS = T2 - delta on the selected blocks whatever the scores are
+        float pv = PLAIN ? 1.0f : ex2q(fmaf(__uint_as_float(sv[c]), sc, -my_lse));
         if (valid < 64 && ch * 32 + c >= valid) pv = 0.f;
         pf[c] = active ? pv : 0.f;
       }
@@ -410,7 +411,7 @@ constexpr int kDqStaticSmem = 1024;   // statically allocated shared memory of t
 
 bool sparse_bwd_dq_pair_fits(const sla_shape* s) { return dq_pair_smem_bytes(s->D, s->topk) + kDqStaticSmem <= 227 * 1024; }
 
-template <typename T, int D, int BM>
+template <typename T, int D, int BM, bool PLAIN>
 static int launch_dq_pair(const sla_shape* s, const BwdParams& bp, const float2* stats, int Lpad, cudaStream_t st) {
   const int bh = s->B * s->H;
   const int smem = dq_pair_smem_bytes(D, bp.topk);
@@ -429,7 +430,7 @@ static int launch_dq_pair(const sla_shape* s, const BwdParams& bp, const float2*
   p.trace = trace_buffer() ? trace_buffer() + 2048 : nullptr;   // behind the two per-entry timelines of the other kernels
   p.L = s->L; p.Lpad = Lpad; p.mb = bp.mb; p.topk = bp.topk; p.accumulate = bp.accumulate;
   p.scale = bp.scale; p.scale_log2 = bp.scale_log2;
-  auto kern = tc::sparse_bwd_dq_pair_kernel<T, D, BM>;
+  auto kern = tc::sparse_bwd_dq_pair_kernel<T, D, BM, PLAIN>;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   kern<<<dim3(ceil_div(s->L, 128), bh), 576, smem, st>>>(tq, tdo, tk, tv, tdq, p);
   SLA_LAUNCH_OK();
@@ -440,12 +441,18 @@ static int launch_dq_pair(const sla_shape* s, const BwdParams& bp, const float2*
 // launched) when the entry list does not fit the kernel's shared memory.
 int run_sparse_bwd_dq_pair(const sla_shape* s, const BwdParams& bp, const void* stats, int Lpad, cudaStream_t st) {
   const float2* sp = static_cast<const float2*>(stats);
-#define SLA_DQ(TT)                                                                                              \
-  if (s->D == 64)                                                                                               \
-    return s->BLKQ == 64 ? launch_dq_pair<TT, 64, 64>(s, bp, sp, Lpad, st) : launch_dq_pair<TT, 64, 128>(s, bp, sp, Lpad, st); \
-  return s->BLKQ == 64 ? launch_dq_pair<TT, 128, 64>(s, bp, sp, Lpad, st) : launch_dq_pair<TT, 128, 128>(s, bp, sp, Lpad, st);
+#define SLA_DQ2(TT, DD, BB) \
+  return bp.plain ? launch_dq_pair<TT, DD, BB, true>(s, bp, sp, Lpad, st) : launch_dq_pair<TT, DD, BB, false>(s, bp, sp, Lpad, st)
+#define SLA_DQ(TT)                                  \
+  if (s->D == 64) {                                 \
+    if (s->BLKQ == 64) SLA_DQ2(TT, 64, 64);         \
+    SLA_DQ2(TT, 64, 128);                           \
+  }                                                 \
+  if (s->BLKQ == 64) SLA_DQ2(TT, 128, 64);          \
+  SLA_DQ2(TT, 128, 128);
   if (s->dtype == SLA_BF16) { SLA_DQ(__nv_bfloat16) }
   SLA_DQ(__half)
+#undef SLA_DQ2
 #undef SLA_DQ
 }
 

@@ -61,7 +61,7 @@ __device__ __forceinline__ void trace_ev(long long* tr, int role, int j, int ev)
 enum : int { kBErrX = 201, kBErrYFull = 202, kBErrYEmpty = 203, kBErrTFull = 204, kBErrCFull = 205,
              kBErrAcc = 206, kBErrDrain = 207, kBErrDh = 208, kBErrPhi = 209, kBErrLin = 210 };
 
-template <typename T, int D, int BM>
+template <typename T, int D, int BM, bool PLAIN>
 __global__ void __launch_bounds__(576, 1)
 sparse_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                      const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
@@ -347,12 +347,19 @@ sparse_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_co
         for (int c = 0; c < 32; c += 2) {
           const float4 st = stc[c >> 1];                                    // {lse, delta} of two query rows
           const float lse0 = st.x, del0 = st.y, lse1 = st.z, del1 = st.w;
-          float p0 = ex2b(__uint_as_float(sv[c]) * sc - lse0);
-          float p1 = ex2b(__uint_as_float(sv[c + 1]) * sc - lse1);
-          if (!key_ok) p0 = p1 = 0.f;                                       // kernel.py:216
+          float p0, p1, w0, w1;                                             // P and the factor of (dP - delta) in dS
+          if (PLAIN) {   // no softmax (BwdParams::plain): K and Q tiles are feature maps
+            p0 = __uint_as_float(sv[c]); p1 = __uint_as_float(sv[c + 1]);   // zero rows (past the end) give S = 0
+            w0 = w1 = 1.0f;
+          } else {
+            p0 = ex2b(__uint_as_float(sv[c]) * sc - lse0);
+            p1 = ex2b(__uint_as_float(sv[c + 1]) * sc - lse1);
+            if (!key_ok) p0 = p1 = 0.f;                                     // kernel.py:216
+            w0 = p0; w1 = p1;
+          }
           pp[c >> 1] = Elem<T>::pack2(p0, p1);
-          ds[c >> 1] = Elem<T>::pack2(p0 * (__uint_as_float(dv[c]) - del0),
-                                      p1 * (__uint_as_float(dv[c + 1]) - del1));   // kernel.py:161 / :224
+          ds[c >> 1] = Elem<T>::pack2(w0 * (__uint_as_float(dv[c]) - del0),
+                                      w1 * (__uint_as_float(dv[c + 1]) - del1));   // kernel.py:161 / :224
         }
       } else {
 #pragma unroll
@@ -402,7 +409,9 @@ sparse_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_co
             x[c8 * 8 + 2 * i] = f.x; x[c8 * 8 + 2 * i + 1] = f.y;
           }
         }
-        if (p.lin_feature == SLA_PHI_SOFTMAX) {
+        if (PLAIN) {
+          // the stationary tile already holds phi(k)
+        } else if (p.lin_feature == SLA_PHI_SOFTMAX) {
           float mx = x[0];
 #pragma unroll
           for (int c = 1; c < CW; ++c) mx = fmaxf(mx, x[c]);
@@ -436,15 +445,21 @@ sparse_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_co
         float ps = 0.f;                                        // sum_i phi_i dphi_i of this group's columns
         if (lin_ok) {
           tc_fence_after();
-          uint32_t tv[CW];
+          uint32_t tv[CW], ak0[CW];
           if constexpr (CW == 32) tmem_ld_x32(tmem + lane_addr + COL_T + c_lo, tv); else tmem_ld_x16(tmem + lane_addr + COL_T + c_lo, tv);
+          if (PLAIN && n_ent > 0) {    // dK of the un-normalised product is a gradient of phi(k): it goes through phi' too
+            if constexpr (CW == 32) tmem_ld_x32(tmem + lane_addr + COL_ACC1 + c_lo, ak0); else tmem_ld_x16(tmem + lane_addr + COL_ACC1 + c_lo, ak0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < CW; ++c) ak0[c] = 0u;
+          }
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < CW; c += 2) {
             const float2 ph = Elem<T>::unpack2(phi[c >> 1]);
             x[c] = ph.x; x[c + 1] = ph.y;
-            dk_out[c] = __uint_as_float(tv[c]) + s_dz[c_lo + c];
-            dk_out[c + 1] = __uint_as_float(tv[c + 1]) + s_dz[c_lo + c + 1];
+            dk_out[c] = __uint_as_float(tv[c]) + s_dz[c_lo + c] + __uint_as_float(ak0[c]);
+            dk_out[c + 1] = __uint_as_float(tv[c + 1]) + s_dz[c_lo + c + 1] + __uint_as_float(ak0[c + 1]);
             ps += ph.x * dk_out[c] + ph.y * dk_out[c + 1];
           }
         }
@@ -463,7 +478,7 @@ sparse_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_co
           }
           // + the sparse branch's dK (times the softmax scale, kernel.py:236); dV already holds both parts
           uint32_t ak[CW], av[CW];
-          if (n_ent > 0) {
+          if (n_ent > 0 && !PLAIN) {
             if constexpr (CW == 32) tmem_ld_x32(tmem + lane_addr + COL_ACC1 + c_lo, ak); else tmem_ld_x16(tmem + lane_addr + COL_ACC1 + c_lo, ak);
           } else {
 #pragma unroll
@@ -613,7 +628,7 @@ static int bwd_tc_smem_bytes(int D, int max_entries) {
 }
 constexpr int kBwdStaticSmem = 8 * 1024;   // statically allocated shared memory of the kernels (barriers, exchange slots)
 
-template <typename T, int D, int BM>
+template <typename T, int D, int BM, bool PLAIN>
 static int launch_dkdv(const sla_shape* s, const BwdParams& bp, const float2* stats, int Lpad, cudaStream_t st) {
   const int bh = s->B * s->H;
   CUtensorMap x1, x2, y1, y2, o1, o2, dh;
@@ -641,7 +656,7 @@ static int launch_dkdv(const sla_shape* s, const BwdParams& bp, const float2* st
   p.max_entries = 2 * bp.mb;            // a KV block may have been selected by every query block
   const int smem = bwd_tc_smem_bytes(D, p.max_entries);
   if (smem + kBwdStaticSmem > 227 * 1024) return SLA_ERR_BAD_SHAPE;
-  auto kern = tc::sparse_bwd_dkdv_kernel<T, D, BM>;
+  auto kern = tc::sparse_bwd_dkdv_kernel<T, D, BM, PLAIN>;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   kern<<<dim3(ceil_div(bp.nb, 2), bh), 576, smem, st>>>(x1, x2, y1, y2, o1, o2, dh, p);
   SLA_LAUNCH_OK();
@@ -653,12 +668,15 @@ static int run_bwd_tc_typed(const sla_shape* s, const BwdParams& bp, float2* sta
   const int bh = s->B * s->H;
   // nothing is launched unless both kernels fit: the caller falls back to another path on BAD_SHAPE
   if (!sparse_bwd_tc_fits(s)) return SLA_ERR_BAD_SHAPE;
-  bwd_prep_kernel<T, D><<<dim3(ceil_div(Lpad, 64), bh), 256, 0, st>>>(
-      static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L, Lpad);
-  SLA_LAUNCH_OK();
+  if (!bp.plain) {   // plain mode: the caller has filled the row statistics
+    bwd_prep_kernel<T, D><<<dim3(ceil_div(Lpad, 64), bh), 256, 0, st>>>(
+        static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L, Lpad);
+    SLA_LAUNCH_OK();
+  }
   int rc = run_sparse_bwd_dq_pair(s, bp, stats, Lpad, st);
   if (rc != SLA_OK) return rc;
-  return launch_dkdv<T, D, BM>(s, bp, stats, Lpad, st);
+  return bp.plain ? launch_dkdv<T, D, BM, true>(s, bp, stats, Lpad, st)
+                  : launch_dkdv<T, D, BM, false>(s, bp, stats, Lpad, st);
 }
 
 // Whether the tcgen05 backward kernels fit this shape (so that a caller can decide what to fuse into them before

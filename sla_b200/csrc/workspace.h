@@ -131,6 +131,39 @@ inline WsSparseBwd ws_sparse_bwd(const sla_shape* s) {
   return w;
 }
 
+// ---- backward of the "unselected" linear scope (behind the two regions above) ----
+struct WsBwdUnselected {
+  size_t phiq, phik, cnum, dn_neg;   // 16-bit [BH][L][D]: phi(q), phi(k), C_num (recomputed), -dN
+  size_t cden;                       // fp32 [BH][L]
+  size_t stats;                      // float2 [BH][Lpad] {unused, dden}
+  size_t g_partial;                  // fp32 [BH][NCH][2*D*D + 2*D]
+  size_t g_sum;                      // fp32 [BH][2*D*D + 2*D]
+  size_t total;
+};
+inline WsBwdUnselected ws_bwd_unselected(const sla_shape* s) {
+  WsBwdUnselected w;
+  const size_t bh = size_t(s->B) * s->H, n = bh * s->L;
+  const size_t lpad = size_t(ws_ceil_div(s->L, 128)) * 128;
+  const size_t rec = 2 * size_t(s->D) * s->D + 2 * s->D;
+  const int nch = ws_bwd(s).nch;
+  size_t o = 0;
+  w.phiq = o;      o += ws_round(n * s->D * 2);
+  w.phik = o;      o += ws_round(n * s->D * 2);
+  w.cnum = o;      o += ws_round(n * s->D * 2);
+  w.dn_neg = o;    o += ws_round(n * s->D * 2);
+  w.cden = o;      o += ws_round(n * 4);
+  w.stats = o;     o += ws_round(bh * lpad * 8);
+  w.g_partial = o; o += ws_round(bh * nch * rec * 4);
+  w.g_sum = o;     o += ws_round(bh * rec * 4);
+  w.total = o;
+  return w;
+}
+inline size_t ws_bwd_total(const sla_shape* s) {
+  size_t t = ws_bwd(s).total + ws_sparse_bwd(s).total;
+  if (s->flags & SLA_FLAG_LINEAR_UNSELECTED) t += ws_bwd_unselected(s).total;
+  return t;
+}
+
 // ---- SageSLA quantized forward ----
 struct WsSage {
   size_t lin;      // linear-state partials (same layout as WsLinearState)

@@ -83,6 +83,8 @@ WORKLOADS = {
     "c5": Workload("c5", 5, 1, 16, 131072, 64, 128, 64, 0.05, feature="relu", grid=(32, 64, 64)),
     "refbench": Workload("refbench", 6, 2, 16, 32760, 128, 128, 64, 0.05, seed=42),
     "tiny": Workload("tiny", 9, 1, 2, 1000, 64, 64, 64, 0.25, grid=(5, 10, 20)),
+    # 2 of c3's 12 heads: the same kernels and per-CTA work on 130 MB of tensors, sized for profiler captures
+    "c3s": Workload("c3s", 3, 1, 2, 32760, 128, 64, 64, 0.05, grid=(21, 30, 52)),
     # 8 of c4's 40 heads: the same kernels and per-CTA work on 0.6 GB of inputs, sized for profiler captures
     "c4s": Workload("c4s", 4, 1, 8, 75600, 128, 128, 64, 0.05, grid=(21, 45, 80), backward=False, quantized=True),
 }

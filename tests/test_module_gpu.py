@@ -150,8 +150,6 @@ def test_unselected_scope_vs_oracle(feat, D, BLKQ, L, ratio):
     # and it differs from the all-token scope (the test would pass vacuously otherwise)
     o_all = O.sla_forward(q, k, v, w, b, ratio, feat, BLKQ, 64, linear_scope="all").float()
     assert (o_all - o_ref.float()).abs().mean() > 5 * (o - o_ref.float()).abs().mean()
-    with pytest.raises(NotImplementedError):
-        m(q.cuda().requires_grad_(True), k.cuda(), v.cuda())
 
 
 @pytest.mark.parametrize("fork", [False, True])
@@ -268,3 +266,52 @@ def test_block_map_reuse_and_packed_form():
     assert torch.equal(o2, ref[0]) and sp == bm.topk / bm.n_blocks
     with pytest.raises(ValueError):
         m(q[:, :1], k[:, :1], v[:, :1], block_map=bm)
+
+
+@pytest.mark.parametrize("feat,D,BLKQ,L,ratio,fp16", [
+    ("softmax", 128, 64, 2000, 0.1, False), ("relu", 64, 128, 1100, 0.25, False), ("elu", 128, 128, 900, 0.2, False),
+    ("softmax", 64, 64, 1024, 0.25, True), ("softmax", 128, 64, 320, 1.0, False), ("relu", 128, 64, 191, 0.34, False)])
+def test_unselected_scope_backward_vs_oracle_autograd(feat, D, BLKQ, L, ratio, fp16):
+    """Gradients of linear_scope='unselected' (unpinned: no reference code has this scope) against the fp64
+    autograd of the CPU restatement, which sums per-block states over the blocks a query block did not select.
+    proj_l is given weights large enough for the linear branch to carry a fair share of every gradient. The case
+    with ratio 1 selects every block: the branch is then defined as 0 and only the bias gradient flows through it."""
+    import sla_b200
+    from oracle import sla_oracle as O
+    dt = torch.float16 if fp16 else torch.bfloat16
+    g = torch.Generator().manual_seed(3 * L + D)
+    B, H = 1, 2
+    q, k, v, do = (torch.randn(B, H, L, D, generator=g).to(dt) for _ in range(4))
+    w = torch.randn(D, D, generator=g) / D ** 0.5
+    b = torch.randn(D, generator=g) * 0.05
+    m = sla_b200.SparseLinearAttention(D, ratio, feat, BLKQ, 64, use_bf16=not fp16, linear_scope="unselected").cuda()
+    with torch.no_grad():
+        m.proj_l.weight.copy_(w)
+        m.proj_l.bias.copy_(b)
+    qg, kg, vg = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o = m(qg, kg, vg)
+    o.backward(do.cuda())
+    smap, _, _ = O.get_block_map(q, k, ratio, BLKQ, 64)
+    qd, kd, vd = (t.double().requires_grad_(True) for t in (q, k, v))
+    wd, bd = w.double().requires_grad_(True), b.double().requires_grad_(True)
+    o_ref = O.sla_forward_fp(qd, kd, vd, wd, bd, smap, feat, BLKQ, 64, linear_scope="unselected")
+    o_ref.backward(do.double())
+    assert_close_parity(o.detach().float().cpu(), o_ref.detach(), what="o")
+    assert_close_parity(qg.grad.float().cpu(), qd.grad, what="dq")
+    assert_close_parity(kg.grad.float().cpu(), kd.grad, what="dk")
+    assert_close_parity(vg.grad.float().cpu(), vd.grad, what="dv")
+    assert_close_parity(m.proj_l.weight.grad.cpu(), wd.grad, l1_max=2e-2, what="dw")
+    assert_close_parity(m.proj_l.bias.grad.cpu(), bd.grad, l1_max=2e-2, what="db")
+    # the linear branch's own share of the gradients (total minus the sparse-only operator's)
+    from sla_b200 import ops
+    bm = ops.block_map(q.cuda(), k.cuda(), ratio, BLKQ, 64, want_map=True, want_cols=True)
+    q2, k2, v2 = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    ops._attention.apply(q2, k2, v2, bm.sparse_map, bm.lut.long(), bm.topk, BLKQ, 64).backward(do.cuda())
+    q3, k3, v3 = (t.double().requires_grad_(True) for t in (q, k, v))
+    O.sparse_fwd_dense(q3, k3, v3, smap, BLKQ, 64)[0].backward(do.double())
+    if ratio < 1.0:
+        for n, a, a_s, r, r_s in (("dq", qg.grad, q2.grad, qd.grad, q3.grad), ("dk", kg.grad, k2.grad, kd.grad, k3.grad),
+                                  ("dv", vg.grad, v2.grad, vd.grad, v3.grad)):
+            # a difference of two 16-bit tensors: it carries the rounding of the (larger) totals
+            assert_close_parity((a.float() - a_s.float()).cpu(), r - r_s, cos_min=0.98, l1_max=2e-1,
+                                what=f"linear share of {n}")
