@@ -602,6 +602,28 @@ def main():
     def k_map():
         ops.block_map(q, k, w.topk, BLKQ, BLKK, want_cols=True)
 
+    # the fused front end (per-head RMS norm + rotary embedding + block sums) and the mask prediction from its sums
+    front = {}
+    if True:
+        gain = torch.ones(w.D, device=dev)
+        pos = torch.arange(w.L, device=dev, dtype=torch.float32)[:, None]
+        inv = 10000.0 ** (-torch.arange(w.D // 2, device=dev, dtype=torch.float32) / (w.D // 2))
+        rc, rs = torch.cos(pos * inv), torch.sin(pos * inv)
+        q_f, k_f = torch.empty_like(q), torch.empty_like(k)
+        holder = {}
+
+        def k_front():
+            holder["p"] = ops.qk_norm_rope_pool(q, k, gain, gain, rc, rs, 1e-6, True, BLKQ, BLKK)[2]
+
+        def k_map_pooled():
+            ops.block_map_pooled(holder["p"], w.topk, want_cols=True)
+
+        fr_ms = timed(k_front, args.steps, 3, torch.cuda.synchronize)
+        mp_ms = timed(k_map_pooled, args.steps, 3, torch.cuda.synchronize)
+        front = {"qk_norm_rope_pool": {"ms": fr_ms, "gbs": 4 * tensor_bytes / fr_ms / 1e6},
+                 "block_map_from_sums": {"ms": mp_ms}}
+        del q_f, k_f, holder
+
     kf_ms = timed(k_fwd, args.steps, 3, torch.cuda.synchronize)
     if bwd:
         k_fwd()
@@ -613,6 +635,7 @@ def main():
         "sparse_fwd": {"ms": kf_ms, "tflops": fwd_flops / kf_ms / 1e9},
         "block_map": {"ms": km_ms, "gbs": 2 * tensor_bytes / km_ms / 1e6},
     }
+    kernels.update(front)
     if bwd:
         kernels["sparse_bwd_dq_dkdv"] = {"ms": kb_ms, "tflops": bwd_flops / kb_ms / 1e9}
     # DRAM bytes per launch from the committed ncu captures (profiles/tcgen05_sparse_kernels_c3.md,

@@ -129,6 +129,30 @@ SLA_API int sla_block_map(const sla_shape* shape, int in_dtype, const void* q, c
                   int32_t* lut, int8_t* sparse_map, int32_t* col_offsets, int32_t* col_index,
                   void* ws, size_t ws_bytes, sla_stream_t stream);
 
+/* The step before the path, fused with the first pass of the mask prediction. The attention layer of a video DiT
+ * produces q and k, normalises each head's rows (RMS norm with a learned gain) and rotates them (rotary position
+ * embedding) before it calls the operator (the caller of sparse_linear_attention/core.py:69); sla_block_map then reads q
+ * once and k twice again. This entry point applies
+ *     y = x * rsqrt(mean_D(x^2) + eps) * gain            (skipped for a NULL gain)
+ *     (a, b) -> (a cos - b sin, a sin + b cos) per pair  (skipped for NULL tables; rope_cos, rope_sin: (L, D/2) fp32;
+ *                                                         pairs (y[2i], y[2i+1]) if `interleaved`, else (y[i], y[i+D/2]))
+ * to q_in, k_in (shape.dtype, 16-bit), writes q_out, k_out (may alias the inputs) and leaves in `pooled_sums`
+ * (sla_pooled_sums_bytes) the fp32 per-block column sums of the rows it wrote. sla_block_map_pooled finishes the
+ * prediction from those sums without touching q or k. No counterpart in the reference. */
+SLA_API size_t sla_pooled_sums_bytes(const sla_shape* shape);
+SLA_API int sla_qk_norm_rope_pool(const sla_shape* shape, const void* q_in, const void* k_in, const float* gain_q,
+                                  const float* gain_k, const float* rope_cos, const float* rope_sin, float eps,
+                                  int interleaved, void* q_out, void* k_out, void* pooled_sums, size_t sums_bytes,
+                                  sla_stream_t stream);
+/* sla_block_map from the block sums of sla_qk_norm_rope_pool (workspace: sla_workspace_bytes(shape, SLA_OP_BLOCK_MAP);
+ * shape.dtype is the dtype q and k were written in). One rounding point differs from utils.py:56 + :40: the reference
+ * rounds every element of k - mean(k) to the tensor dtype before pooling, this takes round(block mean - mean(k)). The
+ * pooled K values differ by a fraction of a unit in the last place, so a row's selection can differ from
+ * sla_block_map's where two scores are within rounding of each other at the k-th place. */
+SLA_API int sla_block_map_pooled(const sla_shape* shape, const void* pooled_sums, int32_t* lut, int8_t* sparse_map,
+                                 int32_t* col_offsets, int32_t* col_index, void* ws, size_t ws_bytes,
+                                 sla_stream_t stream);
+
 /* Builds the per-KV-block query-block lists from a 0/1 block map. Stands in for the way
  * sparse_linear_attention/kernel.py:208-210 consults k_block_id inside the dK/dV kernel: callers
  * that bring their own sparse_map (the `_attention.apply` signature, kernel.py:242) convert it once. */

@@ -19,7 +19,8 @@ FLAG_SPARSE_ONLY, FLAG_LEGACY_MMA, FLAG_LINEAR_UNSELECTED, FLAG_STATE_READY, FLA
 # every symbol include/sla_b200.h declares
 EXPORTS = (
     "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_debug_set_trace", "sla_debug_set_wait_limit_ns", "sla_debug_drop_first_k_tile", "sla_topk_count", "sla_workspace_bytes", "sla_kernel_path",
-    "sla_block_map", "sla_column_lists", "sla_index_convert", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_linear_state_static", "sla_fwd", "sla_fwd_prepare", "sla_bwd",
+    "sla_block_map", "sla_column_lists", "sla_index_convert", "sla_pooled_sums_bytes", "sla_qk_norm_rope_pool",
+    "sla_block_map_pooled", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_linear_state_static", "sla_fwd", "sla_fwd_prepare", "sla_bwd",
     "sage_sla_fwd", "sage_sla_prepare",
 )
 
@@ -67,6 +68,12 @@ def _load() -> C.CDLL:
     lib.sla_workspace_bytes.argtypes = [sp, C.c_int]
     lib.sla_block_map.restype = C.c_int
     lib.sla_block_map.argtypes = [sp, C.c_int, vp, vp, i32p, i8p, i32p, i32p, vp, C.c_size_t, vp]
+    lib.sla_pooled_sums_bytes.restype = C.c_size_t
+    lib.sla_pooled_sums_bytes.argtypes = [sp]
+    lib.sla_qk_norm_rope_pool.restype = C.c_int
+    lib.sla_qk_norm_rope_pool.argtypes = [sp, vp, vp, f32p, f32p, f32p, f32p, C.c_float, C.c_int, vp, vp, vp, C.c_size_t, vp]
+    lib.sla_block_map_pooled.restype = C.c_int
+    lib.sla_block_map_pooled.argtypes = [sp, vp, i32p, i8p, i32p, i32p, vp, C.c_size_t, vp]
     lib.sla_index_convert.restype = C.c_int
     lib.sla_index_convert.argtypes = [vp, C.c_int, vp, C.c_int, C.c_size_t, vp]
     lib.sla_column_lists.restype = C.c_int

@@ -75,6 +75,17 @@ class SparseLinearAttention(nn.Module):
         return ops.block_map(q.contiguous(), k.contiguous(), self.topk, self.BLKQ, self.BLKK,
                              want_cols=with_column_lists)
 
+    def norm_rope_and_predict(self, q, k, gain_q=None, gain_k=None, rope_cos=None, rope_sin=None, eps=1e-6,
+                              interleaved=True, with_column_lists=True, inplace=False):
+        R"""Not in the reference: the layer's per-head RMS norm and rotary embedding of q and k fused with the first
+        pass of the mask prediction (`ops.qk_norm_rope_pool` + `ops.block_map_pooled`), for callers that would otherwise
+        run those as separate passes over q and k in front of `forward`. q, k: (B, H, L, D) in this module's compute
+        dtype. Returns (q_out, k_out, block_map): call ``forward(q_out, k_out, v, block_map=block_map)``. Forward only
+        (no autograd through the norm and the rotation)."""
+        q_out, k_out, pooled = ops.qk_norm_rope_pool(q.contiguous(), k.contiguous(), gain_q, gain_k, rope_cos, rope_sin,
+                                                     eps, interleaved, self.BLKQ, self.BLKK, inplace)
+        return q_out, k_out, ops.block_map_pooled(pooled, self.topk, want_cols=with_column_lists)
+
     def forward(self, q, k, v, return_sparsity=False, block_map=None):
         R"""
         Args:

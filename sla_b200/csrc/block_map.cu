@@ -330,6 +330,10 @@ __global__ void __launch_bounds__(1024) col_count_kernel(const int8_t* __restric
 }
 
 template <typename TIn, int D>
+static int score_and_select(const sla_shape* s, const TIn* pq, const TIn* pk, int32_t* lut, int8_t* sparse_map,
+                            int32_t* col_offsets, int32_t* col_index, cudaStream_t st);
+
+template <typename TIn, int D>
 static int launch_block_map(const sla_shape* s, const TIn* q, const TIn* k, int32_t* lut, int8_t* sparse_map,
                             int32_t* col_offsets, int32_t* col_index, unsigned char* ws, cudaStream_t st) {
   const int bh = s->B * s->H, L = s->L;
@@ -348,6 +352,16 @@ static int launch_block_map(const sla_shape* s, const TIn* q, const TIn* k, int3
   SLA_LAUNCH_OK();
   pool_kernel<TIn, D><<<dim3(max(mb, nb), bh, 2), 256, 0, st>>>(q, k, kmean, pq, pk, L, s->BLKQ, s->BLKK);
   SLA_LAUNCH_OK();
+  return score_and_select<TIn, D>(s, pq, pk, lut, sparse_map, col_offsets, col_index, st);
+}
+
+// pooled Q, pooled smoothed K (in the input dtype) -> LUT, optional 0/1 map and column lists
+template <typename TIn, int D>
+static int score_and_select(const sla_shape* s, const TIn* pq, const TIn* pk, int32_t* lut, int8_t* sparse_map,
+                            int32_t* col_offsets, int32_t* col_index, cudaStream_t st) {
+  const int bh = s->B * s->H, L = s->L;
+  const int mb = ceil_div(L, s->BLKQ), nb = ceil_div(L, s->BLKK);
+  const bool want_cols = col_offsets != nullptr && col_index != nullptr;
   if (want_cols) SLA_CUDA_OK(cudaMemsetAsync(col_offsets, 0, sizeof(int32_t) * size_t(bh) * (nb + 1), st));
   size_t smem = (size_t(kTopkRows) * (2 * D + nb) * 4 + 15) / 16 * 16 + size_t(kScoreStages) * 2 * kTopkRows * 32 * 16;
   if (smem > 200 * 1024) return SLA_ERR_BAD_SHAPE;
@@ -386,6 +400,243 @@ int run_k_mean(const sla_shape* s, const void* k, float* partial, float* kmean, 
 }
 
 }  // namespace sla
+
+namespace sla {
+// ---- 8. the step before the path: per-head RMS norm and rotary embedding of q and k, with the block sums the mask
+// prediction needs taken from the rows while they are in registers ----
+// One CTA = one block of rows of one head (z = 0: a query block, z = 1: a KV block). A row is spread over D/8
+// threads with 16-byte loads and stores. Per row: y = x * rsqrt(mean(x^2) + eps) * g (skipped when g is NULL), then
+// the rotation of each pair by the row's angles (skipped when cos is NULL): pairs are (y[2i], y[2i+1]) when
+// `interleaved`, else (y[i], y[i + D/2]). The result is rounded to T, stored, and the ROUNDED values are summed per
+// column into sums[bh][block][D] (fp32): the mask prediction then starts from the same bits a separate pooling
+// pass over the stored tensor would read.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) qk_norm_rope_pool_kernel(
+    const T* __restrict__ q_in, const T* __restrict__ k_in, const float* __restrict__ gq, const float* __restrict__ gk,
+    const float* __restrict__ cs, const float* __restrict__ sn, float eps, int interleaved, T* __restrict__ q_out,
+    T* __restrict__ k_out, float* __restrict__ qsum, float* __restrict__ ksum, int L, int blkq, int blkk) {
+  constexpr int TPR = D / 8;       // threads per row
+  constexpr int RP = 256 / TPR;    // rows per pass
+  __shared__ float red[RP][D];
+  const bool is_k = blockIdx.z == 1;
+  const int blk = is_k ? blkk : blkq;
+  const int nblk = (L + blk - 1) / blk;
+  if (static_cast<int>(blockIdx.x) >= nblk) return;
+  const int bh = blockIdx.y, ib = blockIdx.x;
+  const int tid = threadIdx.x, rg = tid / TPR, c = (tid % TPR) * 8;
+  const int row0 = ib * blk, row1 = min(L, row0 + blk);
+  const T* src = (is_k ? k_in : q_in) + static_cast<size_t>(bh) * L * D;
+  T* dst = (is_k ? k_out : q_out) + static_cast<size_t>(bh) * L * D;
+  const float* gw = is_k ? gk : gq;
+  float g8[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) g8[i] = gw ? gw[c + i] : 1.f;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  // every thread runs the same number of passes (the shuffles below need the whole row group); rows past the
+  // block are computed on zeros and dropped
+  const int passes = (blk + RP - 1) / RP;
+  for (int it = 0; it < passes; ++it) {
+    const int r = row0 + it * RP + rg;
+    const bool live = r < row1;
+    float x[8];
+    if (live) {
+      uint4 raw = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * D + c);
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = Elem<T>::unpack2(w[i]);
+        x[2 * i] = f.x; x[2 * i + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = 0.f;
+    }
+    if (gw != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+      for (int o = 1; o < TPR; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float inv = rsqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = x[i] * inv * g8[i];
+    }
+    if (cs != nullptr) {
+      const int rr = live ? r : 0;
+      const float* cr = cs + static_cast<size_t>(rr) * (D / 2);
+      const float* sr = sn + static_cast<size_t>(rr) * (D / 2);
+      if (interleaved) {
+        const float4 c4 = *reinterpret_cast<const float4*>(cr + c / 2), s4 = *reinterpret_cast<const float4*>(sr + c / 2);
+        const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float a = x[2 * i], b = x[2 * i + 1];
+          x[2 * i] = a * cc[i] - b * sv[i];
+          x[2 * i + 1] = a * sv[i] + b * cc[i];
+        }
+      } else {
+        // the partner of column j is column j +- D/2, held by the lane TPR/2 away in the same row group
+        const bool upper = c >= D / 2;
+        const int j0 = upper ? c - D / 2 : c;
+        const float4 ca = *reinterpret_cast<const float4*>(cr + j0), cb = *reinterpret_cast<const float4*>(cr + j0 + 4);
+        const float4 sa = *reinterpret_cast<const float4*>(sr + j0), sb = *reinterpret_cast<const float4*>(sr + j0 + 4);
+        const float cc[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+        const float sv[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, x[i], TPR / 2);
+          x[i] = upper ? x[i] * cc[i] + other * sv[i] : x[i] * cc[i] - other * sv[i];
+        }
+      }
+    }
+    uint4 outv;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&outv);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      ow[i] = Elem<T>::pack2(x[2 * i], x[2 * i + 1]);
+      const float2 f = Elem<T>::unpack2(ow[i]);
+      if (live) { acc[2 * i] += f.x; acc[2 * i + 1] += f.y; }
+    }
+    if (live) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * D + c) = outv;
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[rg][c + i] = acc[i];
+  __syncthreads();
+  if (tid < D) {
+    float sm = 0.f;
+#pragma unroll 4
+    for (int g = 0; g < RP; ++g) sm += red[g][tid];
+    float* out = (is_k ? ksum : qsum) + (static_cast<size_t>(bh) * nblk + ib) * D;
+    out[tid] = sm;
+  }
+}
+
+// Block sums -> what score_topk reads: kmean = round_T(sum_blocks ksum / L); pooled_q = round_T(qsum / nx);
+// pooled_k = round_T(ksum / nx - kmean). The last line is where this path departs from utils.py:56 + :40, which
+// round every element of k - mean(k) to T before pooling: the block mean of those rounding errors (well below one
+// unit in the last place of the pooled value) is not reproduced.
+template <typename TIn>
+__global__ void __launch_bounds__(128) pooled_kmean_kernel(const float* __restrict__ ksum, float* __restrict__ kmean,
+                                                           int L, int nb, int D) {
+  const int bh = blockIdx.x, d = threadIdx.x;
+  if (d >= D) return;
+  float s = 0.f;
+  for (int j = 0; j < nb; ++j) s += ksum[(static_cast<size_t>(bh) * nb + j) * D + d];
+  kmean[static_cast<size_t>(bh) * D + d] = round_to<TIn>(s / static_cast<float>(L));
+}
+template <typename TIn>
+__global__ void __launch_bounds__(256) pooled_finalize_kernel(const float* __restrict__ qsum, const float* __restrict__ ksum,
+                                                              const float* __restrict__ kmean, TIn* __restrict__ pq,
+                                                              TIn* __restrict__ pk, int L, int blkq, int blkk, int D) {
+  const bool is_k = blockIdx.z == 1;
+  const int blk = is_k ? blkk : blkq;
+  const int nblk = (L + blk - 1) / blk;
+  const int bh = blockIdx.y;
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= nblk * D) return;
+  const int ib = i / D, d = i % D;
+  const float nx = static_cast<float>(min(L, (ib + 1) * blk) - ib * blk);
+  const size_t o = static_cast<size_t>(bh) * nblk * D + i;
+  if (is_k) pk[o] = Elem<TIn>::from_f(ksum[o] / nx - kmean[static_cast<size_t>(bh) * D + d]);
+  else pq[o] = Elem<TIn>::from_f(qsum[o] / nx);
+}
+
+static size_t pooled_sums_bytes(const sla_shape* s) {
+  const size_t bh = size_t(s->B) * s->H;
+  return ws_round(bh * ceil_div(s->L, s->BLKQ) * s->D * 4) + ws_round(bh * ceil_div(s->L, s->BLKK) * s->D * 4);
+}
+
+template <typename T, int D>
+static int qk_prepare_typed(const sla_shape* s, const T* q_in, const T* k_in, const float* gq, const float* gk,
+                            const float* cs, const float* sn, float eps, int interleaved, T* q_out, T* k_out,
+                            unsigned char* sums, cudaStream_t st) {
+  const int bh = s->B * s->H, mb = ceil_div(s->L, s->BLKQ), nb = ceil_div(s->L, s->BLKK);
+  float* qsum = reinterpret_cast<float*>(sums);
+  float* ksum = reinterpret_cast<float*>(sums + ws_round(size_t(bh) * mb * s->D * 4));
+  qk_norm_rope_pool_kernel<T, D><<<dim3(max(mb, nb), bh, 2), 256, 0, st>>>(q_in, k_in, gq, gk, cs, sn, eps, interleaved,
+                                                                            q_out, k_out, qsum, ksum, s->L, s->BLKQ,
+                                                                            s->BLKK);
+  SLA_LAUNCH_OK();
+  return SLA_OK;
+}
+
+template <typename TIn, int D>
+static int block_map_pooled_typed(const sla_shape* s, const unsigned char* sums, int32_t* lut, int8_t* sparse_map,
+                                  int32_t* col_offsets, int32_t* col_index, unsigned char* ws, cudaStream_t st) {
+  const int bh = s->B * s->H, mb = ceil_div(s->L, s->BLKQ), nb = ceil_div(s->L, s->BLKK);
+  const float* qsum = reinterpret_cast<const float*>(sums);
+  const float* ksum = reinterpret_cast<const float*>(sums + ws_round(size_t(bh) * mb * s->D * 4));
+  WsBlockMap w = ws_block_map(s);
+  float* kmean = reinterpret_cast<float*>(ws + w.kmean);
+  TIn* pq = reinterpret_cast<TIn*>(ws + w.pooled_q);
+  TIn* pk = reinterpret_cast<TIn*>(ws + w.pooled_k);
+  if (col_offsets != nullptr && sparse_map == nullptr) sparse_map = reinterpret_cast<int8_t*>(ws + w.map);
+  pooled_kmean_kernel<TIn><<<bh, 128, 0, st>>>(ksum, kmean, s->L, nb, D);
+  SLA_LAUNCH_OK();
+  pooled_finalize_kernel<TIn><<<dim3(ceil_div(max(mb, nb) * D, 256), bh, 2), 256, 0, st>>>(qsum, ksum, kmean, pq, pk, s->L,
+                                                                                          s->BLKQ, s->BLKK, D);
+  SLA_LAUNCH_OK();
+  return score_and_select<TIn, D>(s, pq, pk, lut, sparse_map, col_offsets, col_index, st);
+}
+}  // namespace sla
+
+extern "C" size_t sla_pooled_sums_bytes(const sla_shape* s) { return s ? sla::pooled_sums_bytes(s) : 0; }
+
+extern "C" int sla_qk_norm_rope_pool(const sla_shape* s, const void* q_in, const void* k_in, const float* gq,
+                                     const float* gk, const float* rope_cos, const float* rope_sin, float eps,
+                                     int interleaved, void* q_out, void* k_out, void* pooled_sums, size_t sums_bytes,
+                                     sla_stream_t stream) {
+  using namespace sla;
+  if (!s || !q_in || !k_in || !q_out || !k_out || !pooled_sums) return SLA_ERR_NULL;
+  if ((rope_cos == nullptr) != (rope_sin == nullptr)) return SLA_ERR_NULL;
+  if (s->B < 1 || s->H < 1 || s->L < 1 || (s->D != 64 && s->D != 128)) return SLA_ERR_BAD_SHAPE;
+  if (s->BLKQ < 16 || s->BLKK < 16 || s->BLKQ > 1024 || s->BLKK > 1024) return SLA_ERR_BAD_SHAPE;
+  if (static_cast<long long>(s->B) * s->H > 65535) return SLA_ERR_BAD_SHAPE;
+  if (s->dtype != SLA_BF16 && s->dtype != SLA_FP16) return SLA_ERR_BAD_DTYPE;
+  if (!aligned16(q_in) || !aligned16(k_in) || !aligned16(q_out) || !aligned16(k_out) || !aligned16(pooled_sums) ||
+      !aligned16(rope_cos) || !aligned16(rope_sin))
+    return SLA_ERR_BAD_ALIGN;
+  if (sums_bytes < pooled_sums_bytes(s)) return SLA_ERR_WS_TOO_SMALL;
+  int rc = check_device_arch();
+  if (rc != SLA_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned char* sums = static_cast<unsigned char*>(pooled_sums);
+#define SLA_QKP(TT, DD) \
+  return qk_prepare_typed<TT, DD>(s, static_cast<const TT*>(q_in), static_cast<const TT*>(k_in), gq, gk, rope_cos, \
+                                  rope_sin, eps, interleaved, static_cast<TT*>(q_out), static_cast<TT*>(k_out), sums, st)
+  if (s->dtype == SLA_BF16) { if (s->D == 64) SLA_QKP(__nv_bfloat16, 64); SLA_QKP(__nv_bfloat16, 128); }
+  if (s->D == 64) SLA_QKP(__half, 64);
+  SLA_QKP(__half, 128);
+#undef SLA_QKP
+}
+
+extern "C" int sla_block_map_pooled(const sla_shape* s, const void* pooled_sums, int32_t* lut, int8_t* sparse_map,
+                                    int32_t* col_offsets, int32_t* col_index, void* ws, size_t ws_bytes,
+                                    sla_stream_t stream) {
+  using namespace sla;
+  if (!s || !pooled_sums || !lut || !ws) return SLA_ERR_NULL;
+  if (s->B < 1 || s->H < 1 || s->L < 1 || (s->D != 64 && s->D != 128)) return SLA_ERR_BAD_SHAPE;
+  if (s->BLKQ < 16 || s->BLKK < 16 || s->BLKQ > 1024 || s->BLKK > 1024) return SLA_ERR_BAD_SHAPE;
+  if (static_cast<long long>(s->B) * s->H > 65535) return SLA_ERR_BAD_SHAPE;
+  if (s->dtype != SLA_BF16 && s->dtype != SLA_FP16) return SLA_ERR_BAD_DTYPE;
+  if (s->topk < 1 || s->topk > ceil_div(s->L, s->BLKK)) return SLA_ERR_BAD_TOPK;
+  if ((col_offsets == nullptr) != (col_index == nullptr)) return SLA_ERR_NULL;
+  if (!aligned16(pooled_sums) || !aligned16(ws)) return SLA_ERR_BAD_ALIGN;
+  if (ws_bytes < ws_block_map(s).total) return SLA_ERR_WS_TOO_SMALL;
+  int rc = check_device_arch();
+  if (rc != SLA_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned char* sums = static_cast<const unsigned char*>(pooled_sums);
+  unsigned char* w = static_cast<unsigned char*>(ws);
+#define SLA_BMP(TT, DD) \
+  return block_map_pooled_typed<TT, DD>(s, sums, lut, sparse_map, col_offsets, col_index, w, st)
+  if (s->dtype == SLA_BF16) { if (s->D == 64) SLA_BMP(__nv_bfloat16, 64); SLA_BMP(__nv_bfloat16, 128); }
+  if (s->D == 64) SLA_BMP(__half, 64);
+  SLA_BMP(__half, 128);
+#undef SLA_BMP
+}
 
 namespace sla {
 // ---- 7. packed block lists: block indices fit 16 bits while N_BLOCKS, M_BLOCKS <= 65536 ----

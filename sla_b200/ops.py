@@ -126,6 +126,61 @@ def block_map(q: torch.Tensor, k: torch.Tensor, topk_ratio: float, BLKQ: int = 6
     return BlockMap(lut, topk, nb, smap, co, ci)
 
 
+@dataclass
+class PooledSums:
+    """Per-block column sums of q and k left by `qk_norm_rope_pool` (fp32, the library's own layout)."""
+    buf: torch.Tensor
+    shape: tuple          # (B, H, L, D)
+    dtype: torch.dtype
+    BLKQ: int
+    BLKK: int
+
+
+def qk_norm_rope_pool(q, k, gain_q=None, gain_k=None, rope_cos=None, rope_sin=None, eps: float = 1e-6,
+                      interleaved: bool = True, BLKQ: int = 64, BLKK: int = 64, inplace: bool = False):
+    """The step in front of the operator in a DiT attention layer -- per-head RMS norm with a learned gain, then the
+    rotary embedding -- in one pass over q and k that also takes the block sums the mask prediction needs.
+    q, k: (B, H, L, D) bf16/fp16; gains: (D,) fp32 or None; rope_cos, rope_sin: (L, D/2) fp32 or None; pairs are
+    (x[2i], x[2i+1]) when `interleaved`, else (x[i], x[i + D/2]). Returns (q_out, k_out, PooledSums); hand the last to
+    `block_map_pooled`."""
+    _require_cuda(q, k, gain_q, gain_k, rope_cos, rope_sin)
+    assert q.is_contiguous() and k.is_contiguous() and q.shape == k.shape and q.dtype == k.dtype
+    if q.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("qk_norm_rope_pool takes bf16 or fp16 tensors")
+    B, H, L, D = q.shape
+    f32 = lambda t: None if t is None else t.detach().to(torch.float32).contiguous()
+    gain_q, gain_k, rope_cos, rope_sin = f32(gain_q), f32(gain_k), f32(rope_cos), f32(rope_sin)
+    if rope_cos is not None and tuple(rope_cos.shape) != (L, D // 2):
+        raise ValueError("rope tables must be (L, D/2)")
+    shape = SlaShape(B, H, L, D, BLKQ, BLKK, 1, _DT[q.dtype], 0, 0, 0.0)
+    q_out, k_out = (q, k) if inplace else (torch.empty_like(q), torch.empty_like(k))
+    sums = torch.empty(int(lib.sla_pooled_sums_bytes(C.byref(shape))), dtype=torch.uint8, device=q.device)
+    check(lib.sla_qk_norm_rope_pool(C.byref(shape), _p(q), _p(k), _p(gain_q), _p(gain_k), _p(rope_cos), _p(rope_sin),
+                                    float(eps), 1 if interleaved else 0, _p(q_out), _p(k_out), _p(sums), sums.numel(),
+                                    _stream(q)))
+    return q_out, k_out, PooledSums(sums, (B, H, L, D), q.dtype, BLKQ, BLKK)
+
+
+def block_map_pooled(pooled: PooledSums, topk_ratio: float, want_map: bool = False, want_cols: bool = False) -> BlockMap:
+    """Mask prediction from the block sums of `qk_norm_rope_pool`: no further pass over q or k. One rounding point
+    differs from `block_map` (see sla_block_map_pooled in the header), so rows whose k-th and (k+1)-th scores are
+    within rounding of each other can select differently."""
+    B, H, L, D = pooled.shape
+    BLKQ, BLKK = pooled.BLKQ, pooled.BLKK
+    mb, nb = (L + BLKQ - 1) // BLKQ, (L + BLKK - 1) // BLKK
+    topk = _lib.topk_count(nb, topk_ratio)
+    shape = SlaShape(B, H, L, D, BLKQ, BLKK, topk, _DT[pooled.dtype], 0, 0, 0.0)
+    dev = pooled.buf.device
+    lut = torch.empty((B, H, mb, max(topk, 0)), dtype=torch.int32, device=dev)
+    smap = torch.empty((B, H, mb, nb), dtype=torch.int8, device=dev) if (want_map or want_cols) else None
+    co = torch.empty((B, H, nb + 1), dtype=torch.int32, device=dev) if want_cols else None
+    ci = torch.empty((B, H, mb * max(topk, 0)), dtype=torch.int32, device=dev) if want_cols else None
+    ws = _workspace(shape, _lib.OP_BLOCK_MAP, dev)
+    check(lib.sla_block_map_pooled(C.byref(shape), _p(pooled.buf), _p(lut), _p(smap), _p(co), _p(ci), _p(ws), ws.numel(),
+                                   torch.cuda.current_stream(dev).cuda_stream))
+    return BlockMap(lut, topk, nb, smap, co, ci)
+
+
 def column_lists(sparse_map: torch.Tensor, L: int, BLKQ: int, BLKK: int, topk: int):
     """Per-KV-block query-block lists from a 0/1 block map (for maps made elsewhere)."""
     _require_cuda(sparse_map)
