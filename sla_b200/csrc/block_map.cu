@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(256) colsum_kernel(const TIn* __restrict__ k, 
   constexpr int TPR = D / N;       // threads per row
   constexpr int RP = 256 / TPR;    // rows per pass
   __shared__ float red[RP][D];
+  pdl_wait();
   int bh = blockIdx.y, ch = blockIdx.x;
   int tid = threadIdx.x, rg = tid / TPR, c = (tid % TPR) * N;
   int row0 = ch * kColsumRows, row1 = min(L, row0 + kColsumRows);
@@ -58,6 +59,7 @@ __global__ void __launch_bounds__(256) colsum_kernel(const TIn* __restrict__ k, 
 template <typename TIn>
 __global__ void kmean_finalize_kernel(const float* __restrict__ partial, float* __restrict__ kmean, int L,
                                       int nch, int D) {
+  pdl_wait();
   int bh = blockIdx.x, d = threadIdx.x;
   if (d >= D) return;
   float s = 0.f;
@@ -74,6 +76,7 @@ __global__ void __launch_bounds__(256) pool_kernel(const TIn* __restrict__ q, co
   constexpr int TPR = D / N;
   constexpr int RP = 256 / TPR;
   __shared__ float red[RP][D];
+  pdl_wait();
   const bool is_k = blockIdx.z == 1;
   const int blk = is_k ? blkk : blkq;
   const int nblk = (L + blk - 1) / blk;
@@ -130,6 +133,7 @@ __global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
   uint32_t* keys = reinterpret_cast<uint32_t*>(spq + kTopkRows * D);       // [R][nb]
   const int bh = blockIdx.y, row_base = blockIdx.x * kTopkRows;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
 
   for (int i = tid; i < kTopkRows * D; i += blockDim.x) {
     int r = i / D, d = i % D;
@@ -259,6 +263,7 @@ __global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
 // ---- 5. column lists: in-place inclusive scan of the per-column counts ----
 __global__ void __launch_bounds__(1024) col_scan_kernel(int32_t* __restrict__ col_offsets, int nb) {
   __shared__ int32_t warp_tot[32];
+  pdl_wait();
   int32_t* c = col_offsets + static_cast<size_t>(blockIdx.x) * (nb + 1);
   int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int per = (nb + 1 + 1023) / 1024;
@@ -295,6 +300,7 @@ __global__ void __launch_bounds__(1024) col_fill_kernel(const int8_t* __restrict
                                                         const int32_t* __restrict__ col_offsets,
                                                         int32_t* __restrict__ col_index, int mb, int nb,
                                                         int topk) {
+  pdl_wait();
   int bh = blockIdx.y;
   int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int j = blockIdx.x * 32 + warp;
@@ -346,11 +352,12 @@ static int launch_block_map(const sla_shape* s, const TIn* q, const TIn* k, int3
   const bool want_cols = col_offsets != nullptr && col_index != nullptr;
   if (want_cols && sparse_map == nullptr) sparse_map = reinterpret_cast<int8_t*>(ws + w.map);
 
-  colsum_kernel<TIn, D><<<dim3(w.nch, bh), 256, 0, st>>>(k, partial, L, w.nch);
+  SLA_CUDA_OK(launch_pdl<false>(colsum_kernel<TIn, D>, dim3(w.nch, bh), dim3(256), 0, st, k, partial, L, w.nch));
   SLA_LAUNCH_OK();
-  kmean_finalize_kernel<TIn><<<bh, D, 0, st>>>(partial, kmean, L, w.nch, D);
+  SLA_CUDA_OK(launch_pdl<false>(kmean_finalize_kernel<TIn>, dim3(bh), dim3(D), 0, st, partial, kmean, L, w.nch, D));
   SLA_LAUNCH_OK();
-  pool_kernel<TIn, D><<<dim3(max(mb, nb), bh, 2), 256, 0, st>>>(q, k, kmean, pq, pk, L, s->BLKQ, s->BLKK);
+  SLA_CUDA_OK(launch_pdl<false>(pool_kernel<TIn, D>, dim3(max(mb, nb), bh, 2), dim3(256), 0, st, q, k, kmean, pq, pk, L,
+                         s->BLKQ, s->BLKK));
   SLA_LAUNCH_OK();
   return score_and_select<TIn, D>(s, pq, pk, lut, sparse_map, col_offsets, col_index, st);
 }
@@ -367,14 +374,15 @@ static int score_and_select(const sla_shape* s, const TIn* pq, const TIn* pk, in
   if (smem > 200 * 1024) return SLA_ERR_BAD_SHAPE;
   auto kern = score_topk_kernel<TIn, D>;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  kern<<<dim3(ceil_div(mb, kTopkRows), bh), kTopkRows * 32, smem, st>>>(
-      pq, pk, lut, sparse_map, want_cols ? col_offsets : nullptr, mb, nb, s->topk);
+  SLA_CUDA_OK(launch_pdl<false>(kern, dim3(ceil_div(mb, kTopkRows), bh), dim3(kTopkRows * 32), smem, st, pq, pk, lut,
+                         sparse_map, want_cols ? col_offsets : nullptr, mb, nb, s->topk));
   SLA_LAUNCH_OK();
   if (want_cols) {
-    col_scan_kernel<<<bh, 1024, 0, st>>>(col_offsets, nb);
+    SLA_CUDA_OK(launch_pdl<false>(col_scan_kernel, dim3(bh), dim3(1024), 0, st, col_offsets, nb));
     SLA_LAUNCH_OK();
-    col_fill_kernel<<<dim3(ceil_div(nb, 32), bh), 1024, 0, st>>>(sparse_map, col_offsets, col_index, mb, nb,
-                                                                s->topk);
+    SLA_CUDA_OK(launch_pdl<false>(col_fill_kernel, dim3(ceil_div(nb, 32), bh), dim3(1024), 0, st,
+                           static_cast<const int8_t*>(sparse_map), static_cast<const int32_t*>(col_offsets), col_index,
+                           mb, nb, s->topk));
     SLA_LAUNCH_OK();
   }
   return SLA_OK;

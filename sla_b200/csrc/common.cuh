@@ -34,6 +34,34 @@ void count_launch();
     SLA_CUDA_OK(cudaGetLastError());    \
   } while (0)
 
+// Programmatic dependent launch: a kernel launched through launch_pdl may be scheduled while its predecessor in
+// the stream is still running; it must call pdl_wait() before it touches global memory (the call returns once the
+// predecessor has completed and its writes are visible; it is a no-op for a kernel launched the ordinary way).
+// pdl_launch_dependents() lets the successor's CTAs take the SMs this kernel's last wave leaves idle. Every kernel
+// launched through launch_pdl calls both first thing, so a chain of them keeps stream order for memory while
+// the launch latency and the partial last wave of one kernel overlap the start of the next.
+// launch_pdl<false> is an ordinary launch through the same interface. The forward path uses it: there the linear-branch
+// state runs on a second stream next to the mask prediction, and a kernel that becomes resident early and sits in
+// pdl_wait() holds SM slots the other stream's kernels could use; no gain was measured there. The backward is one
+// chain of eight kernels on one stream and launches programmatically (about 1 % of the step at L = 32760 with 12
+// heads, 5-8 % with one or two heads per GPU).
+template <bool Programmatic = true, typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = Programmatic ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#if defined(__CUDACC__)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_entry() { pdl_wait(); pdl_launch_dependents(); }
+#endif
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -173,6 +173,7 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_q_kernel(LinBwdParams 
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) linear_bwd_gsum_kernel(const float* __restrict__ part,
                                                               float* __restrict__ gsum, int nch, int n) {
+  pdl_entry();
   const int bh = blockIdx.y;
   const int i = blockIdx.x * 256 + threadIdx.x;
   if (i >= n) return;
@@ -188,6 +189,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_reduce_kernel(LinBwdParams p) {
   constexpr int NT = D / 16 * 32, KS = D / 16, dd = D * D, n = dd + 2 * D;
   extern __shared__ __align__(128) unsigned char smem[];
+  pdl_entry();
   unsigned char* sG = smem;              // [n][i] T
   unsigned char* sW = sG + dd * 2;       // [n][j] T
   unsigned char* sH = sW + dd * 2;       // [i][k] T
@@ -253,6 +255,7 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_bwd_reduce_kernel(LinBwdPa
 
 __global__ void dw_final_kernel(const float* __restrict__ dw_part, float* __restrict__ dw,
                                 float* __restrict__ dbias, int bh, int dd, int d) {
+  pdl_entry();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= dd + d) return;
   float s = 0.f;
@@ -335,13 +338,15 @@ template <typename T, int D>
 static int reductions_typed(const sla_shape* s, const LinBwdParams& p, cudaStream_t st) {
   const int bh = s->B * s->H, dd = D * D;
   const int n = p.g_stride ? p.g_stride : dd + 2 * D;
-  linear_bwd_gsum_kernel<<<dim3(ceil_div(n, 256), bh), 256, 0, st>>>(p.g_partial, p.g_sum, p.nch, n);
+  SLA_CUDA_OK(launch_pdl(linear_bwd_gsum_kernel, dim3(ceil_div(n, 256), bh), dim3(256), 0, st,
+                         static_cast<const float*>(p.g_partial), p.g_sum, p.nch, n));
   SLA_LAUNCH_OK();
   auto rk = linear_bwd_reduce_kernel<T, D>;
   SLA_CUDA_OK(cudaFuncSetAttribute(rk, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * dd * 2));
-  rk<<<bh, D / 16 * 32, 3 * dd * 2, st>>>(p);
+  SLA_CUDA_OK(launch_pdl(rk, dim3(bh), dim3(D / 16 * 32), 3 * dd * 2, st, p));
   SLA_LAUNCH_OK();
-  dw_final_kernel<<<ceil_div(dd + D, 256), 256, 0, st>>>(p.dw_part, p.dw, p.dbias, bh, dd, D);
+  SLA_CUDA_OK(launch_pdl(dw_final_kernel, dim3(ceil_div(dd + D, 256)), dim3(256), 0, st,
+                         static_cast<const float*>(p.dw_part), p.dw, p.dbias, bh, dd, D));
   SLA_LAUNCH_OK();
   return SLA_OK;
 }

@@ -76,6 +76,7 @@ linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int ch = blockIdx.x, bh = blockIdx.y;
   const int L = p.L;
+  pdl_entry();
   const uint32_t raw_a = smem_u32(smem_raw);
   const uint32_t base_a = (raw_a + 1023u) & ~1023u;
   const uint32_t sHW = base_a, sQ = base_a + TILE, sDY = base_a + 2 * TILE;
@@ -437,7 +438,7 @@ static int launch_lin_q_tc(const sla_shape* s, const LinBwdParams& lp, cudaStrea
   auto kern = tc::linear_bwd_q_tc_kernel<T>;
   const int smem = 1024 + 3 * 2 * 128 * 128;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  kern<<<dim3(lp.nch, bh), 192, smem, st>>>(tq, tdy, tdq, thw, p);
+  SLA_CUDA_OK(launch_pdl(kern, dim3(lp.nch, bh), dim3(192), smem, st, tq, tdy, tdq, thw, p));
   SLA_LAUNCH_OK();
   return SLA_OK;
 }

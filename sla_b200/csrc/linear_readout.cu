@@ -13,6 +13,7 @@ __global__ void __launch_bounds__(D / 16 * 32) state_proj_kernel(T* __restrict__
                                                                  const T* __restrict__ wbits) {
   constexpr int NT = D / 16 * 32, KS = D / 16;
   extern __shared__ __align__(128) unsigned char smem[];
+  pdl_wait();
   unsigned char* sA = smem;               // H [i][k]
   unsigned char* sB = smem + D * D * 2;   // W [n][k]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -39,7 +40,8 @@ static int launch_state_proj(const sla_shape* s, void* lin_state, const void* wb
   auto pk = state_proj_kernel<T, D>;
   int psmem = 2 * D * D * 2;
   SLA_CUDA_OK(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
-  pk<<<s->B * s->H, D / 16 * 32, psmem, st>>>(static_cast<T*>(lin_state), static_cast<const T*>(wbits));
+  SLA_CUDA_OK(launch_pdl<false>(pk, dim3(s->B * s->H), dim3(D / 16 * 32), psmem, st, static_cast<T*>(lin_state),
+                         static_cast<const T*>(wbits)));
   SLA_LAUNCH_OK();
   return SLA_OK;
 }

@@ -153,6 +153,7 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_state_kernel(const T* __re
                                                                    float* __restrict__ partial, int L,
                                                                    int nch, int rows) {
   extern __shared__ __align__(128) unsigned char smem[];   // two {K, V} buffers of 64 rows
+  pdl_wait();
   linear_state_chunk<T, D, FEAT>(k, v, partial, L, nch, rows, smem);
 }
 
@@ -160,6 +161,7 @@ __global__ void __launch_bounds__(D / 16 * 32) linear_state_kernel(const T* __re
 template <typename T>
 __global__ void linear_state_reduce_kernel(const float* __restrict__ partial, T* __restrict__ state, int nch,
                                            int n, int rec_stride) {
+  pdl_wait();
   int bh = blockIdx.y;
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -177,7 +179,7 @@ static int launch_state(const sla_shape* s, const T* k, const T* v, T* state, fl
   const int smem = 4 * 64 * D * 2;
   auto go = [&](auto kern) -> int {
     SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<grid, D / 16 * 32, smem, st>>>(k, v, partial, s->L, nch, rows);
+    SLA_CUDA_OK(launch_pdl<false>(kern, grid, dim3(D / 16 * 32), smem, st, k, v, partial, s->L, nch, rows));
     SLA_LAUNCH_OK();
     return SLA_OK;
   };
@@ -189,7 +191,8 @@ static int launch_state(const sla_shape* s, const T* k, const T* v, T* state, fl
   }
   if (rc != SLA_OK) return rc;
   int n = D * D + D;
-  linear_state_reduce_kernel<T><<<dim3(ceil_div(n, 256), bh), 256, 0, st>>>(partial, state, nch, n, 2 * D * D + D);
+  SLA_CUDA_OK(launch_pdl<false>(linear_state_reduce_kernel<T>, dim3(ceil_div(n, 256), bh), dim3(256), 0, st,
+                         static_cast<const float*>(partial), state, nch, n, 2 * D * D + D));
   SLA_LAUNCH_OK();
   return SLA_OK;
 }

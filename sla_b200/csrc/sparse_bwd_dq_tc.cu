@@ -72,6 +72,7 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, bh = blockIdx.y;
   const int L = p.L;
+  pdl_entry();
   long long* trc = (p.trace != nullptr && tid == 0) ? p.trace + 8 * (static_cast<size_t>(bh) * gridDim.x + tile) : nullptr;
   const long long clk0 = clock64();
   if (trc) {
@@ -432,7 +433,7 @@ static int launch_dq_pair(const sla_shape* s, const BwdParams& bp, const float2*
   p.scale = bp.scale; p.scale_log2 = bp.scale_log2;
   auto kern = tc::sparse_bwd_dq_pair_kernel<T, D, BM, PLAIN>;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  kern<<<dim3(ceil_div(s->L, 128), bh), 576, smem, st>>>(tq, tdo, tk, tv, tdq, p);
+  SLA_CUDA_OK(launch_pdl(kern, dim3(ceil_div(s->L, 128), bh), dim3(576), smem, st, tq, tdo, tk, tv, tdq, p));
   SLA_LAUNCH_OK();
   return SLA_OK;
 }

@@ -90,6 +90,7 @@ sparse_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_co
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, bh = blockIdx.y;
   const int L = p.L;
+  pdl_entry();
 
   const uint32_t raw_a = smem_u32(smem_raw);
   const uint32_t base_a = (raw_a + 1023u) & ~1023u;
@@ -586,6 +587,7 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ o_s
   constexpr int LPR = D / 8;              // lanes per row
   constexpr int RPI = 32 / LPR;           // rows per warp iteration
   constexpr int ITER = 8 / RPI;
+  pdl_entry();
   const int bh = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane / LPR, col = (lane % LPR) * 8;
   const int r_base = blockIdx.x * 64 + warp * 8;
@@ -658,7 +660,7 @@ static int launch_dkdv(const sla_shape* s, const BwdParams& bp, const float2* st
   if (smem + kBwdStaticSmem > 227 * 1024) return SLA_ERR_BAD_SHAPE;
   auto kern = tc::sparse_bwd_dkdv_kernel<T, D, BM, PLAIN>;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  kern<<<dim3(ceil_div(bp.nb, 2), bh), 576, smem, st>>>(x1, x2, y1, y2, o1, o2, dh, p);
+  SLA_CUDA_OK(launch_pdl(kern, dim3(ceil_div(bp.nb, 2), bh), dim3(576), smem, st, x1, x2, y1, y2, o1, o2, dh, p));
   SLA_LAUNCH_OK();
   return SLA_OK;
 }
@@ -669,8 +671,9 @@ static int run_bwd_tc_typed(const sla_shape* s, const BwdParams& bp, float2* sta
   // nothing is launched unless both kernels fit: the caller falls back to another path on BAD_SHAPE
   if (!sparse_bwd_tc_fits(s)) return SLA_ERR_BAD_SHAPE;
   if (!bp.plain) {   // plain mode: the caller has filled the row statistics
-    bwd_prep_kernel<T, D><<<dim3(ceil_div(Lpad, 64), bh), 256, 0, st>>>(
-        static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L, Lpad);
+    SLA_CUDA_OK(launch_pdl(bwd_prep_kernel<T, D>, dim3(ceil_div(Lpad, 64), bh), dim3(256), 0, st,
+                           static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L,
+                           Lpad));
     SLA_LAUNCH_OK();
   }
   int rc = run_sparse_bwd_dq_pair(s, bp, stats, Lpad, st);

@@ -237,6 +237,7 @@ __global__ void __launch_bounds__(BM / 16 * 32) sparse_fwd_mma_kernel(FwdParams 
 template <typename T>
 __global__ void convert_proj_kernel(const float* __restrict__ w, const float* __restrict__ bias,
                                     T* __restrict__ out, int dd, int d) {
+  pdl_wait();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < dd) out[i] = Elem<T>::from_f(w[i]);
   else if (i < dd + d) out[i] = Elem<T>::from_f(bias ? bias[i - dd] : 0.f);
@@ -245,9 +246,11 @@ __global__ void convert_proj_kernel(const float* __restrict__ w, const float* __
 int convert_proj(const sla_shape* s, const float* w, const float* bias, void* out, cudaStream_t st) {
   int dd = s->D * s->D, n = dd + s->D;
   if (s->dtype == SLA_BF16)
-    convert_proj_kernel<__nv_bfloat16><<<ceil_div(n, 256), 256, 0, st>>>(w, bias, static_cast<__nv_bfloat16*>(out), dd, s->D);
+    SLA_CUDA_OK(launch_pdl(convert_proj_kernel<__nv_bfloat16>, dim3(ceil_div(n, 256)), dim3(256), 0, st, w, bias,
+                           static_cast<__nv_bfloat16*>(out), dd, s->D));
   else
-    convert_proj_kernel<__half><<<ceil_div(n, 256), 256, 0, st>>>(w, bias, static_cast<__half*>(out), dd, s->D);
+    SLA_CUDA_OK(launch_pdl(convert_proj_kernel<__half>, dim3(ceil_div(n, 256)), dim3(256), 0, st, w, bias,
+                           static_cast<__half*>(out), dd, s->D));
   SLA_LAUNCH_OK();
   return SLA_OK;
 }

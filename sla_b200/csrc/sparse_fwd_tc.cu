@@ -86,6 +86,7 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, bh = blockIdx.y;
   const int L = p.L;
+  pdl_entry();
 
   // 1024-byte aligned tile area (required by the 128B swizzle pattern)
   const uint32_t raw_a = smem_u32(smem_raw);
@@ -689,7 +690,7 @@ static int launch_tc(const sla_shape* s, const FwdParams& fp, cudaStream_t st) {
   const int smem = fwd_tc_smem_bytes(D, fp.topk);
   if (!sparse_fwd_tc_fits(s)) return SLA_ERR_BAD_SHAPE;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  kern<<<dim3(p.n_tiles, bh), 192, smem, st>>>(tq, tk, tv, to, tos, thw, p);
+  SLA_CUDA_OK(launch_pdl<false>(kern, dim3(p.n_tiles, bh), dim3(192), smem, st, tq, tk, tv, to, tos, thw, p));
   SLA_LAUNCH_OK();
   return SLA_OK;
 }
