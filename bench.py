@@ -500,6 +500,40 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             strong["gather_ms"] = float(t.item())
             strong["gather_bytes_per_rank"] = w.units * w.L * w.D * 2
+            # the forward as its own all-gather (sla_fwd_gather: the kernel's epilogue stores every output tile into the
+            # peers' buffers as well) against forward + NCCL all-gather, forward only, same shards
+            if hi > lo and not w.quantized and min(counts) > 0:
+                go = sharding.GatheredOutput(w.units, w.L, w.D, q.dtype, dev)
+
+                def fwd_plain():
+                    with torch.no_grad():
+                        return m(sq, sk, sv)
+
+                def fwd_nccl():
+                    sharding.all_gather_units(fwd_plain()[0], w.units)
+
+                def fwd_fused():
+                    with torch.no_grad():
+                        m(sq, sk, sv, gather=go)
+
+                res = {}
+                for name, fn in (("fwd_ms", fwd_plain), ("fwd_then_nccl_gather_ms", fwd_nccl),
+                                 ("fwd_fused_gather_ms", fwd_fused)):
+                    v_ms = timed(fn, args.steps, 3, sync)
+                    t = torch.tensor([v_ms], dtype=torch.float64, device=dev)
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                    res[name] = float(t.item())
+                go.full.zero_()
+                sync()
+                fwd_fused()
+                go.wait()
+                ref_full = sharding.all_gather_units(fwd_plain()[0], w.units)
+                same = torch.tensor([1.0 if torch.equal(go.full, ref_full) else 0.0], device=dev)
+                dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                res["fused_equals_nccl_on_every_rank"] = bool(same.item() == 1.0)
+                strong["fused_gather"] = res
+                check_device("the fused gather")
+                del go
         del mine
 
     # ---- end to end through the module API with HOST buffers ----

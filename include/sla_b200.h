@@ -208,6 +208,32 @@ SLA_API int sla_fwd(const sla_shape* shape, const void* q, const void* k, const 
             const int32_t* lut, const float* w, const float* bias, void* o, void* o_s, float* lse,
             void* lin_state, void* ws, size_t ws_bytes, sla_stream_t stream);
 
+/* sla_fwd whose epilogue also writes the output tile by tile into up to 8 further buffers, each laid out like `o`
+ * (a (B, H, L, D) block): gather_dst[i] is the address, in THIS process's address space, of the place in
+ * destination i where this call's o belongs. A destination may be memory of another GPU of the node mapped into
+ * this process (CUDA IPC, peer access enabled: sla_enable_peer_access): every rank of a (batch x head)-sharded run
+ * then leaves its slice of o in every peer's full-size buffer, and the forward is its own all-gather, written
+ * over NVLink with plain stores while the kernel computes (no TMA and no multicast touch peer memory). Stands in for
+ * the all-gather a caller of sparse_linear_attention/core.py:69 runs after the module when heads are sharded over
+ * GPUs; no counterpart in the reference, which is single-GPU. The copies are complete when the stream has reached
+ * the end of this call; readers on other GPUs need their own synchronisation with it (a barrier between the ranks).
+ * tcgen05 kernels only: SLA_ERR_UNSUPPORTED with SLA_FLAG_LEGACY_MMA, SLA_FLAG_LINEAR_UNSELECTED or a top-k
+ * beyond the tcgen05 forward's list budget. */
+SLA_API int sla_fwd_gather(const sla_shape* shape, const void* q, const void* k, const void* v, const int32_t* lut,
+                   const float* w, const float* bias, void* o, void* o_s, float* lse, void* lin_state, void* ws,
+                   size_t ws_bytes, void* const* gather_dst, int n_gather, sla_stream_t stream);
+/* Helpers for sla_fwd_gather (no counterpart in the reference). sla_ipc_export: the 64-byte CUDA IPC handle of the
+ * device allocation `ptr` lies in (cudaMalloc memory, e.g. a PyTorch tensor without expandable segments) and ptr's
+ * offset inside it; send both to the other processes of the node. sla_ipc_open maps such an allocation into this
+ * process FOR THE CURRENT DEVICE: call it with the GPU current whose kernels will write the buffer, not the GPU that
+ * owns it; *ptr is the allocation's base (add the offset). sla_ipc_close unmaps it. */
+SLA_API int sla_ipc_export(const void* ptr, void* handle64, size_t* offset);
+SLA_API int sla_ipc_open(const void* handle64, void** ptr);
+SLA_API int sla_ipc_close(void* ptr);
+/* Enables access from the current device to `peer_device`'s memory (cudaDeviceEnablePeerAccess; fine if it already
+ * is). SLA_ERR_UNSUPPORTED when the two GPUs have no peer path. */
+SLA_API int sla_enable_peer_access(int peer_device);
+
 /* The part of sla_fwd that depends on k, v and proj_l only (core.py:91,93-94 and the 16-bit copy of the
  * projection): a caller may run it on a second stream next to sla_block_map, which depends on q and k only,
  * and then call sla_fwd with SLA_FLAG_STATE_READY and the same lin_state and workspace. No counterpart in the

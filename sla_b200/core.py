@@ -86,13 +86,16 @@ class SparseLinearAttention(nn.Module):
                                                      eps, interleaved, self.BLKQ, self.BLKK, inplace)
         return q_out, k_out, ops.block_map_pooled(pooled, self.topk, want_cols=with_column_lists)
 
-    def forward(self, q, k, v, return_sparsity=False, block_map=None):
+    def forward(self, q, k, v, return_sparsity=False, block_map=None, gather=None):
         R"""
         Args:
             q, k, v: (B, H, L, D) CUDA tensors (any float dtype; output has q's dtype).
             return_sparsity: also return topk / N_BLOCKS, the kept fraction of KV blocks.
             block_map: not in the reference. A map from `predict_block_map` (or its packed form) to use instead of
                 predicting one from this call's q and k.
+            gather: not in the reference. A `sharding.GatheredOutput`: the result is written into this rank's slice of
+                its full-size buffer and, by the same kernel, into every peer GPU's buffer (q, k, v must then be in
+                the module's compute dtype and hold exactly this rank's units as (1, U, L, D)).
         """
         dtype = q.dtype
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
@@ -118,8 +121,13 @@ class SparseLinearAttention(nn.Module):
         if prep is not None:
             torch.cuda.current_stream(q.device).wait_stream(side)
         q, k, v = q.to(self.dtype), kc, vc
+        out, gather_ptrs = None, None
+        if gather is not None:
+            if dtype != self.dtype:
+                raise TypeError("gather= needs inputs in the module's compute dtype")
+            out, gather_ptrs = gather.local_view(q.shape), gather.peer_pointers()
         o = ops.sla_attention(q, k, v, self.proj_l.weight, self.proj_l.bias, bm, self.BLKQ, self.BLKK,
-                              self.feature_map, self.impl_flags, prep)
+                              self.feature_map, self.impl_flags, prep, out, gather_ptrs)
         o = o.to(dtype)
         if return_sparsity:
             return o, bm.topk / bm.n_blocks

@@ -1,5 +1,7 @@
 // extern "C" entry points of the attention operators: argument checks, workspace carving, launches.
+#include <cuda.h>
 #include <initializer_list>
+#include <string.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -134,17 +136,30 @@ int sla_fwd_prepare(const sla_shape* s, const void* k, const void* v, const floa
   return run_state_proj(s, lin_state, wbits, st);
 }
 
-int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
-            const float* w, const float* bias, void* o, void* o_s, float* lse, void* lin_state, void* ws,
-            size_t ws_bytes, sla_stream_t stream) {
+static int fwd_impl(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+                    const float* w, const float* bias, void* o, void* o_s, float* lse, void* lin_state, void* ws,
+                    size_t ws_bytes, void* const* gather_dst, int n_gather, sla_stream_t stream) {
   if (!q || !k || !v || !lut || !o || !lse) return SLA_ERR_NULL;
   int rc = check_common(s);
   if (rc != SLA_OK) return rc;
+  if (n_gather < 0 || n_gather > 8 || (n_gather > 0 && gather_dst == nullptr)) return SLA_ERR_UNSUPPORTED;
+  for (int g = 0; g < n_gather; ++g) {
+    if (gather_dst[g] == nullptr) return SLA_ERR_NULL;
+    if (!aligned16(gather_dst[g])) return SLA_ERR_BAD_ALIGN;
+  }
+  // the copies are written by the tcgen05 kernel's epilogue only
+  if (n_gather > 0 && ((s->flags & (SLA_FLAG_LEGACY_MMA | SLA_FLAG_LINEAR_UNSELECTED)) || !sparse_fwd_tc_fits(s)))
+    return SLA_ERR_UNSUPPORTED;
+  auto with_gather = [&](FwdParams p) {
+    p.n_gather = n_gather;
+    for (int g = 0; g < n_gather; ++g) p.gather_dst[g] = gather_dst[g];
+    return p;
+  };
   if (!all_aligned({q, k, v, o, o_s, lin_state, ws})) return SLA_ERR_BAD_ALIGN;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool legacy = (s->flags & SLA_FLAG_LEGACY_MMA) != 0;
   if (s->flags & SLA_FLAG_SPARSE_ONLY) {
-    FwdParams p = make_fwd(s, q, k, v, lut, o, nullptr, lse, nullptr, nullptr);
+    FwdParams p = with_gather(make_fwd(s, q, k, v, lut, o, nullptr, lse, nullptr, nullptr));
     return run_sparse_fwd(s, p, false, st);
   }
   if (!w || !lin_state || !ws) return SLA_ERR_NULL;
@@ -162,7 +177,7 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
     rc = run_state_proj(s, lin_state, wbits, st);
     if (rc != SLA_OK) return rc;
   }
-  FwdParams p = make_fwd(s, q, k, v, lut, o, o_s, lse, lin_state, wbits);
+  FwdParams p = with_gather(make_fwd(s, q, k, v, lut, o, o_s, lse, lin_state, wbits));
   if (unselected) {
     // sparse branch; then the same block lists once more without softmax on (phi(q), phi(k), v) for the
     // selected blocks' share of the linear state, which the read-out takes off the all-token state
@@ -187,6 +202,69 @@ int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, con
   }
   // sparse branch with the linear read-out, proj_l and the final sum fused into its epilogue
   return run_sparse_fwd(s, p, true, st);
+}
+
+int sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+            const float* w, const float* bias, void* o, void* o_s, float* lse, void* lin_state, void* ws,
+            size_t ws_bytes, sla_stream_t stream) {
+  return fwd_impl(s, q, k, v, lut, w, bias, o, o_s, lse, lin_state, ws, ws_bytes, nullptr, 0, stream);
+}
+
+int sla_fwd_gather(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+                   const float* w, const float* bias, void* o, void* o_s, float* lse, void* lin_state, void* ws,
+                   size_t ws_bytes, void* const* gather_dst, int n_gather, sla_stream_t stream) {
+  return fwd_impl(s, q, k, v, lut, w, bias, o, o_s, lse, lin_state, ws, ws_bytes, gather_dst, n_gather, stream);
+}
+
+int sla_enable_peer_access(int peer_device) {
+  int dev = 0;
+  SLA_CUDA_OK(cudaGetDevice(&dev));
+  if (peer_device == dev) return SLA_OK;
+  int can = 0;
+  SLA_CUDA_OK(cudaDeviceCanAccessPeer(&can, dev, peer_device));
+  if (!can) return SLA_ERR_UNSUPPORTED;
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); return SLA_OK; }
+  SLA_CUDA_OK(e);
+  return SLA_OK;
+}
+
+int sla_ipc_export(const void* ptr, void* handle64, size_t* offset) {
+  if (!ptr || !handle64 || !offset) return SLA_ERR_NULL;
+  // the handle names the whole allocation `ptr` lies in: find its base
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  SLA_CUDA_OK(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres));
+  if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return SLA_ERR_UNSUPPORTED;
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (reinterpret_cast<RangeFn>(fn)(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS) {
+    set_last_cuda_error(cudaErrorInvalidValue);
+    return SLA_ERR_CUDA;
+  }
+  cudaIpcMemHandle_t h;
+  SLA_CUDA_OK(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+  memcpy(handle64, &h, sizeof(h));
+  *offset = reinterpret_cast<CUdeviceptr>(ptr) - base;
+  return SLA_OK;
+}
+
+int sla_ipc_open(const void* handle64, void** ptr) {
+  if (!handle64 || !ptr) return SLA_ERR_NULL;
+  cudaIpcMemHandle_t h;
+  static_assert(sizeof(h) == 64, "CUDA IPC handles are 64 bytes");
+  memcpy(&h, handle64, sizeof(h));
+  // opened with the ACCESSING device current: the mapping (and, lazily, peer access to the owning GPU) is set up for
+  // this device's kernels. A handle opened under the owner's device index is only usable by that device.
+  SLA_CUDA_OK(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return SLA_OK;
+}
+
+int sla_ipc_close(void* ptr) {
+  if (!ptr) return SLA_ERR_NULL;
+  SLA_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+  return SLA_OK;
 }
 
 static int sparse_bwd_impl(const sla_shape* s, const void* q, const void* k, const void* v, const void* o_s,

@@ -18,6 +18,11 @@ struct FwdParams {
   int L, mb, topk;
   float scale_log2;       // softmax scale * log2(e)
   int plain = 0;          // tcgen05 forward only: P = S without softmax, unnormalised O, row sums in `lse`
+  // tcgen05 forward only: further copies of the output, written tile by tile from the epilogue with plain 16-byte
+  // stores. Each pointer addresses a (B, H, L, D) block laid out like `o`; it may be memory of another GPU mapped
+  // into this process (peer access enabled), which makes the forward its own all-gather.
+  void* gather_dst[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int n_gather = 0;
 };
 
 struct BwdParams {

@@ -43,6 +43,8 @@ struct TcFwdParams {
   int store_os;            // also store the sparse branch output through tmOs
   const void* lin_state;   // [BH][2*D*D + D] T: H, z, H W^T
   const void* wbits;       // [D*D + D] T: W, bias
+  void* gather[8];         // further destinations of the output tile (FwdParams::gather_dst)
+  int n_gather;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -399,6 +401,23 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       auto chunk_addr = [&](uint32_t tile_base, int ch) {
         return tile_base + (ch >> 3) * Q_SLAB + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
       };
+      // The staged output tile once more to every gather destination, with plain stores (a destination may be
+      // another GPU's memory: no TMA, no multicast). Sixteen-byte chunks of a row go to consecutive lanes, so a
+      // warp writes whole rows; rows past the end of the sequence are skipped.
+      auto gather_store = [&](uint32_t tile_base) {
+        constexpr int CH = D / 8;
+        for (int idx = tid; idx < 128 * CH; idx += 128) {
+          const int r = idx / CH, ch = idx % CH;
+          const int gr = tile * 128 + r;
+          if (gr < L) {
+            uint32_t w0, w1, w2, w3;
+            ld_shared_v4(tile_base + (ch >> 3) * Q_SLAB + r * 128 + (((ch & 7) ^ (r & 7)) << 4), w0, w1, w2, w3);
+            const size_t off = ((static_cast<size_t>(bh) * L + gr) * D + ch * 8) * sizeof(T);
+            for (int g = 0; g < p.n_gather; ++g)
+              *reinterpret_cast<uint4*>(static_cast<char*>(p.gather[g]) + off) = make_uint4(w0, w1, w2, w3);
+          }
+        }
+      };
       // O / l -> T for columns [c0, c0 + 32), written to the staging tile
       auto stage_os = [&](uint32_t tile_base, int c0) {
         uint32_t ov[32];
@@ -423,8 +442,9 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (tid == 0) {
           for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO, sQ + c * Q_SLAB, c * 64, tile * 128, bh);
           tma_store_commit();
-          tma_store_wait_read();
         }
+        if (p.n_gather > 0) gather_store(sQ);
+        if (tid == 0) tma_store_wait_read();
       } else {
         // ---- phi(q) over the Q tile in place (core.py:90) and 1 / den per row (core.py:95) ----
         // Eight threads per row (thread = 16-byte chunk `pc` of every 64-column slab), sixteen rows per pass, eight
@@ -544,8 +564,9 @@ sparse_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmOs, sV0 + c * Q_SLAB, c * 64, tile * 128, bh);
           for (int c = 0; c < SLABS; ++c) tma_store_3d(&tmO, sQ + c * Q_SLAB, c * 64, tile * 128, bh);
           tma_store_commit();
-          tma_store_wait_read();
         }
+        if (p.n_gather > 0 && !*abortp) gather_store(sQ);
+        if (tid == 0) tma_store_wait_read();
       }
     }
   }
@@ -673,6 +694,8 @@ static int launch_tc(const sla_shape* s, const FwdParams& fp, cudaStream_t st) {
   p.store_os = fused && fp.o_s != nullptr && fp.o_s != fp.o;
   p.lin_state = fp.lin_state; p.wbits = fp.wbits;
   p.plain = fp.plain;
+  p.n_gather = fp.n_gather;
+  for (int g = 0; g < 8; ++g) p.gather[g] = g < fp.n_gather ? fp.gather_dst[g] : nullptr;
   if (p.store_os && (rc = make_tmap_3d(&tos, fp.o_s, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
   if (fused) {
     // H W^T sits behind H and z in each head's record: D rows of D elements, records 2*D*D + D apart

@@ -301,11 +301,17 @@ class _SLAFused(torch.autograd.Function):
     """core.py:88-100 (sparse branch + feature maps + linear branch + proj_l + sum) as one operator."""
 
     @staticmethod
-    def forward(ctx, q, k, v, weight, bias, bm: BlockMap, BLKQ, BLKK, feature, need_grad, impl_flags, prep):
+    def forward(ctx, q, k, v, weight, bias, bm: BlockMap, BLKQ, BLKK, feature, need_grad, impl_flags, prep,
+                out=None, gather_ptrs=None):
         B, H, L, D = q.shape
         shape = make_shape(B, H, L, D, BLKQ, BLKK, bm.topk, q.dtype, feature, flags=impl_flags)
         dev = q.device
-        o = torch.empty_like(q)
+        if out is not None:
+            if tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype or not out.is_contiguous():
+                raise ValueError("`out` must be a contiguous tensor of q's shape and dtype")
+            o = out
+        else:
+            o = torch.empty_like(q)
         o_s = torch.empty_like(q) if need_grad else None
         lse = torch.empty((B, H, L), dtype=torch.float32, device=dev)
         if prep is not None:
@@ -318,8 +324,14 @@ class _SLAFused(torch.autograd.Function):
             lin_state = torch.empty((B, H, 2 * D * D + D), dtype=q.dtype, device=dev)
             ws = _workspace(shape, _lib.OP_FWD, dev)
             fwd_shape = shape
-        check(lib.sla_fwd(C.byref(fwd_shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o), _p(o_s),
-                          _p(lse), _p(lin_state), _p(ws), ws.numel(), _stream(q)))
+        if gather_ptrs:
+            dst = (C.c_void_p * len(gather_ptrs))(*[int(x) for x in gather_ptrs])
+            check(lib.sla_fwd_gather(C.byref(fwd_shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o),
+                                     _p(o_s), _p(lse), _p(lin_state), _p(ws), ws.numel(), dst, len(gather_ptrs),
+                                     _stream(q)))
+        else:
+            check(lib.sla_fwd(C.byref(fwd_shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o), _p(o_s),
+                              _p(lse), _p(lin_state), _p(ws), ws.numel(), _stream(q)))
         _check_device()
         if need_grad:
             ctx.save_for_backward(q, k, v, o_s, lse, lin_state, weight, bm.lut, bm.col_offsets, bm.col_index)
@@ -341,19 +353,24 @@ class _SLAFused(torch.autograd.Function):
                           _p(weight), _p(lin_state), _p(dq), _p(dk), _p(dv), _p(dw), _p(db), _p(ws), ws.numel(),
                           _stream(q)))
         _check_device()
-        return dq, dk, dv, dw, (db if ctx.has_bias else None), None, None, None, None, None, None, None
+        return dq, dk, dv, dw, (db if ctx.has_bias else None), None, None, None, None, None, None, None, None, None
 
 
 def sla_attention(q, k, v, weight, bias, bm: BlockMap, BLKQ=64, BLKK=64, feature="softmax",
-                  impl_flags: int = 0, prep: Optional[LinearPrep] = None):
+                  impl_flags: int = 0, prep: Optional[LinearPrep] = None, out: Optional[torch.Tensor] = None,
+                  gather_ptrs=None):
     """o = o_s + proj_l(o_l) for q, k, v already in the 16-bit compute dtype. `prep`: the result of
-    `prepare_linear` on the same k, v, weight, bias (already joined into the current stream)."""
+    `prepare_linear` on the same k, v, weight, bias (already joined into the current stream). `out`: write the
+    result there instead of into a new tensor. `gather_ptrs`: up to 8 device addresses (this process's view) of
+    further (B, H, L, D) blocks the kernel's epilogue also writes the result to, e.g. this rank's place in every peer
+    GPU's full-size output (`sharding.GatheredOutput`)."""
     _require_cuda(q, k, v, weight)
     need_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (q, k, v, weight, bias))
     if need_grad and bm.col_offsets is None:
         raise RuntimeError("the block map was built without column lists (want_cols=True) but a backward is needed")
-    return _SLAFused.apply(q, k, v, weight, bias, bm, BLKQ, BLKK, feature, need_grad, impl_flags, prep)
+    return _SLAFused.apply(q, k, v, weight, bias, bm, BLKQ, BLKK, feature, need_grad, impl_flags, prep, out,
+                           gather_ptrs)
 
 
 def sage_prepare(q, k, v, weight, bias, topk: int, feature="softmax", sparse_only: bool = False,

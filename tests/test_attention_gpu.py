@@ -119,3 +119,55 @@ def test_reference_asserts_are_kept():
         ops._attention.apply(q, q, q, smap, lut, topk, 64, 128)    # kernel.py:248
     with pytest.raises(AssertionError):
         ops._attention.apply(q.transpose(-1, -2), q, q, smap, lut, topk, 64, 64)  # kernel.py:243
+
+
+@pytest.mark.parametrize("fused,D,BLKQ,L", [(False, 128, 64, 1000), (True, 128, 64, 1100), (True, 64, 128, 777)])
+def test_forward_writes_its_output_to_gather_destinations(fused, D, BLKQ, L):
+    """sla_fwd_gather: the epilogue's extra copies of the output, here into three other buffers of the same GPU
+    standing in for peer GPUs' memory (two of them slices at an offset inside larger buffers, as a rank's place in
+    a full-size output is). Every copy must equal o bit for bit, memory around the slices must stay untouched, and
+    o itself must equal what sla_fwd gives."""
+    import ctypes as C
+    from sla_b200 import _lib, ops
+    from sla_b200._lib import check, lib
+    g = torch.Generator(device="cuda").manual_seed(L + D)
+    B, H = 1, 2
+    q, k, v = (torch.randn(B, H, L, D, generator=g, device="cuda").bfloat16() for _ in range(3))
+    bm = ops.block_map(q, k, 0.25, BLKQ, 64)
+    W = torch.randn(D, D, generator=g, device="cuda") * 0.05
+    bias = torch.randn(D, generator=g, device="cuda") * 0.05
+    flags = 0 if fused else _lib.FLAG_SPARSE_ONLY
+    shape = ops.make_shape(B, H, L, D, BLKQ, 64, bm.topk, torch.bfloat16, "softmax", flags=flags)
+    lse = torch.empty(B, H, L, dtype=torch.float32, device="cuda")
+    lin_state = torch.empty(B, H, 2 * D * D + D, dtype=torch.bfloat16, device="cuda")
+    ws = ops._workspace(shape, _lib.OP_FWD, "cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    n = B * H * L * D
+
+    def call(o, dst):
+        arr = (C.c_void_p * len(dst))(*dst) if dst else None
+        check(lib.sla_fwd_gather(C.byref(shape), q.data_ptr(), k.data_ptr(), v.data_ptr(), bm.lut.data_ptr(),
+                                 W.data_ptr(), bias.data_ptr(), o.data_ptr(), None, lse.data_ptr(), lin_state.data_ptr(),
+                                 ws.data_ptr(), ws.numel(), arr, len(dst), st))
+
+    o_ref = torch.empty_like(q)
+    check(lib.sla_fwd(C.byref(shape), q.data_ptr(), k.data_ptr(), v.data_ptr(), bm.lut.data_ptr(), W.data_ptr(),
+                      bias.data_ptr(), o_ref.data_ptr(), None, lse.data_ptr(), lin_state.data_ptr(), ws.data_ptr(),
+                      ws.numel(), st))
+    o = torch.empty_like(q)
+    plain = torch.full((n,), -7.0, dtype=torch.bfloat16, device="cuda")
+    big1 = torch.full((3 * n,), -7.0, dtype=torch.bfloat16, device="cuda")
+    big2 = torch.full((2 * n + 64,), -7.0, dtype=torch.bfloat16, device="cuda")
+    call(o, [plain.data_ptr(), big1.data_ptr() + 2 * n, big2.data_ptr() + 2 * (n + 64)])
+    torch.cuda.synchronize()
+    assert torch.equal(o, o_ref)
+    flat = o.flatten()
+    assert torch.equal(plain, flat)
+    assert torch.equal(big1[n:2 * n], flat) and bool((big1[:n] == -7.0).all()) and bool((big1[2 * n:] == -7.0).all())
+    assert torch.equal(big2[n + 64:], flat) and bool((big2[:n + 64] == -7.0).all())
+    # more than eight destinations, or the mma.sync kernels, are refused before anything is launched
+    nine = (C.c_void_p * 9)(*([plain.data_ptr()] * 9))
+    rc = lib.sla_fwd_gather(C.byref(shape), q.data_ptr(), k.data_ptr(), v.data_ptr(), bm.lut.data_ptr(), W.data_ptr(),
+                            bias.data_ptr(), o.data_ptr(), None, lse.data_ptr(), lin_state.data_ptr(), ws.data_ptr(),
+                            ws.numel(), nine, 9, st)
+    assert rc == -10
