@@ -525,14 +525,33 @@ __global__ void __launch_bounds__(256) qk_norm_rope_pool_kernel(
 // pooled_k = round_T(ksum / nx - kmean). The last line is where this path departs from utils.py:56 + :40, which
 // round every element of k - mean(k) to T before pooling: the block mean of those rounding errors (well below one
 // unit in the last place of the pooled value) is not reproduced.
+// One CTA per head, 1024 threads = 8 groups of 128 columns: group g sums the blocks j = g (mod 8) with four loads in
+// flight, the eight partial sums are added in a fixed order.
 template <typename TIn>
-__global__ void __launch_bounds__(128) pooled_kmean_kernel(const float* __restrict__ ksum, float* __restrict__ kmean,
-                                                           int L, int nb, int D) {
-  const int bh = blockIdx.x, d = threadIdx.x;
-  if (d >= D) return;
-  float s = 0.f;
-  for (int j = 0; j < nb; ++j) s += ksum[(static_cast<size_t>(bh) * nb + j) * D + d];
-  kmean[static_cast<size_t>(bh) * D + d] = round_to<TIn>(s / static_cast<float>(L));
+__global__ void __launch_bounds__(1024) pooled_kmean_kernel(const float* __restrict__ ksum, float* __restrict__ kmean,
+                                                            int L, int nb, int D) {
+  __shared__ float part[8][128];
+  const int bh = blockIdx.x, d = threadIdx.x & 127, g = threadIdx.x >> 7;
+  const float* base = ksum + static_cast<size_t>(bh) * nb * D;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (d < D) {
+    int j = g;
+    for (; j + 24 < nb; j += 32) {
+      s0 += base[static_cast<size_t>(j) * D + d];
+      s1 += base[static_cast<size_t>(j + 8) * D + d];
+      s2 += base[static_cast<size_t>(j + 16) * D + d];
+      s3 += base[static_cast<size_t>(j + 24) * D + d];
+    }
+    for (; j < nb; j += 8) s0 += base[static_cast<size_t>(j) * D + d];
+  }
+  part[g][d] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (g == 0 && d < D) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += part[i][d];
+    kmean[static_cast<size_t>(bh) * D + d] = round_to<TIn>(s / static_cast<float>(L));
+  }
 }
 template <typename TIn>
 __global__ void __launch_bounds__(256) pooled_finalize_kernel(const float* __restrict__ qsum, const float* __restrict__ ksum,
@@ -581,7 +600,7 @@ static int block_map_pooled_typed(const sla_shape* s, const unsigned char* sums,
   TIn* pq = reinterpret_cast<TIn*>(ws + w.pooled_q);
   TIn* pk = reinterpret_cast<TIn*>(ws + w.pooled_k);
   if (col_offsets != nullptr && sparse_map == nullptr) sparse_map = reinterpret_cast<int8_t*>(ws + w.map);
-  pooled_kmean_kernel<TIn><<<bh, 128, 0, st>>>(ksum, kmean, s->L, nb, D);
+  pooled_kmean_kernel<TIn><<<bh, 1024, 0, st>>>(ksum, kmean, s->L, nb, D);
   SLA_LAUNCH_OK();
   pooled_finalize_kernel<TIn><<<dim3(ceil_div(max(mb, nb) * D, 256), bh, 2), 256, 0, st>>>(qsum, ksum, kmean, pq, pk, s->L,
                                                                                           s->BLKQ, s->BLKK, D);
