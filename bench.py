@@ -502,7 +502,7 @@ def main():
             strong["gather_bytes_per_rank"] = w.units * w.L * w.D * 2
             # the forward as its own all-gather (sla_fwd_gather: the kernel's epilogue stores every output tile into the
             # peers' buffers as well) against forward + NCCL all-gather, forward only, same shards
-            if hi > lo and not w.quantized and min(counts) > 0:
+            if hi > lo and min(counts) > 0:
                 go = sharding.GatheredOutput(w.units, w.L, w.D, q.dtype, dev)
 
                 def fwd_plain():

@@ -257,6 +257,12 @@ SLA_API int sage_sla_fwd(const sla_shape* shape, const void* q, const void* k, c
                  const int32_t* lut, const float* w, const float* bias, void* o, void* lin_state,
                  void* ws, size_t ws_bytes, sla_stream_t stream);
 
+/* sage_sla_fwd with the gather destinations of sla_fwd_gather (same meaning, same limits: up to 8 further
+ * (B, H, L, D) blocks, peers' memory allowed, written from the kernel's epilogue with plain stores). */
+SLA_API int sage_sla_fwd_gather(const sla_shape* shape, const void* q, const void* k, const void* v,
+                        const int32_t* lut, const float* w, const float* bias, void* o, void* lin_state, void* ws,
+                        size_t ws_bytes, void* const* gather_dst, int n_gather, sla_stream_t stream);
+
 /* The part of sage_sla_fwd that does not need the block map: the linear-branch state and the quantized copies of
  * q, k, v (SageSLA/core.py:102-108,127-129). A caller may run it on a second stream next to sla_block_map and then
  * call sage_sla_fwd with SLA_FLAG_STATE_READY and the same lin_state and workspace. */

@@ -21,7 +21,7 @@ EXPORTS = (
     "sla_version", "sla_status_string", "sla_last_cuda_error", "sla_launch_count", "sla_poll_device_error", "sla_debug_set_trace", "sla_debug_set_wait_limit_ns", "sla_debug_drop_first_k_tile", "sla_topk_count", "sla_workspace_bytes", "sla_kernel_path",
     "sla_block_map", "sla_column_lists", "sla_index_convert", "sla_pooled_sums_bytes", "sla_qk_norm_rope_pool",
     "sla_block_map_pooled", "sla_sparse_fwd", "sla_sparse_bwd", "sla_linear_state", "sla_linear_state_static", "sla_fwd", "sla_fwd_gather", "sla_enable_peer_access", "sla_ipc_export", "sla_ipc_open", "sla_ipc_close", "sla_fwd_prepare", "sla_bwd",
-    "sage_sla_fwd", "sage_sla_prepare",
+    "sage_sla_fwd", "sage_sla_fwd_gather", "sage_sla_prepare",
 )
 
 
@@ -106,6 +106,9 @@ def _load() -> C.CDLL:
                             vp, C.c_size_t, vp]
     lib.sage_sla_prepare.restype = C.c_int
     lib.sage_sla_prepare.argtypes = [sp, vp, vp, vp, f32p, f32p, vp, vp, C.c_size_t, vp]
+    lib.sage_sla_fwd_gather.restype = C.c_int
+    lib.sage_sla_fwd_gather.argtypes = [sp, vp, vp, vp, i32p, f32p, f32p, vp, vp, vp, C.c_size_t,
+                                        C.POINTER(C.c_void_p), C.c_int, vp]
     lib.sage_sla_fwd.restype = C.c_int
     lib.sage_sla_fwd.argtypes = [sp, vp, vp, vp, i32p, f32p, f32p, vp, vp, vp, C.c_size_t, vp]
     return lib

@@ -156,7 +156,9 @@ class SageSparseLinearAttention(nn.Module):
             nn.init.zeros_(self.proj_l.weight)
             nn.init.zeros_(self.proj_l.bias)
 
-    def forward(self, q, k, v, return_sparsity=False):
+    def forward(self, q, k, v, return_sparsity=False, gather=None):
+        R"""As the reference's forward; `gather` (not in the reference): a `sharding.GatheredOutput`, see
+        `SparseLinearAttention.forward` (under torch.no_grad(), inputs in the module's compute dtype)."""
         dtype = q.dtype
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         assert q.size(-1) in [64, 128], "headdim should be in [64, 128]."
@@ -173,7 +175,13 @@ class SageSparseLinearAttention(nn.Module):
         if prep is not None:
             torch.cuda.current_stream(q.device).wait_stream(side)
         # differentiable through the linear branch and proj_l only (SageSLA/core.py:148-158), like the reference
-        o = ops.sage_sla_attention(qc, kc, vc, self.proj_l.weight, self.proj_l.bias, bm, self.feature_map, prep=prep)
+        out, gather_ptrs = None, None
+        if gather is not None:
+            if dtype != self.dtype:
+                raise TypeError("gather= needs inputs in the module's compute dtype")
+            out, gather_ptrs = gather.local_view(qc.shape), gather.peer_pointers()
+        o = ops.sage_sla_attention(qc, kc, vc, self.proj_l.weight, self.proj_l.bias, bm, self.feature_map, prep=prep,
+                                   out=out, gather_ptrs=gather_ptrs)
         o = o.to(dtype)
         if return_sparsity:
             return o, bm.topk / bm.n_blocks

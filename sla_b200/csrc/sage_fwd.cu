@@ -33,6 +33,8 @@ struct SageParams {
   int feature;
   const void* lin_state;   // [BH][2*D*D + D] T: H, z, H W^T
   const void* wbits;       // [D*D + D] T: W, bias
+  void* gather[8];         // further destinations of the output tile, written with plain stores (peers' memory allowed)
+  int n_gather;
 };
 
 __device__ __forceinline__ float ex2s(float x) {
@@ -473,8 +475,24 @@ sage_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (tid == 0 && !*abortp) {
         for (int c = 0; c < NSLAB; ++c) tma_store_3d(&tmO, sO + c * O_SLAB, c * 64, tile * 128, bh);
         tma_store_commit();
-        tma_store_wait_read();
       }
+      if (p.n_gather > 0 && !*abortp) {
+        // the staged tile once more to every gather destination (sla_fwd_gather's scheme: consecutive lanes write
+        // consecutive 16-byte chunks of a row; no TMA and no multicast touch memory that may be another GPU's)
+        constexpr int CH = D / 8;
+        for (int idx = tid; idx < 128 * CH; idx += 128) {
+          const int r = idx / CH, ch = idx % CH;
+          const int gr = tile * 128 + r;
+          if (gr < L) {
+            uint32_t w0, w1, w2, w3;
+            ld_shared_v4(sO + (ch >> 3) * O_SLAB + r * 128 + (((ch & 7) ^ (r & 7)) << 4), w0, w1, w2, w3);
+            const size_t off = ((static_cast<size_t>(bh) * L + gr) * D + ch * 8) * sizeof(T);
+            for (int g = 0; g < p.n_gather; ++g)
+              *reinterpret_cast<uint4*>(static_cast<char*>(p.gather[g]) + off) = make_uint4(w0, w1, w2, w3);
+          }
+        }
+      }
+      if (tid == 0) tma_store_wait_read();
     }
   }
   __syncwarp();
@@ -657,7 +675,8 @@ static int run_sage_quant_typed(const sla_shape* s, const void* q, const void* k
 // The attention kernel on the quantized copies.
 template <typename T, int D>
 static int run_sage_main_typed(const sla_shape* s, const void* q, const int32_t* lut, void* o_s, float* lse,
-                               unsigned char* ws, const void* lin_state, const void* wbits, cudaStream_t st) {
+                               unsigned char* ws, const void* lin_state, const void* wbits, cudaStream_t st,
+                               void* const* gather_dst, int n_gather) {
   const int bh = s->B * s->H, L = s->L;
   const int mb = ceil_div(L, 128), nb = ceil_div(L, 64);
   WsSage w = ws_sage(s);
@@ -688,6 +707,8 @@ static int run_sage_main_typed(const sla_shape* s, const void* q, const int32_t*
   if (p.err == nullptr) return SLA_ERR_CUDA;
   p.L = L; p.mb = mb; p.nb = nb; p.topk = s->topk;
   p.scale_log2 = softmax_scale(s) * kLog2e;
+  p.n_gather = n_gather;
+  for (int g = 0; g < 8; ++g) p.gather[g] = g < n_gather ? gather_dst[g] : nullptr;
   auto kern = tc::sage_fwd_tc_kernel<T, D>;
   const int smem = 1024 + 2 * 128 * 128 + 2 * 4 * 64 * 128 + s->topk * 8 + 16;
   // up to 113 KB two CTAs share an SM, a longer list takes the SM alone; beyond 227 KB there is no quantized path
@@ -710,12 +731,13 @@ static int sage_quant(const sla_shape* s, const void* q, const void* k, const vo
                               : run_sage_quant_typed<__half, 128>(s, q, k, v, ws, st);
 }
 static int sage_main(const sla_shape* s, const void* q, const int32_t* lut, void* o, float* lse, unsigned char* ws,
-                     const void* state, const void* wbits, cudaStream_t st) {
+                     const void* state, const void* wbits, cudaStream_t st, void* const* gather_dst = nullptr,
+                     int n_gather = 0) {
   if (s->D == 64)
-    return s->dtype == SLA_BF16 ? run_sage_main_typed<__nv_bfloat16, 64>(s, q, lut, o, lse, ws, state, wbits, st)
-                                : run_sage_main_typed<__half, 64>(s, q, lut, o, lse, ws, state, wbits, st);
-  return s->dtype == SLA_BF16 ? run_sage_main_typed<__nv_bfloat16, 128>(s, q, lut, o, lse, ws, state, wbits, st)
-                              : run_sage_main_typed<__half, 128>(s, q, lut, o, lse, ws, state, wbits, st);
+    return s->dtype == SLA_BF16 ? run_sage_main_typed<__nv_bfloat16, 64>(s, q, lut, o, lse, ws, state, wbits, st, gather_dst, n_gather)
+                                : run_sage_main_typed<__half, 64>(s, q, lut, o, lse, ws, state, wbits, st, gather_dst, n_gather);
+  return s->dtype == SLA_BF16 ? run_sage_main_typed<__nv_bfloat16, 128>(s, q, lut, o, lse, ws, state, wbits, st, gather_dst, n_gather)
+                              : run_sage_main_typed<__half, 128>(s, q, lut, o, lse, ws, state, wbits, st, gather_dst, n_gather);
 }
 static int sage_check(const sla_shape* s) {
   int rc = validate_shape(s);
@@ -757,13 +779,18 @@ extern "C" int sage_sla_prepare(const sla_shape* s, const void* q, const void* k
   return sage_quant(s, q, k, v, base, st);
 }
 
-extern "C" int sage_sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
-                            const float* w, const float* bias, void* o, void* lin_state, void* ws, size_t ws_bytes,
-                            sla_stream_t stream) {
+static int sage_fwd_impl(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+                         const float* w, const float* bias, void* o, void* lin_state, void* ws, size_t ws_bytes,
+                         void* const* gather_dst, int n_gather, sla_stream_t stream) {
   using namespace sla;
   if (!q || !k || !v || !lut || !o || !ws) return SLA_ERR_NULL;
   int rc = sage_check(s);
   if (rc != SLA_OK) return rc;
+  if (n_gather < 0 || n_gather > 8 || (n_gather > 0 && gather_dst == nullptr)) return SLA_ERR_UNSUPPORTED;
+  for (int g = 0; g < n_gather; ++g) {
+    if (gather_dst[g] == nullptr) return SLA_ERR_NULL;
+    if (!aligned16(gather_dst[g])) return SLA_ERR_BAD_ALIGN;
+  }
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(ws)) return SLA_ERR_BAD_ALIGN;
   WsSage wsz = ws_sage(s);
   if (ws_bytes < wsz.total) return SLA_ERR_WS_TOO_SMALL;
@@ -779,5 +806,17 @@ extern "C" int sage_sla_fwd(const sla_shape* s, const void* q, const void* k, co
     state = lin_state;
   }
   if (!ready && (rc = sage_quant(s, q, k, v, base, st)) != SLA_OK) return rc;
-  return sage_main(s, q, lut, o, lse, base, state, base + wsz.wbits, st);
+  return sage_main(s, q, lut, o, lse, base, state, base + wsz.wbits, st, gather_dst, n_gather);
+}
+
+extern "C" int sage_sla_fwd(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+                            const float* w, const float* bias, void* o, void* lin_state, void* ws, size_t ws_bytes,
+                            sla_stream_t stream) {
+  return sage_fwd_impl(s, q, k, v, lut, w, bias, o, lin_state, ws, ws_bytes, nullptr, 0, stream);
+}
+
+extern "C" int sage_sla_fwd_gather(const sla_shape* s, const void* q, const void* k, const void* v, const int32_t* lut,
+                                   const float* w, const float* bias, void* o, void* lin_state, void* ws,
+                                   size_t ws_bytes, void* const* gather_dst, int n_gather, sla_stream_t stream) {
+  return sage_fwd_impl(s, q, k, v, lut, w, bias, o, lin_state, ws, ws_bytes, gather_dst, n_gather, stream);
 }

@@ -427,22 +427,30 @@ class _SageFused(torch.autograd.Function):
 
 
 def sage_sla_attention(q, k, v, weight, bias, bm: BlockMap, feature="softmax", sparse_only: bool = False,
-                       prep: Optional[LinearPrep] = None):
+                       prep: Optional[LinearPrep] = None, out: Optional[torch.Tensor] = None, gather_ptrs=None):
     """SageSLA/core.py:100-158: quantized sparse branch + linear branch + proj_l.
     ``sparse_only`` returns the quantized sparse branch alone (the o_s of SageSLA/core.py:114). When a gradient is
-    required it flows through the linear branch and proj_l only, as in the reference."""
+    required it flows through the linear branch and proj_l only, as in the reference. `out`, `gather_ptrs`: as in
+    `sla_attention` (forward without gradient only)."""
     _require_cuda(q, k, v, weight)
     need_grad = not sparse_only and torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (q, k, v, weight, bias))
     if need_grad:
+        if out is not None or gather_ptrs:
+            raise NotImplementedError("out= / gather_ptrs= of the quantized forward need torch.no_grad()")
         return _SageFused.apply(q, k, v, weight, bias, bm, feature, prep)
-    return _sage_forward(q, k, v, weight, bias, bm, feature, sparse_only, prep)[0]
+    return _sage_forward(q, k, v, weight, bias, bm, feature, sparse_only, prep, out, gather_ptrs)[0]
 
 
-def _sage_forward(q, k, v, weight, bias, bm, feature, sparse_only, prep):
+def _sage_forward(q, k, v, weight, bias, bm, feature, sparse_only, prep, out=None, gather_ptrs=None):
     B, H, L, D = q.shape
     flags = _lib.FLAG_SPARSE_ONLY if sparse_only else 0
-    o = torch.empty_like(q)
+    if out is not None:
+        if tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype or not out.is_contiguous():
+            raise ValueError("`out` must be a contiguous tensor of q's shape and dtype")
+        o = out
+    else:
+        o = torch.empty_like(q)
     if prep is not None:
         if prep.key != (B, H, L, D, 128, 64, bm.topk, q.dtype, feature, flags):
             raise ValueError("sage_prepare was called for another shape or configuration")
@@ -452,7 +460,12 @@ def _sage_forward(q, k, v, weight, bias, bm, feature, sparse_only, prep):
     if prep is None:
         lin_state = torch.empty((B, H, 2 * D * D + D), dtype=q.dtype, device=q.device)
         ws = _workspace(shape, _lib.OP_SAGE_FWD, q.device)
-    check(lib.sage_sla_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o),
-                           _p(lin_state), _p(ws), ws.numel(), _stream(q)))
+    if gather_ptrs:
+        dst = (C.c_void_p * len(gather_ptrs))(*[int(x) for x in gather_ptrs])
+        check(lib.sage_sla_fwd_gather(C.byref(shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o),
+                                      _p(lin_state), _p(ws), ws.numel(), dst, len(gather_ptrs), _stream(q)))
+    else:
+        check(lib.sage_sla_fwd(C.byref(shape), _p(q), _p(k), _p(v), _p(bm.lut), _p(weight), _p(bias), _p(o),
+                               _p(lin_state), _p(ws), ws.numel(), _stream(q)))
     _check_device()
     return o, lin_state

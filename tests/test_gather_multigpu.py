@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, n_units, L, D):
+def _worker(rank, world, port, n_units, L, D, quantized):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -25,7 +25,7 @@ def _worker(rank, world, port, n_units, L, D):
     dev = torch.device("cuda", rank)
     g = torch.Generator().manual_seed(123)
     q, k, v = (torch.randn(1, n_units, L, D, generator=g).bfloat16().to(dev) for _ in range(3))
-    m = sla_b200.SparseLinearAttention(D, 0.2).to(dev)
+    m = (sla_b200.SageSparseLinearAttention(D, 0.2) if quantized else sla_b200.SparseLinearAttention(D, 0.2)).to(dev)
     with torch.no_grad():
         m.proj_l.weight.copy_((torch.randn(D, D, generator=g) * 0.05).to(dev))
         m.proj_l.bias.copy_((torch.randn(D, generator=g) * 0.05).to(dev))
@@ -42,9 +42,9 @@ def _worker(rank, world, port, n_units, L, D):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("n_units", [4, 3])
-def test_forward_is_its_own_all_gather_on_two_gpus(n_units):
+@pytest.mark.parametrize("n_units,quantized", [(4, False), (3, False), (3, True)])
+def test_forward_is_its_own_all_gather_on_two_gpus(n_units, quantized):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(2, 29650 + n_units, n_units, 1500, 128), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, 29650 + n_units + 10 * quantized, n_units, 1500, 128, quantized), nprocs=2, join=True)

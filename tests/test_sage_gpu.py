@@ -123,3 +123,27 @@ def test_sage_module_backward_is_the_linear_branch(D, feature, L):
     assert_close_parity(vg.grad.float().cpu(), vd.grad, what="dv")
     assert_close_parity(m.proj_l.weight.grad.cpu(), wd.grad, l1_max=2e-2, what="dw")
     assert_close_parity(m.proj_l.bias.grad.cpu(), bd.grad, l1_max=2e-2, what="db")
+
+
+@pytest.mark.parametrize("D,L", [(128, 1100), (64, 900)])
+def test_sage_forward_writes_its_output_to_gather_destinations(D, L):
+    """sage_sla_fwd_gather on one GPU: two other buffers stand in for peer GPUs' memory (one of them a slice at an
+    offset inside a larger buffer). Each copy must equal o bit for bit, o must equal what sage_sla_fwd gives, and
+    memory around the slice must stay untouched."""
+    from sla_b200 import ops
+    B, H = 1, 2
+    q, k, v = (t.cuda() for t in _inputs(B, H, L, D, L, 0.5))
+    g = torch.Generator().manual_seed(L)
+    w = (torch.randn(D, D, generator=g) * 0.05).cuda()
+    b = (torch.randn(D, generator=g) * 0.05).cuda()
+    bm = ops.block_map(q, k, 0.25, 128, 64)
+    with torch.no_grad():
+        ref = ops.sage_sla_attention(q, k, v, w, b, bm)
+        n = q.numel()
+        plain = torch.full((n,), -7.0, dtype=torch.bfloat16, device="cuda")
+        big = torch.full((3 * n,), -7.0, dtype=torch.bfloat16, device="cuda")
+        o = ops.sage_sla_attention(q, k, v, w, b, bm, gather_ptrs=[plain.data_ptr(), big.data_ptr() + 2 * n])
+    torch.cuda.synchronize()
+    assert torch.equal(o, ref)
+    assert torch.equal(plain, ref.flatten())
+    assert torch.equal(big[n:2 * n], ref.flatten()) and bool((big[:n] == -7.0).all()) and bool((big[2 * n:] == -7.0).all())
