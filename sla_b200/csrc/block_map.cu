@@ -67,54 +67,150 @@ __global__ void kmean_finalize_kernel(const float* __restrict__ partial, float* 
   kmean[static_cast<size_t>(bh) * D + d] = round_to<TIn>(s / static_cast<float>(L));
 }
 
-// ---- 3. mean pooling of Q (z = 0) and of K - mean (z = 1), utils.py:21-40 ----
-template <typename TIn, int D>
-__global__ void __launch_bounds__(256) pool_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k,
-                                                   const float* __restrict__ kmean, TIn* __restrict__ pooled_q,
-                                                   TIn* __restrict__ pooled_k, int L, int blkq, int blkk) {
+// ---- 3. mean pooling of Q and of K - mean, utils.py:21-40 ----
+// One warp pools one block: a row is D / N lanes of 16 bytes, so a warp-wide load covers 32 * N / D rows and every
+// lane keeps N running sums; the row groups are folded with shuffles at the end. Eight blocks per CTA.
+constexpr int kPoolWarps = 8;
+
+template <typename TIn, int D, bool IS_K>
+__device__ inline void pool_blocks(const TIn* __restrict__ x, const float* __restrict__ kmean,
+                                   TIn* __restrict__ pooled, int L, int blk, int nblk) {
   constexpr int N = VecLoad<TIn>::N;
-  constexpr int TPR = D / N;
-  constexpr int RP = 256 / TPR;
-  __shared__ float red[RP][D];
-  pdl_wait();
-  const bool is_k = blockIdx.z == 1;
-  const int blk = is_k ? blkk : blkq;
-  const int nblk = (L + blk - 1) / blk;
-  if (static_cast<int>(blockIdx.x) >= nblk) return;
-  int bh = blockIdx.y, ib = blockIdx.x;
-  int tid = threadIdx.x, rg = tid / TPR, c = (tid % TPR) * N;
-  int row0 = ib * blk, row1 = min(L, row0 + blk);
-  const TIn* base = (is_k ? k : q) + static_cast<size_t>(bh) * L * D;
+  constexpr int TPR = D / N;        // lanes per row
+  constexpr int RPW = 32 / TPR;     // rows per warp-wide load
+  static_assert(TPR <= 32 && 32 % TPR == 0, "a row is a whole fraction of a warp");
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ib = blockIdx.x * kPoolWarps + warp, bh = blockIdx.y;
+  if (ib >= nblk) return;
+  const int rg = lane / TPR, c = (lane % TPR) * N;
+  const int row0 = ib * blk, row1 = min(L, row0 + blk);
+  const TIn* base = x + static_cast<size_t>(bh) * L * D + c;
   float mean[N];
 #pragma unroll
-  for (int i = 0; i < N; ++i) mean[i] = is_k ? kmean[static_cast<size_t>(bh) * D + c + i] : 0.f;
+  for (int i = 0; i < N; ++i) mean[i] = IS_K ? kmean[static_cast<size_t>(bh) * D + c + i] : 0.f;
   float acc[N];
 #pragma unroll
   for (int i = 0; i < N; ++i) acc[i] = 0.f;
-#pragma unroll 4
-  for (int r = row0 + rg; r < row1; r += RP) {
+#pragma unroll 8
+  for (int r = row0 + rg; r < row1; r += RPW) {
     float v[N];
-    VecLoad<TIn>::load(v, base + static_cast<size_t>(r) * D + c);
+    VecLoad<TIn>::load(v, base + static_cast<size_t>(r) * D);
 #pragma unroll
-    for (int i = 0; i < N; ++i) acc[i] += is_k ? round_to<TIn>(v[i] - mean[i]) : v[i];
+    for (int i = 0; i < N; ++i) acc[i] += IS_K ? round_to<TIn>(v[i] - mean[i]) : v[i];
   }
 #pragma unroll
-  for (int i = 0; i < N; ++i) red[rg][c + i] = acc[i];
-  __syncthreads();
-  if (tid < D) {
-    float s = 0.f;
-#pragma unroll 4
-    for (int g = 0; g < RP; ++g) s += red[g][tid];
-    float nx = static_cast<float>(row1 - row0);
-    TIn* out = (is_k ? pooled_k : pooled_q) + (static_cast<size_t>(bh) * nblk + ib) * D;
-    out[tid] = Elem<TIn>::from_f(s / nx);
+  for (int o = 16; o >= TPR; o >>= 1) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
   }
+  if (rg == 0) {
+    const float nx = static_cast<float>(row1 - row0);
+    alignas(16) TIn o[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) o[i] = Elem<TIn>::from_f(acc[i] / nx);
+    *reinterpret_cast<uint4*>(pooled + (static_cast<size_t>(bh) * nblk + ib) * D + c) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// z = 0: Q, z = 1: K - mean
+template <typename TIn, int D>
+__global__ void __launch_bounds__(kPoolWarps * 32) pool_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k,
+                                                               const float* __restrict__ kmean,
+                                                               TIn* __restrict__ pooled_q, TIn* __restrict__ pooled_k,
+                                                               int L, int blkq, int blkk, int mb, int nb) {
+  pdl_wait();
+  if (blockIdx.z == 0) pool_blocks<TIn, D, false>(q, nullptr, pooled_q, L, blkq, mb);
+  else pool_blocks<TIn, D, true>(k, kmean, pooled_k, L, blkk, nb);
 }
 
 // ---- 4. pooled scores + per-row top-k ----
 __device__ inline uint32_t order_key(float x) {
   uint32_t u = __float_as_uint(x);
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One warp selects the top-k of one row of order-preserving keys (shared memory, nb of them) by a bitwise search
+// for the k-th largest key and writes the selected indices in ascending order; ties at the k-th score go to the
+// lower index.
+template <typename TIn>
+__device__ inline void select_topk_row(const uint32_t* kr, int nb, int topk, int lane, int32_t* out,
+                                       int8_t* map_row, int32_t* cols) {
+  // Key of the topk-th largest element, one bit at a time from the top: the largest value v with
+  // count(key >= v) >= topk. Counting is a compare and an add per key and one warp reduction per bit; no
+  // histogram, so rows whose scores share their high bits (all of them) cost the same as any other.
+  // The first 32 * kKeyRegs keys of the row sit in registers (all of them up to 512 KV blocks), the rest is re-read
+  // from shared memory; a missing key is 0, below every candidate (a candidate has at least one bit set).
+  constexpr int kKeyRegs = 16;
+  uint32_t kreg[kKeyRegs];
+#pragma unroll
+  for (int i = 0; i < kKeyRegs; ++i) kreg[i] = lane + 32 * i < nb ? kr[lane + 32 * i] : 0u;
+  // Scores were rounded to TIn, so the kLowZero low bits of a score's fp32 pattern are clear. order_key() keeps
+  // them clear for a non-negative score and turns them all into ones for a negative one (it complements the
+  // pattern). Keys that agree above bit kLowZero have the same sign, hence the same low bits: the search only
+  // has to decide the high bits, and the low bits follow from the sign of what it found.
+  constexpr int kLowZero = std::is_same<TIn, __nv_bfloat16>::value ? 16 : (std::is_same<TIn, __half>::value ? 13 : 0);
+  uint32_t prefix = 0;
+  for (int bit = 31; bit >= kLowZero; --bit) {
+    const uint32_t cand = prefix | (1u << bit);
+    int c0 = 0, c1 = 0;
+#pragma unroll
+    for (int i = 0; i < kKeyRegs; i += 2) {
+      c0 += kreg[i] >= cand ? 1 : 0;
+      c1 += kreg[i + 1] >= cand ? 1 : 0;
+    }
+    for (int j = lane + 32 * kKeyRegs; j < nb; j += 32) c0 += kr[j] >= cand ? 1 : 0;
+    if (__reduce_add_sync(0xffffffffu, c0 + c1) >= topk) prefix = cand;
+  }
+  if (kLowZero > 0 && !(prefix & 0x80000000u)) prefix |= (1u << kLowZero) - 1u;   // k-th score is negative
+  int above = 0;
+#pragma unroll
+  for (int i = 0; i < kKeyRegs; ++i) above += kreg[i] > prefix ? 1 : 0;
+  for (int j = lane + 32 * kKeyRegs; j < nb; j += 32) above += kr[j] > prefix ? 1 : 0;
+  const int need = topk - __reduce_add_sync(0xffffffffu, above);
+  const uint32_t thr = prefix;  // key of the k-th largest; `need` of the elements equal to it are taken
+  int n_out = 0, eq_seen = 0;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  int n_eq = 0;
+#pragma unroll
+  for (int i = 0; i < kKeyRegs; ++i) n_eq += kreg[i] == thr ? 1 : 0;
+  for (int j = lane + 32 * kKeyRegs; j < nb; j += 32) n_eq += kr[j] == thr ? 1 : 0;
+  if (__reduce_add_sync(0xffffffffu, n_eq) == need) {
+    // no surplus ties at the threshold (nearly every row): exactly topk keys are >= thr, one ballot per 32 keys
+#pragma unroll 4
+    for (int base = 0; base < nb; base += 32) {
+      const int j = base + lane;
+      const bool sel = j < nb && kr[j] >= thr;
+      const uint32_t bs = __ballot_sync(0xffffffffu, sel);
+      if (sel) {
+        out[n_out + __popc(bs & lt_mask)] = j;
+        if (cols) atomicAdd(&cols[j + 1], 1);
+      }
+      if (map_row && j < nb) map_row[j] = sel ? 1 : 0;
+      n_out += __popc(bs);
+    }
+    return;
+  }
+  for (int base = 0; base < nb; base += 32) {
+    int j = base + lane;
+    uint32_t key = j < nb ? kr[j] : 0u;
+    bool gt = j < nb && key > thr;
+    bool eq = j < nb && key == thr;
+    uint32_t be = __ballot_sync(0xffffffffu, eq);
+    int eq_rank = eq_seen + __popc(be & lt_mask);
+    bool sel = gt || (eq && eq_rank < need);
+    uint32_t bs = __ballot_sync(0xffffffffu, sel);
+    // a row never emits more than topk entries, whatever the scores are (NaNs included): the LUT row, the 0/1
+    // map and the column counts are sized for exactly topk
+    sel = sel && n_out + __popc(bs & lt_mask) < topk;
+    bs = __ballot_sync(0xffffffffu, sel);
+    if (sel) {
+      out[n_out + __popc(bs & lt_mask)] = j;
+      if (cols) atomicAdd(&cols[j + 1], 1);
+    }
+    if (map_row && j < nb) map_row[j] = sel ? 1 : 0;
+    n_out += __popc(bs);
+    eq_seen += __popc(be);
+  }
 }
 
 constexpr int kTopkRows = 8;  // query-block rows per CTA == warps per CTA
@@ -198,65 +294,76 @@ __global__ void __launch_bounds__(kTopkRows * 32) score_topk_kernel(
 
   const int row = row_base + warp;
   if (row >= mb) return;
-  const uint32_t* kr = keys + warp * nb;
-  // Key of the topk-th largest element, one bit at a time from the top: the largest value v with
-  // count(key >= v) >= topk. Counting is a compare and an add per key and one warp reduction per bit; no
-  // histogram, so rows whose scores share their high bits (all of them) cost the same as any other.
-  // The first 32 * kKeyRegs keys of the row sit in registers (all of them up to 512 KV blocks), the rest is re-read
-  // from shared memory; a missing key is 0, below every candidate (a candidate has at least one bit set).
-  constexpr int kKeyRegs = 16;
-  uint32_t kreg[kKeyRegs];
+  select_topk_row<TIn>(keys + warp * nb, nb, topk, lane, lut + (static_cast<size_t>(bh) * mb + row) * topk,
+                       sparse_map ? sparse_map + (static_cast<size_t>(bh) * mb + row) * nb : nullptr,
+                       col_offsets ? col_offsets + static_cast<size_t>(bh) * (nb + 1) : nullptr);
+}
+
+// ---- 4b. the same for 16-bit inputs, scores on the tensor cores ----
+// One CTA scores kMmaRows query-block rows against every KV block of the head with mma.m16n8k16 (fp32 accumulate;
+// the products of two 16-bit values are exact in fp32, so only the order of the fp32 additions differs from the
+// scalar kernel above, as it does from any other GEMM), rounds each score to the input type (utils.py:59) and
+// selects per row as above. Operands go from global memory straight into fragments: the contraction index is
+// permuted so that a thread's share of 32 consecutive dimensions is the 16 contiguous bytes [8t, 8t + 8), the same
+// permutation on both operands, which leaves every dot product unchanged.
+constexpr int kMmaRows = 16;
+__host__ __device__ inline int score_key_stride(int nb) { return (nb + 31) / 32 * 32 + 8; }
+constexpr int kMmaWarps = 16;   // one row per warp in the selection phase
+
+template <typename TIn, int D>
+__global__ void __launch_bounds__(kMmaWarps * 32, 2) score_topk_mma_kernel(
+    const TIn* __restrict__ pooled_q, const TIn* __restrict__ pooled_k, int32_t* __restrict__ lut,
+    int8_t* __restrict__ sparse_map, int32_t* __restrict__ col_offsets, int mb, int nb, int topk) {
+  static_assert(D % 32 == 0, "head dimension in steps of 32");
+  constexpr int KP = D / 32;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw);   // [kMmaRows][stride]
+  const int stride = score_key_stride(nb);
+  const int bh = blockIdx.y, row_base = blockIdx.x * kMmaRows;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  pdl_wait();
+
+  // rows past the last query block repeat it; their scores are never selected from
+  const TIn* q0 = pooled_q + (static_cast<size_t>(bh) * mb + min(row_base + g, mb - 1)) * D + t * 8;
+  const TIn* q1 = pooled_q + (static_cast<size_t>(bh) * mb + min(row_base + g + 8, mb - 1)) * D + t * 8;
+  uint4 a0[KP], a1[KP];
 #pragma unroll
-  for (int i = 0; i < kKeyRegs; ++i) kreg[i] = lane + 32 * i < nb ? kr[lane + 32 * i] : 0u;
-  // Scores were rounded to TIn, so the kLowZero low bits of a score's fp32 pattern are clear. order_key() keeps
-  // them clear for a non-negative score and turns them all into ones for a negative one (it complements the
-  // pattern). Keys that agree above bit kLowZero have the same sign, hence the same low bits: the search only
-  // has to decide the high bits, and the low bits follow from the sign of what it found.
-  constexpr int kLowZero = std::is_same<TIn, __nv_bfloat16>::value ? 16 : (std::is_same<TIn, __half>::value ? 13 : 0);
-  uint32_t prefix = 0;
-  for (int bit = 31; bit >= kLowZero; --bit) {
-    const uint32_t cand = prefix | (1u << bit);
-    int c0 = 0, c1 = 0;
-#pragma unroll
-    for (int i = 0; i < kKeyRegs; i += 2) {
-      c0 += kreg[i] >= cand ? 1 : 0;
-      c1 += kreg[i + 1] >= cand ? 1 : 0;
-    }
-    for (int j = lane + 32 * kKeyRegs; j < nb; j += 32) c0 += kr[j] >= cand ? 1 : 0;
-    if (__reduce_add_sync(0xffffffffu, c0 + c1) >= topk) prefix = cand;
+  for (int kp = 0; kp < KP; ++kp) {
+    a0[kp] = __ldg(reinterpret_cast<const uint4*>(q0 + kp * 32));
+    a1[kp] = __ldg(reinterpret_cast<const uint4*>(q1 + kp * 32));
   }
-  if (kLowZero > 0 && !(prefix & 0x80000000u)) prefix |= (1u << kLowZero) - 1u;   // k-th score is negative
-  int above = 0;
+  const TIn* pkh = pooled_k + static_cast<size_t>(bh) * nb * D;
+  const int ntiles = (nb + 7) / 8;
+#pragma unroll 2
+  for (int nt = warp; nt < ntiles; nt += kMmaWarps) {
+    const TIn* kr = pkh + static_cast<size_t>(min(nt * 8 + g, nb - 1)) * D + t * 8;
+    uint4 b[KP];
 #pragma unroll
-  for (int i = 0; i < kKeyRegs; ++i) above += kreg[i] > prefix ? 1 : 0;
-  for (int j = lane + 32 * kKeyRegs; j < nb; j += 32) above += kr[j] > prefix ? 1 : 0;
-  const int need = topk - __reduce_add_sync(0xffffffffu, above);
-  const uint32_t thr = prefix;  // key of the k-th largest; `need` of the elements equal to it are taken
-  int32_t* out = lut + (static_cast<size_t>(bh) * mb + row) * topk;
-  int8_t* map_row = sparse_map ? sparse_map + (static_cast<size_t>(bh) * mb + row) * nb : nullptr;
-  int32_t* cols = col_offsets ? col_offsets + static_cast<size_t>(bh) * (nb + 1) : nullptr;
-  int n_out = 0, eq_seen = 0;
-  const uint32_t lt_mask = (1u << lane) - 1u;
-  for (int base = 0; base < nb; base += 32) {
-    int j = base + lane;
-    uint32_t key = j < nb ? kr[j] : 0u;
-    bool gt = j < nb && key > thr;
-    bool eq = j < nb && key == thr;
-    uint32_t be = __ballot_sync(0xffffffffu, eq);
-    int eq_rank = eq_seen + __popc(be & lt_mask);
-    bool sel = gt || (eq && eq_rank < need);
-    uint32_t bs = __ballot_sync(0xffffffffu, sel);
-    // a row never emits more than topk entries, whatever the scores are (NaNs included): the LUT row, the 0/1
-    // map and the column counts are sized for exactly topk
-    sel = sel && n_out + __popc(bs & lt_mask) < topk;
-    bs = __ballot_sync(0xffffffffu, sel);
-    if (sel) {
-      out[n_out + __popc(bs & lt_mask)] = j;
-      if (cols) atomicAdd(&cols[j + 1], 1);
+    for (int kp = 0; kp < KP; ++kp) b[kp] = __ldg(reinterpret_cast<const uint4*>(kr + kp * 32));
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int kp = 0; kp < KP; ++kp) {
+      const uint32_t lo[4] = {a0[kp].x, a1[kp].x, a0[kp].y, a1[kp].y};
+      const uint32_t hi[4] = {a0[kp].z, a1[kp].z, a0[kp].w, a1[kp].w};
+      mma16816<TIn>(acc, lo, b[kp].x, b[kp].y);
+      mma16816<TIn>(acc, hi, b[kp].z, b[kp].w);
     }
-    if (map_row && j < nb) map_row[j] = sel ? 1 : 0;
-    n_out += __popc(bs);
-    eq_seen += __popc(be);
+    // a row of keys is `stride` words, a multiple of 32 plus 8: the 8-byte stores of a half-warp (g = 0..3,
+    // t = 0..3) then fall on 32 different banks; the words past nb are padding that nothing reads
+    const int c = nt * 8 + 2 * t;
+    *reinterpret_cast<uint2*>(keys + g * stride + c) =
+        make_uint2(order_key(round_to<TIn>(acc[0])), order_key(round_to<TIn>(acc[1])));
+    *reinterpret_cast<uint2*>(keys + (g + 8) * stride + c) =
+        make_uint2(order_key(round_to<TIn>(acc[2])), order_key(round_to<TIn>(acc[3])));
+  }
+  __syncthreads();
+
+  for (int r = warp; r < kMmaRows; r += kMmaWarps) {
+    const int row = row_base + r;
+    if (row >= mb) break;
+    select_topk_row<TIn>(keys + r * stride, nb, topk, lane, lut + (static_cast<size_t>(bh) * mb + row) * topk,
+                         sparse_map ? sparse_map + (static_cast<size_t>(bh) * mb + row) * nb : nullptr,
+                         col_offsets ? col_offsets + static_cast<size_t>(bh) * (nb + 1) : nullptr);
   }
 }
 
@@ -296,25 +403,63 @@ __global__ void __launch_bounds__(1024) col_scan_kernel(int32_t* __restrict__ co
 }
 
 // ---- 6. column lists: for KV block j the ascending list of query blocks whose row selects j ----
+// One CTA fills the lists of 32 neighbouring KV blocks: a thread reads the 32 map bytes of one query-block row (one
+// 32-byte sector), each warp transposes its 32 x 32 bits with ballots so that lane c holds column c's rows, and
+// the position of a warp's first entry in a column is the column's running offset plus the counts of the warps
+// below it. Rows go in ascending order: passes, then warps, then bits.
 __global__ void __launch_bounds__(1024) col_fill_kernel(const int8_t* __restrict__ sparse_map,
                                                         const int32_t* __restrict__ col_offsets,
                                                         int32_t* __restrict__ col_index, int mb, int nb,
                                                         int topk) {
+  __shared__ int32_t cnt[32][33];   // [warp][column]
+  __shared__ int32_t col_pos[32];   // next free position of each column
   pdl_wait();
-  int bh = blockIdx.y;
-  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int j = blockIdx.x * 32 + warp;
-  if (j >= nb) return;
+  const int bh = blockIdx.y, j0 = blockIdx.x * 32;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int8_t* m = sparse_map + static_cast<size_t>(bh) * mb * nb;
   int32_t* out = col_index + static_cast<size_t>(bh) * mb * topk;
-  int pos = col_offsets[static_cast<size_t>(bh) * (nb + 1) + j];
-  const uint32_t lt_mask = (1u << lane) - 1u;
-  for (int i0 = 0; i0 < mb; i0 += 32) {
-    int i = i0 + lane;
-    bool f = i < mb && m[static_cast<size_t>(i) * nb + j] != 0;
-    uint32_t b = __ballot_sync(0xffffffffu, f);
-    if (f) out[pos + __popc(b & lt_mask)] = i;
-    pos += __popc(b);
+  if (warp == 0) col_pos[lane] = j0 + lane < nb ? col_offsets[static_cast<size_t>(bh) * (nb + 1) + j0 + lane] : 0;
+  const bool vec = nb % 16 == 0 && j0 + 32 <= nb &&
+                   (reinterpret_cast<uintptr_t>(sparse_map) & 15) == 0;   // every row's 32 bytes 16-byte aligned
+  auto nonzero4 = [](uint32_t w) {   // bit b set when byte b of w is not zero
+    uint32_t y = __vcmpne4(w, 0u) & 0x08040201u;
+    return (y | (y >> 8) | (y >> 16) | (y >> 24)) & 0xfu;
+  };
+  for (int i0 = 0; i0 < mb; i0 += 1024) {
+    const int i = i0 + tid;
+    uint32_t mask = 0;
+    if (i < mb) {
+      const int8_t* row = m + static_cast<size_t>(i) * nb + j0;
+      if (vec) {
+        const uint4 x = *reinterpret_cast<const uint4*>(row), y = *reinterpret_cast<const uint4*>(row + 16);
+        mask = nonzero4(x.x) | nonzero4(x.y) << 4 | nonzero4(x.z) << 8 | nonzero4(x.w) << 12 |
+               nonzero4(y.x) << 16 | nonzero4(y.y) << 20 | nonzero4(y.z) << 24 | nonzero4(y.w) << 28;
+      } else {
+        for (int c = 0; c < 32 && j0 + c < nb; ++c) mask |= row[c] != 0 ? 1u << c : 0u;
+      }
+    }
+    uint32_t colbits = 0;   // lane c: which of this warp's 32 rows select column j0 + c
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      const uint32_t b = __ballot_sync(0xffffffffu, (mask >> c) & 1u);
+      if (lane == c) colbits = b;
+    }
+    cnt[warp][lane] = __popc(colbits);
+    __syncthreads();
+    int pos = col_pos[lane];
+    for (int w = 0; w < warp; ++w) pos += cnt[w][lane];
+    while (colbits) {
+      out[pos++] = i0 + warp * 32 + __ffs(colbits) - 1;
+      colbits &= colbits - 1;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      int tot = 0;
+#pragma unroll 8
+      for (int w = 0; w < 32; ++w) tot += cnt[w][lane];
+      col_pos[lane] += tot;
+    }
+    __syncthreads();
   }
 }
 
@@ -356,8 +501,9 @@ static int launch_block_map(const sla_shape* s, const TIn* q, const TIn* k, int3
   SLA_LAUNCH_OK();
   SLA_CUDA_OK(launch_pdl<false>(kmean_finalize_kernel<TIn>, dim3(bh), dim3(D), 0, st, partial, kmean, L, w.nch, D));
   SLA_LAUNCH_OK();
-  SLA_CUDA_OK(launch_pdl<false>(pool_kernel<TIn, D>, dim3(max(mb, nb), bh, 2), dim3(256), 0, st, q, k, kmean, pq, pk, L,
-                         s->BLKQ, s->BLKK));
+  SLA_CUDA_OK(launch_pdl<false>(pool_kernel<TIn, D>, dim3(ceil_div(max(mb, nb), kPoolWarps), bh, 2),
+                                dim3(kPoolWarps * 32), 0, st, q, k, static_cast<const float*>(kmean), pq, pk, L,
+                                s->BLKQ, s->BLKK, mb, nb));
   SLA_LAUNCH_OK();
   return score_and_select<TIn, D>(s, pq, pk, lut, sparse_map, col_offsets, col_index, st);
 }
@@ -370,13 +516,25 @@ static int score_and_select(const sla_shape* s, const TIn* pq, const TIn* pk, in
   const int mb = ceil_div(L, s->BLKQ), nb = ceil_div(L, s->BLKK);
   const bool want_cols = col_offsets != nullptr && col_index != nullptr;
   if (want_cols) SLA_CUDA_OK(cudaMemsetAsync(col_offsets, 0, sizeof(int32_t) * size_t(bh) * (nb + 1), st));
-  size_t smem = (size_t(kTopkRows) * (2 * D + nb) * 4 + 15) / 16 * 16 + size_t(kScoreStages) * 2 * kTopkRows * 32 * 16;
-  if (smem > 200 * 1024) return SLA_ERR_BAD_SHAPE;
-  auto kern = score_topk_kernel<TIn, D>;
-  SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  SLA_CUDA_OK(launch_pdl<false>(kern, dim3(ceil_div(mb, kTopkRows), bh), dim3(kTopkRows * 32), smem, st, pq, pk, lut,
-                         sparse_map, want_cols ? col_offsets : nullptr, mb, nb, s->topk));
-  SLA_LAUNCH_OK();
+  if constexpr (sizeof(TIn) == 2) {
+    const size_t smem = size_t(kMmaRows) * score_key_stride(nb) * 4;
+    if (smem > 200 * 1024) return SLA_ERR_BAD_SHAPE;
+    auto kern = score_topk_mma_kernel<TIn, D>;
+    SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    SLA_CUDA_OK(launch_pdl<false>(kern, dim3(ceil_div(mb, kMmaRows), bh), dim3(kMmaWarps * 32), smem, st, pq, pk, lut,
+                                  sparse_map, want_cols ? col_offsets : nullptr, mb, nb, s->topk));
+    SLA_LAUNCH_OK();
+  } else {
+    // fp32 inputs: the scalar kernel (one sequential fp32 sum per score)
+    const size_t smem =
+        (size_t(kTopkRows) * (2 * D + nb) * 4 + 15) / 16 * 16 + size_t(kScoreStages) * 2 * kTopkRows * 32 * 16;
+    if (smem > 200 * 1024) return SLA_ERR_BAD_SHAPE;
+    auto kern = score_topk_kernel<TIn, D>;
+    SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    SLA_CUDA_OK(launch_pdl<false>(kern, dim3(ceil_div(mb, kTopkRows), bh), dim3(kTopkRows * 32), smem, st, pq, pk, lut,
+                                  sparse_map, want_cols ? col_offsets : nullptr, mb, nb, s->topk));
+    SLA_LAUNCH_OK();
+  }
   if (want_cols) {
     SLA_CUDA_OK(launch_pdl<false>(col_scan_kernel, dim3(bh), dim3(1024), 0, st, col_offsets, nb));
     SLA_LAUNCH_OK();
