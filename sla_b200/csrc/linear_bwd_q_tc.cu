@@ -6,11 +6,11 @@
 // db += sum_m dY_m).
 //
 // One CTA = one chunk of rows of one head (the chunking of the mma.sync pass A: same partial buffers, same
-// per-head reduction kernels afterwards). 320 threads: warps 0-7 are the row warps, two threads per tile row (thread
-// (row, h) owns columns [64 h, 64 h + 64); TMEM lane = row), warp 8 is the TMA producer and sums the columns of dY
-// for db, warp 9 issues the MMAs and sums the columns of phi_q / den for dz. Shared memory holds H W^T (32 KB) and
-// ONE {Q, dY} tile pair (64 KB): two CTAs share an SM, and one computes while the other waits for its loads.
-// Tensor memory: G (128 columns, accumulated over the CTA's tiles) and t (128 columns).
+// per-head reduction kernels afterwards). 192 threads: warps 0-3 own one tile row each (thread = row = TMEM lane),
+// warp 4 is the TMA producer and sums the columns of dY for db, warp 5 issues the MMAs and sums the columns
+// of phi_q / den for dz. Shared memory holds H W^T (32 KB) and ONE {Q, dY} tile pair (64 KB): two CTAs share
+// an SM, and one computes while the other waits for its loads. Tensor memory: G (128 columns, accumulated
+// over the CTA's tiles) and t (128 columns, which first park exp(q - max) of the softmax feature map).
 //   Q tile:  q  ->  phi_q / den (MN-major B operand of the G GEMM, then read for dz)
 //   dY tile: K-major A operand of the t GEMM, MN-major A operand of the G GEMM  ->  dq staging for the TMA store
 // All waits are bounded (tc_common.cuh).
@@ -30,7 +30,6 @@ struct LinQParams {
   const void* lin_state;   // [BH][2*D*D + D] T: H, z, H W^T
   float* g_partial;        // [BH][NCH][D*D + 2*D]
   int* err;
-  long long* trace;        // optional: 8 words per CTA, SM clocks tid 0 spent in each phase of a tile, summed over tiles
   int L, nch, rows, feature, accumulate;
 };
 
@@ -39,13 +38,13 @@ __device__ __forceinline__ float ex2f(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
-// OR of a predicate over the 256 threads of the row warps (named barrier 1); the result is the same in all of them
+// OR of a predicate over the 128 threads of the row warps (named barrier 1); the result is the same in all of them
 __device__ __forceinline__ bool rows_any(bool pred) {
   uint32_t out;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.u32 q, %1, 0;\n\t"
-      "barrier.cta.red.or.pred p, 1, 256, q;\n\t"
+      "barrier.cta.red.or.pred p, 1, 128, q;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}\n"
       : "=r"(out)
       : "r"(static_cast<uint32_t>(pred))
@@ -54,7 +53,7 @@ __device__ __forceinline__ bool rows_any(bool pred) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(320, 2)
+__global__ void __launch_bounds__(192, 2)
 linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDY,
                        const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmHW,
                        LinQParams p) {
@@ -73,7 +72,6 @@ linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   __shared__ __align__(16) float s_z[D];
   __shared__ __align__(16) uint32_t s_zp[D / 2];     // z as pairs of T
   __shared__ float s_rowc[128];        // dden * den of the tile's rows
-  __shared__ float2 s_ex[4][2][128];   // values the two threads of a row hand each other
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int ch = blockIdx.x, bh = blockIdx.y;
@@ -98,7 +96,7 @@ linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     mbar_init(BAR(B_HW), 1);
     mbar_init(BAR(B_FULL), 1);
     mbar_init(BAR(B_FREE), 2);
-    mbar_init(BAR(B_X), 8);
+    mbar_init(BAR(B_X), 4);
     mbar_init(BAR(B_T), 1);
     mbar_init(BAR(B_G), 1);
     mbar_init(BAR(B_C), 4);
@@ -108,8 +106,8 @@ linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   }
   if (tid < D) s_z[tid] = Elem<T>::to_f(rec[D * D + tid]);
   if (tid < D / 2) s_zp[tid] = reinterpret_cast<const uint32_t*>(rec + D * D)[tid];
-  if (warp == 8 && lane == 0) { prefetch_tmap(&tmQ); prefetch_tmap(&tmDY); prefetch_tmap(&tmDQ); prefetch_tmap(&tmHW); }
-  if (warp == 9) {
+  if (warp == 4 && lane == 0) { prefetch_tmap(&tmQ); prefetch_tmap(&tmDY); prefetch_tmap(&tmDQ); prefetch_tmap(&tmHW); }
+  if (warp == 5) {
     tmem_alloc(smem_u32(&s_tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
@@ -126,7 +124,7 @@ linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     return static_cast<uint32_t>(slab * SLAB + m * 128 + ((((c >> 3) ^ (m & 7))) << 4) + (c & 7) * 2);
   };
 
-  if (warp == 8) {
+  if (warp == 4) {
     // ------------------------------ TMA producer, and db = column sums of dY ------------------------------
     float db[4] = {0.f, 0.f, 0.f, 0.f};
     bool ok = !*abortp;
@@ -164,7 +162,7 @@ linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (hw_issued && lane == 0) mbar_wait(BAR(B_HW), 0, kLErrHw, p.err);   // H W^T has landed before the CTA leaves
 #pragma unroll
     for (int e = 0; e < 4; ++e) out[D * D + D + 4 * lane + e] = db[e];
-  } else if (warp == 9) {
+  } else if (warp == 5) {
     // ------------------------------ MMA issuer, and dz = column sums of c_m phi_q,m / den_m ------------------------------
     float dz[4] = {0.f, 0.f, 0.f, 0.f};
     bool ok = !*abortp && warp_all(mbar_wait(BAR(B_HW), 0, kLErrHw, p.err));
@@ -207,12 +205,8 @@ linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     for (int e = 0; e < 4; ++e) out[D * D + 4 * lane + e] = dz[e];
   } else {
     // ------------------------------ row warps ------------------------------
-    // Two threads per tile row: thread (row, h) owns columns [64 h, 64 h + 64). What a row needs from both halves
-    // (maximum, sums) is exchanged through shared memory; every exchange is a barrier over all 256 row threads, so
-    // the outcome of each bounded wait is first made uniform over them (rows_any) and all of them leave together.
-    const int row = tid & 127, h = tid >> 7;
-    const int ch0 = h * (D / 16);                              // first 16-byte chunk (8 columns) of the half row
-    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int row = tid;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     // 16-byte chunk ch (8 columns) of this thread's row inside a swizzled 128-row tile
     auto chunk_addr = [&](uint32_t tile_base, int ch) {
       return tile_base + (ch >> 3) * SLAB + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
@@ -223,179 +217,164 @@ linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const float2 a = Elem<T>::unpack2(w0), b = Elem<T>::unpack2(w1), c = Elem<T>::unpack2(w2), d = Elem<T>::unpack2(w3);
       f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
     };
-    // the other half's pair of values; lo/hi order the two halves so that both threads of a row form the same sums
-    auto exchange = [&](int slot, float2 mine) {
-      s_ex[slot][h][row] = mine;
-      asm volatile("bar.sync 1, 256;\n" ::: "memory");
-      return s_ex[slot][h ^ 1][row];
-    };
-    auto lo_hi_sum = [&](float mine, float theirs) { return h == 0 ? mine + theirs : theirs + mine; };
     const bool softmax = p.feature == SLA_PHI_SOFTMAX;
-    bool ok = !rows_any(*abortp != 0);
-    long long* trc = (p.trace != nullptr && tid == 0) ? p.trace + 8 * (static_cast<size_t>(bh) * gridDim.x + ch) : nullptr;
-    long long tacc[6] = {0, 0, 0, 0, 0, 0};
-    const long long t_begin = trc ? clock64() : 0;
-    long long tc = t_begin;
-    auto lap = [&](int i) {
-      if (trc) { const long long now = clock64(); tacc[i] += now - tc; tc = now; }
-    };
-    for (int t = 0; ok && t < n_tiles; ++t) {
+    bool ok = warp_all(!*abortp);
+    for (int t = 0; t < n_tiles; ++t) {
       const int row0 = row_begin + t * 128;
-      uint32_t ph[D / 4];        // phi(q) of the half row as pairs of T; later dq_lin
-      ok = !rows_any(!mbar_wait(BAR(B_FULL), t & 1, kLErrFull, p.err));
-      if (!ok) break;
-      lap(0);
-      // ---- phi(q) (core.py:90), den = 1e-5 + sum_d round(phi_d z_d) (core.py:95) ----
-      float dsum = 0.f, sum_pz = 0.f;
-      auto take_phi = [&](int ch, const float (&f)[8]) {
-        const uint4 zq = *reinterpret_cast<const uint4*>(&s_zp[ch * 4]);
-        const uint32_t zz[4] = {zq.x, zq.y, zq.z, zq.w};
+      uint32_t ph[D / 2];        // phi(q) of the row as pairs of T; later dq_lin
+      float rd = 0.f, den = 0.f, sum_pz = 0.f;
+      ok = ok && warp_all(mbar_wait(BAR(B_FULL), t & 1, kLErrFull, p.err));
+      if (ok) {
+        // ---- phi(q) (core.py:90), den = 1e-5 + sum_d round(phi_d z_d) (core.py:95) ----
+        float dsum = 0.f;
+        auto take_phi = [&](int ch, const float (&f)[8]) {
+          const uint4 zq = *reinterpret_cast<const uint4*>(&s_zp[ch * 4]);
+          const uint32_t zz[4] = {zq.x, zq.y, zq.z, zq.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t w = Elem<T>::pack2(f[2 * i], f[2 * i + 1]);
-          ph[(ch - ch0) * 4 + i] = w;
-          const float2 pz = Elem<T>::unpack2(Elem<T>::mul2(w, zz[i]));   // each product rounded to T
-          dsum += pz.x + pz.y;
-          const float2 pf = Elem<T>::unpack2(w), zf = Elem<T>::unpack2(zz[i]);
-          sum_pz = fmaf(pf.x, zf.x, fmaf(pf.y, zf.y, sum_pz));
-        }
-      };
-      if (softmax) {
-        uint32_t m0, m1, m2, m3;                 // row maximum on the packed pairs (exact: no rounding in a max)
-        ld_shared_v4(chunk_addr(sQ, ch0), m0, m1, m2, m3);
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t w = Elem<T>::pack2(f[2 * i], f[2 * i + 1]);
+            ph[ch * 4 + i] = w;
+            const float2 pz = Elem<T>::unpack2(Elem<T>::mul2(w, zz[i]));   // each product rounded to T
+            dsum += pz.x + pz.y;
+            const float2 pf = Elem<T>::unpack2(w), zf = Elem<T>::unpack2(zz[i]);
+            sum_pz = fmaf(pf.x, zf.x, fmaf(pf.y, zf.y, sum_pz));
+          }
+        };
+        if (softmax) {
+          uint32_t m0, m1, m2, m3;                 // row maximum on the packed pairs (exact: no rounding in a max)
+          ld_shared_v4(chunk_addr(sQ, 0), m0, m1, m2, m3);
 #pragma unroll
-        for (int c = 1; c < D / 16; ++c) {
-          uint32_t w0, w1, w2, w3;
-          ld_shared_v4(chunk_addr(sQ, ch0 + c), w0, w1, w2, w3);
-          m0 = Elem<T>::max2(m0, w0); m1 = Elem<T>::max2(m1, w1);
-          m2 = Elem<T>::max2(m2, w2); m3 = Elem<T>::max2(m3, w3);
-        }
-        const float2 mxp = Elem<T>::unpack2(Elem<T>::max2(Elem<T>::max2(m0, m1), Elem<T>::max2(m2, m3)));
-        const float mx_mine = fmaxf(mxp.x, mxp.y);
-        const float neg_mx = -fmaxf(mx_mine, exchange(0, make_float2(mx_mine, 0.f)).x) * kLog2e;
-        // exp(x - max) is formed twice, once for the row sum and once for phi: cheaper than keeping 64 fp32 values
-        float e0 = 0.f, e1 = 0.f;
+          for (int ch = 1; ch < D / 8; ++ch) {
+            uint32_t w0, w1, w2, w3;
+            ld_shared_v4(chunk_addr(sQ, ch), w0, w1, w2, w3);
+            m0 = Elem<T>::max2(m0, w0); m1 = Elem<T>::max2(m1, w1);
+            m2 = Elem<T>::max2(m2, w2); m3 = Elem<T>::max2(m3, w3);
+          }
+          const float2 mxp = Elem<T>::unpack2(Elem<T>::max2(Elem<T>::max2(m0, m1), Elem<T>::max2(m2, m3)));
+          const float neg_mx = -fmaxf(mxp.x, mxp.y) * kLog2e;
+          // exp(x - max) in fp32 is parked in the t columns of this thread's TMEM lane (idle until phi is written)
+          float e0 = 0.f, e1 = 0.f;
 #pragma unroll
-        for (int c = 0; c < D / 16; ++c) {
-          float f[8];
-          load_x(ch0 + c, f);
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t ev[32];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float e = ex2f(fmaf(f[i], kLog2e, neg_mx));
-            if (i & 1) e1 += e; else e0 += e;
+            for (int q4 = 0; q4 < 4; ++q4) {
+              float f[8];
+              load_x((c0 >> 3) + q4, f);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float e = ex2f(fmaf(f[i], kLog2e, neg_mx));
+                if (i & 1) e1 += e; else e0 += e;
+                ev[q4 * 8 + i] = __float_as_uint(e);
+              }
+            }
+            tmem_st_x32(tmem + lane_addr + COL_T + c0, ev);
+          }
+          tmem_wait_st();
+          const float inv_s = 1.f / (e0 + e1);
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t ev[32];
+            tmem_ld_x32(tmem + lane_addr + COL_T + c0, ev);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(ev[q4 * 8 + i]) * inv_s;
+              take_phi((c0 >> 3) + q4, f);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < D / 8; ++ch) {
+            float f[8];
+            load_x(ch, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (p.feature == SLA_PHI_RELU) f[i] = fmaxf(f[i], 0.f);
+              else f[i] = f[i] > 0.f ? f[i] + 1.f : __expf(f[i]);      // elu(x) + 1
+            }
+            take_phi(ch, f);
           }
         }
-        const float es_mine = e0 + e1;
-        const float inv_s = 1.f / lo_hi_sum(es_mine, exchange(1, make_float2(es_mine, 0.f)).x);
+        den = round_to<T>(1e-5f + round_to<T>(dsum));
+        rd = 1.f / den;
+        // phi_q / den over the row of the Q tile: B operand of the G GEMM
 #pragma unroll
-        for (int c = 0; c < D / 16; ++c) {
-          float f[8];
-          load_x(ch0 + c, f);
+        for (int ch = 0; ch < D / 8; ++ch) {
+          uint32_t w[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = ex2f(fmaf(f[i], kLog2e, neg_mx)) * inv_s;
-          take_phi(ch0 + c, f);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < D / 16; ++c) {
-          float f[8];
-          load_x(ch0 + c, f);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (p.feature == SLA_PHI_RELU) f[i] = fmaxf(f[i], 0.f);
-            else f[i] = f[i] > 0.f ? f[i] + 1.f : __expf(f[i]);      // elu(x) + 1
+          for (int i = 0; i < 4; ++i) {
+            const float2 pf = Elem<T>::unpack2(ph[ch * 4 + i]);
+            w[i] = Elem<T>::pack2(pf.x * rd, pf.y * rd);
           }
-          take_phi(ch0 + c, f);
+          st_shared_v4(chunk_addr(sQ, ch), w[0], w[1], w[2], w[3]);
         }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive_warp(BAR(B_X), lane);
       }
-      {
-        const float2 o = exchange(2, make_float2(dsum, sum_pz));
-        dsum = lo_hi_sum(dsum, o.x);
-        sum_pz = lo_hi_sum(sum_pz, o.y);
-      }
-      const float den = round_to<T>(1e-5f + round_to<T>(dsum));
-      const float rd = 1.f / den;
-      // phi_q / den over the half row of the Q tile: B operand of the G GEMM
+      ok = ok && warp_all(mbar_wait(BAR(B_T), t & 1, kLErrT, p.err));
+      if (ok) {
+        tc_fence_after();
+        // ---- s = phi_q . t, dden = -s / den^2 ----
+        float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < D / 16; ++c) {
-        uint32_t w[4];
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t tv[32];
+          tmem_ld_x32(tmem + lane_addr + COL_T + c0, tv);
+          tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 pf = Elem<T>::unpack2(ph[c * 4 + i]);
-          w[i] = Elem<T>::pack2(pf.x * rd, pf.y * rd);
+          for (int i = 0; i < 16; ++i) {
+            const float2 pf = Elem<T>::unpack2(ph[(c0 >> 1) + i]);
+            s0 = fmaf(pf.x, __uint_as_float(tv[2 * i]), s0);
+            s1 = fmaf(pf.y, __uint_as_float(tv[2 * i + 1]), s1);
+          }
         }
-        st_shared_v4(chunk_addr(sQ, ch0 + c), w[0], w[1], w[2], w[3]);
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive_warp(BAR(B_X), lane);
-      lap(1);
-
-      ok = !rows_any(!mbar_wait(BAR(B_T), t & 1, kLErrT, p.err));
-      if (!ok) break;
-      lap(2);
-      tc_fence_after();
-      // ---- s = phi_q . t, dden = -s / den^2 ----
-      float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-      for (int c0 = 0; c0 < D / 2; c0 += 32) {
-        uint32_t tv[32];
-        tmem_ld_x32(tmem + lane_addr + COL_T + h * (D / 2) + c0, tv);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 pf = Elem<T>::unpack2(ph[(c0 >> 1) + i]);
-          s0 = fmaf(pf.x, __uint_as_float(tv[2 * i]), s0);
-          s1 = fmaf(pf.y, __uint_as_float(tv[2 * i + 1]), s1);
-        }
-      }
-      const float sd_mine = s0 + s1;
-      const float sdot = lo_hi_sum(sd_mine, exchange(3, make_float2(sd_mine, 0.f)).x);
-      const float dden = -sdot * rd * rd;
-      if (h == 0) {
+        const float sdot = s0 + s1;
+        const float dden = -sdot * rd * rd;
         s_rowc[row] = dden * den;
         mbar_arrive_warp(BAR(B_C), lane);
-      }
-      const float c2 = softmax ? fmaf(rd, sdot, dden * sum_pz) : 0.f;   // sum_d phi_d dphi_d
-      // ---- dphi_q = t / den + dden z, dq_lin = phi'(q) dphi_q ----
+        const float c2 = softmax ? fmaf(rd, sdot, dden * sum_pz) : 0.f;   // sum_d phi_d dphi_d
+        // ---- dphi_q = t / den + dden z, dq_lin = phi'(q) dphi_q ----
 #pragma unroll
-      for (int c0 = 0; c0 < D / 2; c0 += 32) {
-        uint32_t tv[32];
-        tmem_ld_x32(tmem + lane_addr + COL_T + h * (D / 2) + c0, tv);
-        tmem_wait_ld();
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t tv[32];
+          tmem_ld_x32(tmem + lane_addr + COL_T + c0, tv);
+          tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 pf = Elem<T>::unpack2(ph[(c0 >> 1) + i]);
-          const float2 zf = *reinterpret_cast<const float2*>(&s_z[h * (D / 2) + c0 + 2 * i]);
-          // dphi (minus the softmax's sum_d phi_d dphi_d, c2 = 0 for the other feature maps)
-          float g0 = fmaf(__uint_as_float(tv[2 * i]), rd, fmaf(dden, zf.x, -c2));
-          float g1 = fmaf(__uint_as_float(tv[2 * i + 1]), rd, fmaf(dden, zf.y, -c2));
-          if (softmax) {
-            g0 *= pf.x;
-            g1 *= pf.y;
-          } else if (p.feature == SLA_PHI_RELU) {
-            g0 = pf.x > 0.f ? g0 : 0.f;
-            g1 = pf.y > 0.f ? g1 : 0.f;
-          } else {                                   // elu(x) + 1: derivative 1 for x > 0 (phi > 1), phi otherwise
-            g0 = pf.x > 1.f ? g0 : g0 * pf.x;
-            g1 = pf.y > 1.f ? g1 : g1 * pf.y;
+          for (int i = 0; i < 16; ++i) {
+            const float2 pf = Elem<T>::unpack2(ph[(c0 >> 1) + i]);
+            const float2 zf = *reinterpret_cast<const float2*>(&s_z[c0 + 2 * i]);
+            // dphi (minus the softmax's sum_d phi_d dphi_d, c2 = 0 for the other feature maps)
+            float g0 = fmaf(__uint_as_float(tv[2 * i]), rd, fmaf(dden, zf.x, -c2));
+            float g1 = fmaf(__uint_as_float(tv[2 * i + 1]), rd, fmaf(dden, zf.y, -c2));
+            if (softmax) {
+              g0 *= pf.x;
+              g1 *= pf.y;
+            } else if (p.feature == SLA_PHI_RELU) {
+              g0 = pf.x > 0.f ? g0 : 0.f;
+              g1 = pf.y > 0.f ? g1 : 0.f;
+            } else {                                   // elu(x) + 1: derivative 1 for x > 0 (phi > 1), phi otherwise
+              g0 = pf.x > 1.f ? g0 : g0 * pf.x;
+              g1 = pf.y > 1.f ? g1 : g1 * pf.y;
+            }
+            ph[(c0 >> 1) + i] = Elem<T>::pack2(g0, g1);
           }
-          ph[(c0 >> 1) + i] = Elem<T>::pack2(g0, g1);
         }
+        tc_fence_before();
       }
-      tc_fence_before();
-      lap(3);
       // dq is staged over the dY tile once the G GEMM and the db sums have read it
-      ok = mbar_wait(BAR(B_G), t & 1, kLErrG, p.err) && mbar_wait(BAR(B_DB), t & 1, kLErrDb, p.err);
+      ok = ok && warp_all(mbar_wait(BAR(B_G), t & 1, kLErrG, p.err) && mbar_wait(BAR(B_DB), t & 1, kLErrDb, p.err));
       if (ok) {
 #pragma unroll
-        for (int c = 0; c < D / 16; ++c)
-          st_shared_v4(chunk_addr(sDY, ch0 + c), ph[c * 4], ph[c * 4 + 1], ph[c * 4 + 2], ph[c * 4 + 3]);
+        for (int ch = 0; ch < D / 8; ++ch)
+          st_shared_v4(chunk_addr(sDY, ch), ph[ch * 4], ph[ch * 4 + 1], ph[ch * 4 + 2], ph[ch * 4 + 3]);
         fence_proxy_async_smem();
       }
-      ok = !rows_any(!ok || *abortp != 0);
-      if (!ok) break;
-      lap(4);
+      const bool failed = rows_any(!ok || *abortp != 0);
+      if (failed) { ok = false; break; }
       if (tid == 0) {
         for (int c = 0; c < 2; ++c) {
           if (p.accumulate) tma_reduce_add_3d(&tmDQ, sDY + c * SLAB, c * 64, row0, bh);
@@ -405,24 +384,17 @@ linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tma_store_wait_read();
         mbar_arrive(BAR(B_FREE));
       }
-      lap(5);
-    }
-    if (trc) {
-#pragma unroll
-      for (int i = 0; i < 6; ++i) trc[i] = tacc[i];
-      trc[6] = clock64() - t_begin;
-      trc[7] = n_tiles;
     }
     if (!ok) *abortp = 1;
-    // ---- G of this chunk: row n of G[n][i] is this thread's TMEM lane, columns of its half ----
+    // ---- G of this chunk: row n of G[n][i] is this thread's TMEM lane ----
     if (ok) {
       tc_fence_after();
-      float* grow = out + static_cast<size_t>(row) * D + h * (D / 2);
+      float* grow = out + static_cast<size_t>(row) * D;
 #pragma unroll
-      for (int c0 = 0; c0 < D / 2; c0 += 32) {
+      for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t gv[32];
         if (n_tiles > 0) {
-          tmem_ld_x32(tmem + lane_addr + COL_G + h * (D / 2) + c0, gv);
+          tmem_ld_x32(tmem + lane_addr + COL_G + c0, gv);
           tmem_wait_ld();
         } else {
 #pragma unroll
@@ -438,7 +410,7 @@ linear_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 5) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -462,12 +434,11 @@ static int launch_lin_q_tc(const sla_shape* s, const LinBwdParams& lp, cudaStrea
   p.g_partial = lp.g_partial;
   p.err = tc_error_word();
   if (p.err == nullptr) return SLA_ERR_CUDA;
-  p.trace = trace_buffer() ? trace_buffer() + 32768 : nullptr;   // behind the other kernels' timelines
   p.L = s->L; p.nch = lp.nch; p.rows = lp.rows; p.feature = s->feature_map; p.accumulate = lp.accumulate;
   auto kern = tc::linear_bwd_q_tc_kernel<T>;
   const int smem = 1024 + 3 * 2 * 128 * 128;
   SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  SLA_CUDA_OK(launch_pdl(kern, dim3(lp.nch, bh), dim3(320), smem, st, tq, tdy, tdq, thw, p));
+  SLA_CUDA_OK(launch_pdl(kern, dim3(lp.nch, bh), dim3(192), smem, st, tq, tdy, tdq, thw, p));
   SLA_LAUNCH_OK();
   return SLA_OK;
 }
