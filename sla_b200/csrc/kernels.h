@@ -107,5 +107,9 @@ int run_k_mean(const sla_shape* s, const void* k, float* partial, float* kmean, 
 int run_sparse_bwd_mma(const sla_shape* s, const BwdParams& p, cudaStream_t st);
 int run_linear_bwd(const sla_shape* s, const LinBwdParams& p, cudaStream_t st);
 int run_linear_bwd_q_tc(const sla_shape* s, const LinBwdParams& p, cudaStream_t st);
+// tcgen05 kernel for the per-chunk partials of the linear state (linear_state_tc.cu); SLA_ERR_UNSUPPORTED unless
+// head dim 128 and rows % 128 == 0
+int run_linear_state_partials_tc(const sla_shape* s, const void* k, const void* v, float* partial, int nch, int rows,
+                                 cudaStream_t st);
 
 }  // namespace sla

@@ -176,6 +176,19 @@ static int launch_state(const sla_shape* s, const T* k, const T* v, T* state, fl
                         int rows, cudaStream_t st) {
   int bh = s->B * s->H;
   dim3 grid(nch, bh);
+  const int n = D * D + D;
+  auto reduce = [&]() -> int {
+    SLA_CUDA_OK(launch_pdl<false>(linear_state_reduce_kernel<T>, dim3(ceil_div(n, 256), bh), dim3(256), 0, st,
+                                  static_cast<const float*>(partial), state, nch, n, 2 * D * D + D));
+    SLA_LAUNCH_OK();
+    return SLA_OK;
+  };
+  if (!(s->flags & SLA_FLAG_LEGACY_MMA)) {
+    // tcgen05 kernel (head dim 128, chunks of whole 128-row tiles); anything else takes the mma.sync kernel below
+    const int rc_tc = run_linear_state_partials_tc(s, k, v, partial, nch, rows, st);
+    if (rc_tc == SLA_OK) return reduce();
+    if (rc_tc != SLA_ERR_UNSUPPORTED) return rc_tc;
+  }
   const int smem = 4 * 64 * D * 2;
   auto go = [&](auto kern) -> int {
     SLA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -190,11 +203,7 @@ static int launch_state(const sla_shape* s, const T* k, const T* v, T* state, fl
     default: rc = go(linear_state_kernel<T, D, SLA_PHI_ELU>); break;
   }
   if (rc != SLA_OK) return rc;
-  int n = D * D + D;
-  SLA_CUDA_OK(launch_pdl<false>(linear_state_reduce_kernel<T>, dim3(ceil_div(n, 256), bh), dim3(256), 0, st,
-                         static_cast<const float*>(partial), state, nch, n, 2 * D * D + D));
-  SLA_LAUNCH_OK();
-  return SLA_OK;
+  return reduce();
 }
 
 int run_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, float* partial, int nch,

@@ -40,7 +40,7 @@ struct WsLinearState {
   size_t partial;  // fp32 [BH][NCH][D*D + D]
   size_t total;
   int nch;         // chunks per head
-  int rows;        // rows per chunk (multiple of 64)
+  int rows;        // rows per chunk (multiple of 128)
 };
 inline WsLinearState ws_linear_state(const sla_shape* s) {
   WsLinearState w;
@@ -50,7 +50,7 @@ inline WsLinearState ws_linear_state(const sla_shape* s) {
   // sharded over GPUs: at most 64 chunks per head, at least 512 rows per chunk.
   int nch = ws_ceil_div(s->L, 512);
   if (nch > 64) nch = 64;
-  int rows = (ws_ceil_div(s->L, nch) + 63) / 64 * 64;
+  int rows = (ws_ceil_div(s->L, nch) + 127) / 128 * 128;
   w.rows = rows;
   w.nch = ws_ceil_div(s->L, rows);
   w.partial = 0;
