@@ -2,7 +2,8 @@
 // top-k -> block LUT (+ optional 0/1 map and per-KV-block column lists).
 // Follows sparse_linear_attention/utils.py:21-67 including its rounding points: the column mean, the
 // smoothed K, the pooled means and the pooled scores are each rounded to the input dtype.
-// All kernels here are HBM/L2-bound integer/compare work; none uses tensor cores.
+// All kernels here are HBM/L2-bound streaming, integer and compare work; the one contraction (pooled Q x pooled K,
+// 3 MB of operands) runs on mma.sync for 16-bit inputs.
 #include <type_traits>
 
 #include "common.cuh"
@@ -63,7 +64,8 @@ __global__ void kmean_finalize_kernel(const float* __restrict__ partial, float* 
   int bh = blockIdx.x, d = threadIdx.x;
   if (d >= D) return;
   float s = 0.f;
-  for (int c = 0; c < nch; ++c) s += partial[(static_cast<size_t>(bh) * nch + c) * D + d];
+#pragma unroll 8
+  for (int c = 0; c < nch; ++c) s += partial[(static_cast<size_t>(bh) * nch + c) * D + d];   // loads batched, sum in order
   kmean[static_cast<size_t>(bh) * D + d] = round_to<TIn>(s / static_cast<float>(L));
 }
 

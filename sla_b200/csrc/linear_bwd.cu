@@ -179,7 +179,8 @@ __global__ void __launch_bounds__(256) linear_bwd_gsum_kernel(const float* __res
   if (i >= n) return;
   const float* p = part + static_cast<size_t>(bh) * nch * n + i;
   float s = 0.f;
-  for (int c = 0; c < nch; ++c) s += p[static_cast<size_t>(c) * n];
+#pragma unroll 8
+  for (int c = 0; c < nch; ++c) s += p[static_cast<size_t>(c) * n];   // loads batched, sum in order
   gsum[static_cast<size_t>(bh) * n + i] = s;
 }
 

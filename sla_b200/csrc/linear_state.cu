@@ -167,7 +167,8 @@ __global__ void linear_state_reduce_kernel(const float* __restrict__ partial, T*
   if (i >= n) return;
   const float* p = partial + static_cast<size_t>(bh) * nch * n + i;
   float s = 0.f;
-  for (int c = 0; c < nch; ++c) s += p[static_cast<size_t>(c) * n];
+#pragma unroll 8
+  for (int c = 0; c < nch; ++c) s += p[static_cast<size_t>(c) * n];   // loads batched, sum in order
   state[static_cast<size_t>(bh) * rec_stride + i] = Elem<T>::from_f(s);
 }
 
