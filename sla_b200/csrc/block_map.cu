@@ -64,8 +64,7 @@ __global__ void kmean_finalize_kernel(const float* __restrict__ partial, float* 
   int bh = blockIdx.x, d = threadIdx.x;
   if (d >= D) return;
   float s = 0.f;
-#pragma unroll 8
-  for (int c = 0; c < nch; ++c) s += partial[(static_cast<size_t>(bh) * nch + c) * D + d];   // loads batched, sum in order
+  for (int c = 0; c < nch; ++c) s += partial[(static_cast<size_t>(bh) * nch + c) * D + d];
   kmean[static_cast<size_t>(bh) * D + d] = round_to<TIn>(s / static_cast<float>(L));
 }
 
@@ -97,8 +96,18 @@ __device__ inline void pool_blocks(const TIn* __restrict__ x, const float* __res
   for (int r = row0 + rg; r < row1; r += RPW) {
     float v[N];
     VecLoad<TIn>::load(v, base + static_cast<size_t>(r) * D);
+    if constexpr (IS_K && sizeof(TIn) == 2) {
+      // K - mean rounded to the 16-bit type two at a time: the packed conversion does not go through the SFU pipe
 #pragma unroll
-    for (int i = 0; i < N; ++i) acc[i] += IS_K ? round_to<TIn>(v[i] - mean[i]) : v[i];
+      for (int i = 0; i < N; i += 2) {
+        const float2 r = Elem<TIn>::unpack2(Elem<TIn>::pack2(v[i] - mean[i], v[i + 1] - mean[i + 1]));
+        acc[i] += r.x;
+        acc[i + 1] += r.y;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < N; ++i) acc[i] += IS_K ? round_to<TIn>(v[i] - mean[i]) : v[i];
+    }
   }
 #pragma unroll
   for (int o = 16; o >= TPR; o >>= 1) {
