@@ -99,7 +99,8 @@ int run_sparse_bwd_tc(const sla_shape* s, const BwdParams& p, void* stats, cudaS
 bool sparse_bwd_tc_fits(const sla_shape* s);
 bool sparse_bwd_dq_pair_fits(const sla_shape* s);
 bool sparse_fwd_tc_fits(const sla_shape* s);
-int run_sparse_bwd_dq_pair(const sla_shape* s, const BwdParams& p, const void* stats, int Lpad, cudaStream_t st);
+// softmax variant: fills `stats` ({lse, delta} per row) itself; no-softmax variant (p.plain): reads it
+int run_sparse_bwd_dq_pair(const sla_shape* s, const BwdParams& p, void* stats, int Lpad, cudaStream_t st);
 int run_linear_state(const sla_shape* s, const void* k, const void* v, void* lin_state, float* partial,
                      int nch, int rows, cudaStream_t st);
 int run_linear_state_static(const sla_shape* s, const void* k, const void* v, void* lin_state, cudaStream_t st);

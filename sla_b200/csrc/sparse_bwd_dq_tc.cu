@@ -16,6 +16,9 @@
 // TMEM lane); group g owns score columns [32 g, 32 g + 32), i.e. half of entry g / 2 of the pair. Warp 16 TMA
 // producer, warp 17 MMA issuer. As in the other kernels a tile of two 64-row query blocks walks the union of
 // their lists with two mask bits per entry; an odd list gets its last entry twice, the copy masked out.
+// The kernel also takes the backward's row statistic delta = rowsum(o_s * dO) (kernel.py:102-105): the two groups that
+// move the dO tile to tensor memory hold its rows in registers at that point and read the matching rows of o_s from
+// global memory; {lse, delta} of the tile's rows go to the padded array the dK/dV kernel reads.
 // All waits are bounded (tc_common.cuh).
 #include <type_traits>
 
@@ -28,7 +31,13 @@ namespace tc {
 
 struct TcDqParams {
   const int32_t* lut;        // (B*H, mb, topk)
-  const float2* stats;       // (B*H, Lpad) {lse, delta}
+  const float2* stats;       // (B*H, Lpad) {lse, delta}: read in the no-softmax variant, WRITTEN otherwise (below)
+  // softmax variant: the kernel takes delta = rowsum(o_s * dO) (kernel.py:102-105) of its own 128 rows while it
+  // moves the dO tile to tensor memory, and leaves {lse, delta} (rows past L: {+inf, 0}) in `stats_out` for the
+  // dK/dV kernel; no separate pass over o_s and dO
+  const void* o_s;           // (B*H, L, D)
+  const float* lse;          // (B*H, L)
+  float2* stats_out;         // (B*H, Lpad)
   int* err;
   long long* trace;          // optional: 8 words per CTA {sm, start ns, end ns, then SM clocks since the start of the
                              // CTA: set-up done, operands in TMEM, first T1 there, accumulation done, stored}
@@ -68,6 +77,7 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_n_entries;
   __shared__ int s_abort;
+  __shared__ float s_delta[2][128];      // the two column halves' share of delta
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, bh = blockIdx.y;
@@ -288,16 +298,26 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
     const float sc = p.scale_log2;
     const int grow = tile * 128 + row;
     float my_lse = INFINITY, my_delta = 0.f;
-    {
+    constexpr int NCH = D / 16;                             // 16-byte chunks per thread (D/2 elements)
+    uint4 osr[PLAIN ? 1 : NCH];                             // this thread's half row of o_s (groups 2, 3)
+    if constexpr (PLAIN) {
       float2 st = p.stats[static_cast<size_t>(bh) * p.Lpad + min(grow, p.Lpad - 1)];
       if (grow < L) { my_lse = st.x; my_delta = st.y; }
+    } else {
+      if (grow < L) my_lse = p.lse[static_cast<size_t>(bh) * L + grow];
+      if (wg >= 2) {      // requested before the wait for the tiles, used behind it
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(p.o_s) +
+                                                          (static_cast<size_t>(bh) * L + min(grow, L - 1)) * D +
+                                                          (wg & 1) * (D / 2));
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) osr[c] = grow < L ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+      }
     }
     bool ok = !*abortp;
     if (ok) {
       // stationary tiles -> TMEM as 16-bit A operands: groups 0,1 copy the two column halves of Q, groups 2,3 of dO
       ok = mbar_wait(BAR(B_X), 0, kQErrX, p.err);
       if (ok) {
-        constexpr int NCH = D / 16;                           // 16-byte chunks per thread (D/2 elements)
         const uint32_t src = ((wg >> 1) ? sdO : sQ) + (((wg & 1) * (D / 2)) >> 6) * X_SLAB + row * 128;
         const int chunk0 = (((wg & 1) * (D / 2)) & 63) >> 3;
         uint32_t xr[NCH * 4];
@@ -306,11 +326,32 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
           ld_shared_v4(src + (((chunk0 + c) ^ (row & 7)) << 4), xr[4 * c], xr[4 * c + 1], xr[4 * c + 2], xr[4 * c + 3]);
         const uint32_t dst = tmem + lane_addr + ((wg >> 1) ? COL_XDO : COL_XQ) + (wg & 1) * (D / 4);
         if constexpr (NCH * 4 == 32) tmem_st_x32(dst, xr); else tmem_st_x16(dst, xr);
+        if constexpr (!PLAIN) {
+          if (wg >= 2) {   // dO half row (xr, in column order) times the o_s half row
+            float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+              const uint32_t ow[4] = {osr[c].x, osr[c].y, osr[c].z, osr[c].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 a = Elem<T>::unpack2(xr[4 * c + e]), b = Elem<T>::unpack2(ow[e]);
+                d0 = fmaf(a.x, b.x, d0);
+                d1 = fmaf(a.y, b.y, d1);
+              }
+            }
+            s_delta[wg & 1][row] = d0 + d1;
+          }
+        }
         tmem_wait_st();
         tc_fence_before();
       }
     }
     mbar_arrive_warp(BAR(B_XT), lane);
+    if constexpr (!PLAIN) {
+      asm volatile("bar.sync 2, 512;\n" ::: "memory");      // every compute thread, whatever its waits returned
+      my_delta = grow < L ? s_delta[0][row] + s_delta[1][row] : 0.f;
+      if (wg == 2) p.stats_out[static_cast<size_t>(bh) * p.Lpad + grow] = make_float2(my_lse, my_delta);
+    }
     if (ok) ok = list_ready();
     const int n_pairs = s_n_entries >> 1;
     if (trc) trc[4] = clock64() - clk0;
@@ -408,12 +449,12 @@ sparse_bwd_dq_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
 }  // namespace tc
 
 static int dq_pair_smem_bytes(int D, int topk) { return 1024 + 6 * 128 * D * 2 + (4 * topk + 4) * 4 + 16; }
-constexpr int kDqStaticSmem = 1024;   // statically allocated shared memory of the kernel (barriers)
+constexpr int kDqStaticSmem = 2048;   // statically allocated shared memory of the kernel (barriers, delta halves)
 
 bool sparse_bwd_dq_pair_fits(const sla_shape* s) { return dq_pair_smem_bytes(s->D, s->topk) + kDqStaticSmem <= 227 * 1024; }
 
 template <typename T, int D, int BM, bool PLAIN>
-static int launch_dq_pair(const sla_shape* s, const BwdParams& bp, const float2* stats, int Lpad, cudaStream_t st) {
+static int launch_dq_pair(const sla_shape* s, const BwdParams& bp, float2* stats, int Lpad, cudaStream_t st) {
   const int bh = s->B * s->H;
   const int smem = dq_pair_smem_bytes(D, bp.topk);
   if (!sparse_bwd_dq_pair_fits(s)) return SLA_ERR_BAD_SHAPE;
@@ -426,6 +467,7 @@ static int launch_dq_pair(const sla_shape* s, const BwdParams& bp, const float2*
   if ((rc = make_tmap_3d(&tdq, bp.dq, s->dtype, D, s->L, bh, 128)) != SLA_OK) return rc;
   tc::TcDqParams p;
   p.lut = bp.lut; p.stats = stats;
+  p.o_s = bp.o_s; p.lse = bp.lse; p.stats_out = stats;
   p.err = tc_error_word();
   if (p.err == nullptr) return SLA_ERR_CUDA;
   p.trace = trace_buffer() ? trace_buffer() + 2048 : nullptr;   // behind the two per-entry timelines of the other kernels
@@ -438,10 +480,11 @@ static int launch_dq_pair(const sla_shape* s, const BwdParams& bp, const float2*
   return SLA_OK;
 }
 
-// dQ of the sparse branch; `stats` as written by the row-statistics pre-pass. SLA_ERR_BAD_SHAPE (nothing
+// dQ of the sparse branch; `stats` ({lse, delta} per row, padded to Lpad rows per head) is written by the kernel, or
+// read by it in plain mode (filled by the caller). SLA_ERR_BAD_SHAPE (nothing
 // launched) when the entry list does not fit the kernel's shared memory.
-int run_sparse_bwd_dq_pair(const sla_shape* s, const BwdParams& bp, const void* stats, int Lpad, cudaStream_t st) {
-  const float2* sp = static_cast<const float2*>(stats);
+int run_sparse_bwd_dq_pair(const sla_shape* s, const BwdParams& bp, void* stats, int Lpad, cudaStream_t st) {
+  float2* sp = static_cast<float2*>(stats);
 #define SLA_DQ2(TT, DD, BB) \
   return bp.plain ? launch_dq_pair<TT, DD, BB, true>(s, bp, sp, Lpad, st) : launch_dq_pair<TT, DD, BB, false>(s, bp, sp, Lpad, st)
 #define SLA_DQ(TT)                                  \

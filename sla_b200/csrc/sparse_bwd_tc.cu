@@ -1,6 +1,6 @@
 // dK and dV of the block-sparse branch on tcgen05 / TMEM / TMA (mathematics:
-// sparse_linear_attention/kernel.py:167-237), the row statistics both backward kernels read
-// (kernel.py:85-105), and the host entry of the tcgen05 backward. dQ is sparse_bwd_dq_tc.cu.
+// sparse_linear_attention/kernel.py:167-237) and the host entry of the tcgen05 backward. dQ is sparse_bwd_dq_tc.cu;
+// it also leaves the row statistics this kernel reads (kernel.py:85-105).
 //
 // A CTA owns a 128-key tile (two adjacent KV blocks; K, V stationary in shared memory) and streams
 // 64-row slices Q_i, dO_i of the query blocks that selected either block:
@@ -17,8 +17,8 @@
 //   warp 16     TMA producer (stationary tiles once, then a ring of streamed tiles + row stats)
 //   warp 17     MMA issuer.
 // TMEM: acc1 [0,D) (dK), acc2 [D,2D) (dV), then per buffer T1 (64 cols), T2 (64 cols).
-// Row statistics (lse, delta) come from a padded (B*H, Lpad, 2) fp32 array written by a small
-// preprocessing kernel (delta = rowsum(o_s * dO), kernel.py:102-105; padding rows hold lse = +inf).
+// Row statistics (lse, delta) come from a padded (B*H, Lpad, 2) fp32 array written by the dQ kernel, which runs
+// first (delta = rowsum(o_s * dO), kernel.py:102-105; padding rows hold lse = +inf).
 // All waits are bounded; see tc_common.cuh.
 #include <type_traits>
 
@@ -576,54 +576,6 @@ static long long* g_trace_buffer = nullptr;
 void set_trace_buffer(long long* p) { g_trace_buffer = p; }
 long long* trace_buffer() { return g_trace_buffer; }
 
-// delta = rowsum(o_s * dO) (kernel.py:102-105) and lse, interleaved into a padded (B*H, Lpad) array;
-// rows in [L, Lpad) get lse = +inf, delta = 0 so that they contribute P = 0.
-template <typename T, int D>
-__global__ void __launch_bounds__(256) bwd_prep_kernel(const T* __restrict__ o_s, const T* __restrict__ d_o,
-                                                       const float* __restrict__ lse, float2* __restrict__ stats,
-                                                       float* __restrict__ delta_out, int L, int Lpad) {
-  // 64 rows per CTA, 8 per warp; a row is spread over LPR lanes with 16-byte loads, and the warp's
-  // loads of all its rows are issued before the first use.
-  constexpr int LPR = D / 8;              // lanes per row
-  constexpr int RPI = 32 / LPR;           // rows per warp iteration
-  constexpr int ITER = 8 / RPI;
-  pdl_entry();
-  const int bh = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane / LPR, col = (lane % LPR) * 8;
-  const int r_base = blockIdx.x * 64 + warp * 8;
-  uint4 a[ITER], b[ITER];
-#pragma unroll
-  for (int i = 0; i < ITER; ++i) {
-    const int r = r_base + i * RPI + sub;
-    if (r < L) {
-      const size_t off = (static_cast<size_t>(bh) * L + r) * D + col;
-      a[i] = *reinterpret_cast<const uint4*>(o_s + off);
-      b[i] = *reinterpret_cast<const uint4*>(d_o + off);
-    } else {
-      a[i] = b[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < ITER; ++i) {
-    const int r = r_base + i * RPI + sub;
-    const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a[i]);
-    const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b[i]);
-    float s = 0.f;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float2 x = Elem<T>::unpack2(aw[e]), y = Elem<T>::unpack2(bw[e]);
-      s += x.x * y.x + x.y * y.y;
-    }
-#pragma unroll
-    for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane % LPR == 0 && r < Lpad) {
-      float l = r < L ? lse[static_cast<size_t>(bh) * L + r] : INFINITY;
-      stats[static_cast<size_t>(bh) * Lpad + r] = make_float2(l, r < L ? s : 0.f);
-      if (r < L && delta_out) delta_out[static_cast<size_t>(bh) * L + r] = s;
-    }
-  }
-}
-
 static int bwd_tc_smem_bytes(int D, int max_entries) {
   const int NS = D == 128 ? 4 : 6;
   return 1024 + 2 * 128 * D * 2 + NS * 2 * 64 * D * 2 + NS * 512 + 2 * max_entries * 4 + 16;
@@ -670,12 +622,8 @@ static int run_bwd_tc_typed(const sla_shape* s, const BwdParams& bp, float2* sta
   const int bh = s->B * s->H;
   // nothing is launched unless both kernels fit: the caller falls back to another path on BAD_SHAPE
   if (!sparse_bwd_tc_fits(s)) return SLA_ERR_BAD_SHAPE;
-  if (!bp.plain) {   // plain mode: the caller has filled the row statistics
-    SLA_CUDA_OK(launch_pdl(bwd_prep_kernel<T, D>, dim3(ceil_div(Lpad, 64), bh), dim3(256), 0, st,
-                           static_cast<const T*>(bp.o_s), static_cast<const T*>(bp.d_o), bp.lse, stats, bp.delta, s->L,
-                           Lpad));
-    SLA_LAUNCH_OK();
-  }
+  // The row statistics {lse, delta}: the dQ kernel takes delta of its own rows on the way and leaves both for the
+  // dK/dV kernel; in plain mode the caller has filled them.
   int rc = run_sparse_bwd_dq_pair(s, bp, stats, Lpad, st);
   if (rc != SLA_OK) return rc;
   return bp.plain ? launch_dkdv<T, D, BM, true>(s, bp, stats, Lpad, st)
