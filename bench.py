@@ -676,7 +676,10 @@ def main():
     # profiles/sage_fwd_tc_c4s.md): dram__bytes_read.sum + dram__bytes_write.sum; null where not captured.
     # The captures are the launches of a whole module step: the forward there also writes o (100 MB at c3) and
     # the dK/dV kernel also reads dH; the c4 figure is the 8-head capture times 5 (traffic grows with the heads).
-    traffic_table = {("c3", "sparse_fwd"): 471.8e6, ("c3", "sparse_bwd_dq_dkdv"): 592.7e6 + 585.9e6,
+    # The dQ figure is that capture's 592.7 MB plus what the kernel reads and writes since it also takes the row
+    # statistics (o_s once, the statistics array): +18.9 MB in the 2-head capture of
+    # profiles/tcgen05_sparse_kernels_c3s.md, times 6 for the 12 heads.
+    traffic_table = {("c3", "sparse_fwd"): 471.8e6, ("c3", "sparse_bwd_dq_dkdv"): (592.7e6 + 6 * 18.9e6) + 585.9e6,
                      ("c4", "sparse_fwd"): 5 * 525.5e6, ("c4s", "sparse_fwd"): 525.5e6}
     if w.quantized:
         # no driver-measured 8-bit peak exists: measure an e4m3 GEMM here with the protocol of the bf16 one
